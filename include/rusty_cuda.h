@@ -1,0 +1,202 @@
+/*
+ * rusty_cuda.h — C ABI of the B200 (sm_100a) backend for rusty's
+ * quantized-linear path.
+ *
+ * Every entry point is what a Rust `extern "C"` block inside rusty-backend
+ * would bind to replace the wgpu implementation of the same operation; the
+ * reference interface each one stands in for is cited as file:line (paths
+ * inside the rusty repository).
+ *
+ * Conventions
+ *   - every function returns an int status (RUSTY_CUDA_OK == 0); nothing
+ *     throws, aborts or exits.  `rusty_cuda_last_error` gives the text.
+ *   - all operations enqueue on the context's single stream and return at
+ *     once (rusty: one wgpu::Queue, one submit per op, order = call order).
+ *     `rusty_cuda_buf_download` and `rusty_cuda_sync` are the only blocking
+ *     calls, like `UnifiedTensor::to_vec`'s `device.poll(Wait)`.
+ *   - the caller allocates every output buffer; no op allocates device memory
+ *     (the reference's ops only allocate a 16-byte uniform).
+ *   - one context per host thread per GPU.
+ *   - there is no CPU fallback: without a CUDA device every call fails with
+ *     RUSTY_CUDA_ERR_GPU_INITIALIZATION.
+ */
+#ifndef RUSTY_CUDA_H
+#define RUSTY_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define RUSTY_CUDA_API __attribute__((visibility("default")))
+#else
+#define RUSTY_CUDA_API
+#endif
+
+/* Status codes, named after the variants of rusty-backend's BackendError
+ * (rusty-backend/src/error.rs:13-61). */
+enum {
+    RUSTY_CUDA_OK = 0,
+    RUSTY_CUDA_ERR_GPU_INITIALIZATION = 1, /* GpuInitialization / DeviceCreation */
+    RUSTY_CUDA_ERR_MEMORY_ALLOCATION = 2,  /* MemoryAllocation / OutOfMemory */
+    RUSTY_CUDA_ERR_INVALID_DIMENSIONS = 3, /* InvalidDimensions */
+    RUSTY_CUDA_ERR_INVALID_DATA_TYPE = 4,  /* InvalidDataType */
+    RUSTY_CUDA_ERR_BUFFER_OPERATION = 5,   /* BufferOperation (size/offset out of range) */
+    RUSTY_CUDA_ERR_KERNEL_EXECUTION = 6,   /* KernelExecution (launch or async error) */
+    RUSTY_CUDA_ERR_UNSUPPORTED = 7,        /* UnsupportedOperation */
+    RUSTY_CUDA_ERR_DATA_TRANSFER = 8,      /* DataTransfer */
+    RUSTY_CUDA_ERR_INVALID_OPERATION = 9,  /* InvalidOperation (null handle, wrong state) */
+    RUSTY_CUDA_ERR_TIMEOUT = 10,           /* Timeout (a bounded device-side wait gave up) */
+    RUSTY_CUDA_ERR_OTHER = 11
+};
+
+/* Element types.  rusty's DType has FP32 and FP16 only
+ * (rusty-backend/src/lib.rs:56-76) and moves quantised bytes as untyped
+ * buffers; the fused path needs to name them. */
+enum {
+    RUSTY_CUDA_F32 = 0,
+    RUSTY_CUDA_F16 = 1,
+    RUSTY_CUDA_BF16 = 2,
+    RUSTY_CUDA_I8 = 3,
+    RUSTY_CUDA_U8 = 4
+};
+
+/* Quantisation modes of a fused linear. */
+enum {
+    /* u8 weights, f32 scale and bias per group of 64 consecutive elements of
+     * the flat row-major weight: the layout `affine_dequantize` consumes
+     * (rusty-backend/src/kernels.wgsl:385-400, rusty-loader/src/lib.rs:155-218). */
+    RUSTY_CUDA_QMODE_AFFINE_G64 = 0,
+    /* signed int8 weights, one f32 scale per output feature, no bias. */
+    RUSTY_CUDA_QMODE_SYM_ROW = 1
+};
+
+/* Storage order of a fused linear's weight. */
+enum {
+    RUSTY_CUDA_LAYOUT_NK = 0, /* [out, in]: the matmul_bt contraction (kernels.wgsl:234-242) */
+    RUSTY_CUDA_LAYOUT_KN = 1  /* [in, out]: the matmul_tiled contraction (kernels.wgsl:16-54), rusty's Linear */
+};
+
+typedef struct rusty_cuda_ctx rusty_cuda_ctx;
+typedef struct rusty_cuda_buf rusty_cuda_buf;
+typedef struct rusty_cuda_qlinear rusty_cuda_qlinear;
+typedef struct rusty_cuda_comm rusty_cuda_comm;
+typedef struct rusty_cuda_graph rusty_cuda_graph;
+
+/* ---- context: WgpuContext::new + ComputeEngine::new -----------------------
+ * (rusty-backend/src/lib.rs:20-47, :343).  Owns the device, one stream, the
+ * exact-size-bin buffer pool and the last-error text. */
+RUSTY_CUDA_API int rusty_cuda_device_count(int* count);
+RUSTY_CUDA_API int rusty_cuda_ctx_create(int device, rusty_cuda_ctx** out);
+RUSTY_CUDA_API int rusty_cuda_ctx_destroy(rusty_cuda_ctx* ctx);
+/* WgpuContext::adapter_info (lib.rs:49-52): "<name> (CUDA sm_XY)". */
+RUSTY_CUDA_API int rusty_cuda_ctx_adapter_info(rusty_cuda_ctx* ctx, char* dst, size_t dst_len);
+/* Text of the most recent failure on this context (or of the most recent
+ * failure with no context when ctx is NULL).  Never NULL. */
+RUSTY_CUDA_API const char* rusty_cuda_last_error(rusty_cuda_ctx* ctx);
+/* device.poll(Maintain::Wait) (lib.rs:233): drain the stream; reports any
+ * asynchronous kernel error and any device-side timeout flag. */
+RUSTY_CUDA_API int rusty_cuda_sync(rusty_cuda_ctx* ctx);
+/* Number of kernels this context has launched so far (host-side counter). */
+RUSTY_CUDA_API int rusty_cuda_ctx_launch_count(rusty_cuda_ctx* ctx, uint64_t* count);
+/* The context's CUDA stream as an opaque pointer (cudaStream_t), for callers
+ * that record their own events on it. */
+RUSTY_CUDA_API int rusty_cuda_ctx_stream(rusty_cuda_ctx* ctx, void** stream);
+
+/* ---- buffers: UnifiedTensor's storage --------------------------------------
+ * pooled != 0  : UnifiedTensor::empty (lib.rs:141-153) — taken from, and on the
+ *                last release returned to, the exact-byte-size bin of the pool
+ *                (rusty-backend/src/pool.rs:30-50); contents uninitialised.
+ * pooled == 0  : UnifiedTensor::new / from_bytes (lib.rs:115-135, :165-190) —
+ *                a fresh allocation freed on the last release.
+ * Buffers are reference counted like the Arc<TensorData> they replace
+ * (`reshaped` views share storage, lib.rs:198-213). */
+RUSTY_CUDA_API int rusty_cuda_buf_alloc(rusty_cuda_ctx* ctx, size_t bytes, int pooled, rusty_cuda_buf** out);
+RUSTY_CUDA_API int rusty_cuda_buf_retain(rusty_cuda_buf* buf);
+RUSTY_CUDA_API int rusty_cuda_buf_release(rusty_cuda_buf* buf);
+RUSTY_CUDA_API int rusty_cuda_buf_size(const rusty_cuda_buf* buf, size_t* bytes);
+RUSTY_CUDA_API int rusty_cuda_buf_device_ptr(const rusty_cuda_buf* buf, void** ptr);
+/* queue.write_buffer / create_buffer_init (lib.rs:110-112, :117-126). */
+RUSTY_CUDA_API int rusty_cuda_buf_upload(rusty_cuda_ctx* ctx, rusty_cuda_buf* dst, size_t dst_offset,
+                                         const void* src, size_t bytes);
+/* UnifiedTensor::to_vec (lib.rs:215-240): copy back and wait. */
+RUSTY_CUDA_API int rusty_cuda_buf_download(rusty_cuda_ctx* ctx, const rusty_cuda_buf* src, size_t src_offset,
+                                           void* dst, size_t bytes);
+/* ComputeEngine::copy_tensor (lib.rs:4019-4037): all of src to dst at a byte offset. */
+RUSTY_CUDA_API int rusty_cuda_buf_copy(rusty_cuda_ctx* ctx, const rusty_cuda_buf* src, rusty_cuda_buf* dst,
+                                       size_t dst_offset);
+/* BufferPool::clear (pool.rs:52-55) and a count of idle pooled buffers. */
+RUSTY_CUDA_API int rusty_cuda_pool_clear(rusty_cuda_ctx* ctx);
+RUSTY_CUDA_API int rusty_cuda_pool_idle_count(rusty_cuda_ctx* ctx, size_t bytes, size_t* count);
+/* Pinned host staging memory for callers that want asynchronous transfers. */
+RUSTY_CUDA_API int rusty_cuda_host_alloc(size_t bytes, void** out);
+RUSTY_CUDA_API int rusty_cuda_host_free(void* p);
+/* Asynchronous variants of upload/download: `src`/`dst` should be pinned; the
+ * call returns once the copy is enqueued. */
+RUSTY_CUDA_API int rusty_cuda_buf_upload_async(rusty_cuda_ctx* ctx, rusty_cuda_buf* dst, size_t dst_offset,
+                                               const void* src, size_t bytes);
+RUSTY_CUDA_API int rusty_cuda_buf_download_async(rusty_cuda_ctx* ctx, const rusty_cuda_buf* src,
+                                                 size_t src_offset, void* dst, size_t bytes);
+
+/* ---- unfused operators: ComputeEngine methods ------------------------------
+ * Dimensions are explicit because the C ABI carries no shape vector; the Rust
+ * side passes the values the reference reads from the tensors' shapes. */
+/* ComputeEngine::matmul -> WGSL matmul_tiled (lib.rs:4403-4453, kernels.wgsl:16-54):
+ * out[M,N] = a[M,K] * b[K,N], f32. */
+RUSTY_CUDA_API int rusty_cuda_matmul_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* a, const rusty_cuda_buf* b,
+                                         rusty_cuda_buf* out, uint32_t M, uint32_t K, uint32_t N);
+/* ComputeEngine::matmul_bt -> WGSL matmul_bt (lib.rs:4299-4349, kernels.wgsl:234-242):
+ * out[M,N] = a[M,K] * b[N,K]^T, f32. */
+RUSTY_CUDA_API int rusty_cuda_matmul_bt_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* a, const rusty_cuda_buf* b,
+                                            rusty_cuda_buf* out, uint32_t M, uint32_t K, uint32_t N);
+/* ComputeEngine::dequantize -> WGSL dequantize (lib.rs:4872-4899, kernels.wgsl:156-166):
+ * `n_in` = product of the input tensor's shape (bytes to unpack); the input and
+ * output array lengths that guard the shader's loads and stores are taken from
+ * the buffers' sizes (in/4 words, out/4 floats). */
+RUSTY_CUDA_API int rusty_cuda_dequantize_u8(rusty_cuda_ctx* ctx, const rusty_cuda_buf* in, rusty_cuda_buf* out,
+                                            size_t n_in);
+/* ComputeEngine::affine_dequantize -> WGSL affine_dequantize (lib.rs:4939-4990,
+ * kernels.wgsl:385-400): out[i] = f32(u8[i]) * scales[i/64] + biases[i/64] for
+ * every i < n (the reference's dispatch drops i >= 4 194 240; this does not). */
+RUSTY_CUDA_API int rusty_cuda_affine_dequantize_g64(rusty_cuda_ctx* ctx, const rusty_cuda_buf* weight,
+                                                    const rusty_cuda_buf* scales, const rusty_cuda_buf* biases,
+                                                    rusty_cuda_buf* out, size_t n);
+
+/* ComputeEngine::add -> WGSL add (lib.rs:4039-4083, kernels.wgsl:139-144): out[i] = a[i] + b[i],
+ * f32, i < n.  On the path only as the sum that closes Linear's LoRA branch
+ * (rusty-graph/src/lib.rs:78). */
+RUSTY_CUDA_API int rusty_cuda_add_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* a, const rusty_cuda_buf* b,
+                                      rusty_cuda_buf* out, size_t n);
+
+/* ---- fused quantised linear ------------------------------------------------
+ * Replaces the composition "upload_quantized -> affine_dequantize once -> f32
+ * matmul per forward" (rusty-loader/src/lib.rs:155-218 followed by
+ * rusty-graph/src/lib.rs:69-70 -> rusty-autograd/src/lib.rs:468-477) with
+ * kernels that read the 1-byte weights and their scales once per forward.
+ * The object borrows (retains) the three buffers; it copies nothing.
+ *   AFFINE_G64: weight u8 [N*K], scales/biases f32 [N*K/64]; K % 64 == 0 for
+ *               LAYOUT_NK (N % 64 == 0 for LAYOUT_KN) so a group never
+ *               straddles two rows.
+ *   SYM_ROW   : weight i8 [N*K], scales f32 [N], biases NULL. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_create(rusty_cuda_ctx* ctx, rusty_cuda_buf* weight, rusty_cuda_buf* scales,
+                                             rusty_cuda_buf* biases, uint32_t N, uint32_t K, int layout, int qmode,
+                                             rusty_cuda_qlinear** out);
+RUSTY_CUDA_API int rusty_cuda_qlinear_destroy(rusty_cuda_qlinear* ql);
+/* Linear::forward for a quantised weight (rusty-graph/src/lib.rs:69-70):
+ * y[M,N] = x[M,K] * W^T-or-W with fp32 accumulation.  x_dtype / y_dtype are
+ * RUSTY_CUDA_F32 or RUSTY_CUDA_BF16. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_forward(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql,
+                                              const rusty_cuda_buf* x, int x_dtype, uint32_t M,
+                                              rusty_cuda_buf* y, int y_dtype);
+/* Name of the kernel `rusty_cuda_qlinear_forward` would launch for this shape
+ * ("gemv_f32", "tcgen05", ...); for tests and logs. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype,
+                                           char* dst, size_t dst_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RUSTY_CUDA_H */

@@ -1,0 +1,284 @@
+"""Host-side mirror of rusty-backend's tensor / engine surface over the C ABI.
+
+Same names, argument meaning and error behaviour as the reference's Rust types,
+so the parity tests read like tests of rusty itself:
+
+    CudaContext    <- WgpuContext         (rusty-backend/src/lib.rs:11-53)
+    DType          <- DType               (lib.rs:56-76), extended with BF16/I8/U8
+    UnifiedTensor  <- UnifiedTensor       (lib.rs:78-241)
+    ComputeEngine  <- ComputeEngine       (lib.rs:343; matmul :4403, matmul_bt :4299,
+                                           dequantize :4872, affine_dequantize :4939,
+                                           copy_tensor :4019)
+    QLinear        <- (new) the fused int8 weight the engine multiplies in place of
+                      the load-time-dequantised f32 copy (rusty-loader/src/lib.rs:155-218)
+
+Everything here is glue: each method is one call into librusty_cuda.  numpy is
+used for host arrays only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from enum import IntEnum
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import capi
+from .capi import BackendError, check, lib
+
+
+class DType(IntEnum):
+    FP32 = capi.F32
+    FP16 = capi.F16
+    BF16 = capi.BF16
+    I8 = capi.I8
+    U8 = capi.U8
+
+    def size_bytes(self) -> int:
+        return {DType.FP32: 4, DType.FP16: 2, DType.BF16: 2, DType.I8: 1, DType.U8: 1}[self]
+
+
+def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even f32 -> bf16, returned as uint16 bit patterns."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    rounded = u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))
+    return (rounded >> np.uint32(16)).astype(np.uint16)
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+class CudaContext:
+    """One device, one in-order stream, one buffer pool (WgpuContext::new)."""
+
+    def __init__(self, device: int = 0):
+        h = C.c_void_p()
+        check(lib().rusty_cuda_ctx_create(device, C.byref(h)))
+        self._h = h
+        self.device = device
+
+    @property
+    def handle(self) -> C.c_void_p:
+        if self._h is None:
+            raise BackendError(capi.ERR_INVALID_OPERATION, "context already destroyed")
+        return self._h
+
+    def adapter_info(self) -> str:
+        buf = C.create_string_buffer(256)
+        check(lib().rusty_cuda_ctx_adapter_info(self.handle, buf, 256), self.handle)
+        return buf.value.decode()
+
+    def sync(self) -> None:
+        check(lib().rusty_cuda_sync(self.handle), self.handle)
+
+    def launch_count(self) -> int:
+        n = C.c_uint64()
+        check(lib().rusty_cuda_ctx_launch_count(self.handle, C.byref(n)), self.handle)
+        return n.value
+
+    def stream(self) -> int:
+        s = C.c_void_p()
+        check(lib().rusty_cuda_ctx_stream(self.handle, C.byref(s)), self.handle)
+        return s.value or 0
+
+    def pool_idle_count(self, nbytes: int) -> int:
+        n = C.c_size_t()
+        check(lib().rusty_cuda_pool_idle_count(self.handle, nbytes, C.byref(n)), self.handle)
+        return n.value
+
+    def pool_clear(self) -> None:
+        check(lib().rusty_cuda_pool_clear(self.handle), self.handle)
+
+    def destroy(self) -> None:
+        if self._h is not None:
+            lib().rusty_cuda_ctx_destroy(self._h)
+            self._h = None
+
+
+class _Storage:
+    """Reference-counted device buffer (the Arc<TensorData> of the reference)."""
+
+    def __init__(self, ctx: CudaContext, nbytes: int, pooled: bool):
+        h = C.c_void_p()
+        check(lib().rusty_cuda_buf_alloc(ctx.handle, nbytes, 1 if pooled else 0, C.byref(h)), ctx.handle)
+        self.h = h
+        self.ctx = ctx
+        self.nbytes = nbytes
+
+    def __del__(self):
+        try:
+            if self.h is not None and self.ctx._h is not None:
+                lib().rusty_cuda_buf_release(self.h)
+        except Exception:
+            pass
+        self.h = None
+
+
+class UnifiedTensor:
+    """Buffer + shape + dtype tag."""
+
+    def __init__(self, storage: _Storage, shape: Sequence[int], dtype: DType):
+        self._data = storage
+        self.shape = list(shape)
+        self.dtype = dtype
+
+    # -- constructors (lib.rs:115-196) --
+    @staticmethod
+    def new(ctx: CudaContext, data, shape: Sequence[int]) -> "UnifiedTensor":
+        arr = np.ascontiguousarray(data, dtype=np.float32)
+        return UnifiedTensor.from_bytes_with_dtype(ctx, arr, shape, DType.FP32)
+
+    @staticmethod
+    def empty(ctx: CudaContext, shape: Sequence[int]) -> "UnifiedTensor":
+        return UnifiedTensor.empty_with_dtype(ctx, shape, DType.FP32)
+
+    @staticmethod
+    def empty_with_dtype(ctx: CudaContext, shape: Sequence[int], dtype: DType) -> "UnifiedTensor":
+        n = int(np.prod(shape, dtype=np.int64)) * dtype.size_bytes()
+        return UnifiedTensor(_Storage(ctx, n, pooled=True), shape, dtype)
+
+    @staticmethod
+    def zeros(ctx: CudaContext, shape: Sequence[int]) -> "UnifiedTensor":
+        return UnifiedTensor.new(ctx, np.zeros(int(np.prod(shape, dtype=np.int64)), np.float32), shape)
+
+    @staticmethod
+    def from_bytes(ctx: CudaContext, data, shape: Sequence[int]) -> "UnifiedTensor":
+        return UnifiedTensor.from_bytes_with_dtype(ctx, data, shape, DType.FP32)
+
+    @staticmethod
+    def from_bytes_with_dtype(ctx: CudaContext, data, shape: Sequence[int], dtype: DType) -> "UnifiedTensor":
+        raw = np.ascontiguousarray(data).view(np.uint8).ravel()
+        st = _Storage(ctx, raw.size, pooled=False)
+        t = UnifiedTensor(st, shape, dtype)
+        t.write_data(ctx, raw)
+        return t
+
+    @staticmethod
+    def from_bf16(ctx: CudaContext, data_f32, shape: Sequence[int]) -> "UnifiedTensor":
+        """Upload f32 host values rounded (RNE) to bf16."""
+        return UnifiedTensor.from_bytes_with_dtype(ctx, f32_to_bf16_bits(np.asarray(data_f32, np.float32)), shape, DType.BF16)
+
+    # -- accessors --
+    def buffer(self) -> C.c_void_p:
+        return self._data.h
+
+    def size_in_bytes(self) -> int:
+        return self._data.nbytes
+
+    def device_ptr(self) -> int:
+        p = C.c_void_p()
+        check(lib().rusty_cuda_buf_device_ptr(self._data.h, C.byref(p)))
+        return p.value or 0
+
+    def write_data(self, ctx: CudaContext, data, offset: int = 0) -> None:
+        raw = np.ascontiguousarray(data).view(np.uint8).ravel()
+        check(lib().rusty_cuda_buf_upload(ctx.handle, self._data.h, offset, raw.ctypes.data_as(C.c_void_p), raw.size),
+              ctx.handle)
+
+    def reshaped(self, new_shape: Sequence[int]) -> "UnifiedTensor":
+        cur = int(np.prod(self.shape, dtype=np.int64))
+        new = int(np.prod(new_shape, dtype=np.int64))
+        assert cur == new, f"Cannot reshape tensor of size {cur} to {list(new_shape)}"
+        return UnifiedTensor(self._data, new_shape, self.dtype)
+
+    def to_bytes(self, ctx: CudaContext) -> np.ndarray:
+        out = np.empty(self._data.nbytes, np.uint8)
+        check(lib().rusty_cuda_buf_download(ctx.handle, self._data.h, 0, out.ctypes.data_as(C.c_void_p), out.size),
+              ctx.handle)
+        return out
+
+    def to_vec(self, ctx: CudaContext) -> np.ndarray:
+        """Blocking readback.  FP32 tensors come back as float32 (the reference
+        always reinterprets as f32); BF16 as float32 values; byte types as is."""
+        raw = self.to_bytes(ctx)
+        if self.dtype == DType.BF16:
+            return bf16_bits_to_f32(raw.view(np.uint16))
+        if self.dtype == DType.I8:
+            return raw.view(np.int8)
+        if self.dtype == DType.U8:
+            return raw
+        return raw[: raw.size // 4 * 4].view(np.float32)
+
+
+class QLinear:
+    """A weight kept in its 1-byte quantised form on the device."""
+
+    def __init__(self, ctx: CudaContext, weight: UnifiedTensor, scales: UnifiedTensor,
+                 biases: Optional[UnifiedTensor], out_features: int, in_features: int,
+                 layout: int = capi.LAYOUT_NK, qmode: int = capi.QMODE_SYM_ROW):
+        h = C.c_void_p()
+        check(lib().rusty_cuda_qlinear_create(ctx.handle, weight.buffer(), scales.buffer(),
+                                              biases.buffer() if biases is not None else None,
+                                              out_features, in_features, layout, qmode, C.byref(h)), ctx.handle)
+        self._h = h
+        self.ctx = ctx
+        self.N, self.K = out_features, in_features
+        self.layout, self.qmode = layout, qmode
+        self._keep = (weight, scales, biases)
+
+    @staticmethod
+    def from_host(ctx: CudaContext, q: np.ndarray, scales: np.ndarray, biases: Optional[np.ndarray] = None,
+                  layout: int = capi.LAYOUT_NK) -> "QLinear":
+        """q: int8 (SYM_ROW, no biases) or uint8 (AFFINE_G64 with biases), 2-D in
+        the storage order `layout` names."""
+        q = np.ascontiguousarray(q)
+        N, K = (q.shape if layout == capi.LAYOUT_NK else q.shape[::-1])
+        affine = biases is not None
+        wt = UnifiedTensor.from_bytes_with_dtype(ctx, q, list(q.shape), DType.U8 if affine else DType.I8)
+        st = UnifiedTensor.new(ctx, np.asarray(scales, np.float32).ravel(), [int(np.size(scales))])
+        bt = UnifiedTensor.new(ctx, np.asarray(biases, np.float32).ravel(), [int(np.size(biases))]) if affine else None
+        return QLinear(ctx, wt, st, bt, N, K, layout, capi.QMODE_AFFINE_G64 if affine else capi.QMODE_SYM_ROW)
+
+    def plan(self, M: int, x_dtype: DType = DType.FP32, y_dtype: DType = DType.FP32) -> str:
+        buf = C.create_string_buffer(64)
+        check(lib().rusty_cuda_qlinear_plan(self._h, int(x_dtype), M, int(y_dtype), buf, 64))
+        return buf.value.decode()
+
+    def __del__(self):
+        try:
+            if self._h is not None and self.ctx._h is not None:
+                lib().rusty_cuda_qlinear_destroy(self._h)
+        except Exception:
+            pass
+        self._h = None
+
+
+class ComputeEngine:
+    """The operator surface of rusty-backend's ComputeEngine for this path.
+    Methods enqueue on the context's stream and return; the caller allocates
+    every output."""
+
+    def __init__(self, ctx: CudaContext):
+        self._ctx = ctx
+
+    def matmul(self, ctx: CudaContext, a: UnifiedTensor, b: UnifiedTensor, out: UnifiedTensor) -> None:
+        m, k, n = a.shape[0], a.shape[1], b.shape[1]
+        check(lib().rusty_cuda_matmul_f32(ctx.handle, a.buffer(), b.buffer(), out.buffer(), m, k, n), ctx.handle)
+
+    def matmul_bt(self, ctx: CudaContext, a: UnifiedTensor, b: UnifiedTensor, out: UnifiedTensor) -> None:
+        m, k, n = a.shape[0], a.shape[1], b.shape[0]
+        check(lib().rusty_cuda_matmul_bt_f32(ctx.handle, a.buffer(), b.buffer(), out.buffer(), m, k, n), ctx.handle)
+
+    def dequantize(self, ctx: CudaContext, input: UnifiedTensor, out: UnifiedTensor) -> None:
+        total = int(np.prod(input.shape, dtype=np.int64))
+        check(lib().rusty_cuda_dequantize_u8(ctx.handle, input.buffer(), out.buffer(), total), ctx.handle)
+
+    def affine_dequantize(self, ctx: CudaContext, weight: UnifiedTensor, scales: UnifiedTensor,
+                          biases: UnifiedTensor, out: UnifiedTensor) -> None:
+        total = int(np.prod(out.shape, dtype=np.int64))
+        check(lib().rusty_cuda_affine_dequantize_g64(ctx.handle, weight.buffer(), scales.buffer(), biases.buffer(),
+                                                     out.buffer(), total), ctx.handle)
+
+    def add(self, ctx: CudaContext, a: UnifiedTensor, b: UnifiedTensor, out: UnifiedTensor) -> None:
+        total = int(np.prod(out.shape, dtype=np.int64))
+        check(lib().rusty_cuda_add_f32(ctx.handle, a.buffer(), b.buffer(), out.buffer(), total), ctx.handle)
+
+    def copy_tensor(self, ctx: CudaContext, src: UnifiedTensor, dst: UnifiedTensor, dst_offset: int) -> None:
+        check(lib().rusty_cuda_buf_copy(ctx.handle, src.buffer(), dst.buffer(), dst_offset), ctx.handle)
+
+    def qlinear(self, ctx: CudaContext, x: UnifiedTensor, w: QLinear, out: UnifiedTensor) -> None:
+        """out[M,N] = x[M,K] (.) w, fused dequantise + multiply."""
+        m = int(np.prod(x.shape[:-1], dtype=np.int64))
+        check(lib().rusty_cuda_qlinear_forward(ctx.handle, w._h, x.buffer(), int(x.dtype), m, out.buffer(),
+                                               int(out.dtype)), ctx.handle)

@@ -1,0 +1,128 @@
+// Internal definitions shared by the translation units of librusty_cuda.
+// Nothing here is part of the C ABI (see include/rusty_cuda.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "rusty_cuda.h"
+
+// Device-side status word shared by every kernel that can give up on a bounded
+// wait.  Lives in pinned, mapped host memory so the host can read it without a
+// copy and a kernel can set it with a plain store.
+struct rusty_cuda_dev_status {
+    unsigned int timeout_flag;   // != 0: some bounded wait ran out
+    unsigned int timeout_where;  // kernel-defined site id of the first give-up
+};
+
+struct rusty_cuda_ctx {
+    int device = -1;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    size_t smem_optin = 0;
+    cudaStream_t stream = nullptr;
+    std::string name;
+    std::string last_error;
+    std::atomic<uint64_t> launches{0};
+    // exact-byte-size bins, like rusty-backend/src/pool.rs
+    std::mutex pool_mu;
+    std::unordered_map<size_t, std::vector<void*>> pool_bins;
+    // device-visible status word (pinned + mapped)
+    rusty_cuda_dev_status* status_host = nullptr;
+    rusty_cuda_dev_status* status_dev = nullptr;
+};
+
+struct rusty_cuda_buf {
+    rusty_cuda_ctx* ctx = nullptr;
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    bool pooled = false;
+    bool borrowed = false;  // storage owned by someone else (IPC import / wrap)
+    std::atomic<int> refs{1};
+};
+
+struct rusty_cuda_qlinear {
+    rusty_cuda_ctx* ctx = nullptr;
+    rusty_cuda_buf* weight = nullptr;
+    rusty_cuda_buf* scales = nullptr;
+    rusty_cuda_buf* biases = nullptr;
+    uint32_t N = 0, K = 0;
+    int layout = 0, qmode = 0;
+};
+
+namespace rusty {
+
+int fail(rusty_cuda_ctx* ctx, int code, const char* fmt, ...);
+int check_cuda(rusty_cuda_ctx* ctx, cudaError_t e, const char* what);
+
+// RAII: make the context's device current for the duration of a call.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = (cudaSetDevice(dev) == cudaSuccess);
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+inline void count_launch(rusty_cuda_ctx* ctx, uint64_t n = 1) { ctx->launches.fetch_add(n, std::memory_order_relaxed); }
+
+// Checks the launch error of the kernel just enqueued.
+int after_launch(rusty_cuda_ctx* ctx, const char* kernel);
+
+// Kernel launchers implemented in the .cu files -----------------------------
+int launch_matmul_f32(rusty_cuda_ctx* ctx, const float* a, const float* b, float* out, uint32_t M, uint32_t K,
+                      uint32_t N);
+int launch_matmul_bt_f32(rusty_cuda_ctx* ctx, const float* a, const float* b, float* out, uint32_t M, uint32_t K,
+                         uint32_t N);
+int launch_dequantize_u8(rusty_cuda_ctx* ctx, const uint32_t* in, size_t in_words, size_t n_in, float* out,
+                         size_t n_out);
+int launch_affine_dequantize_g64(rusty_cuda_ctx* ctx, const uint8_t* w, const float* scales, const float* biases,
+                                 float* out, size_t n);
+
+struct QLinearArgs {
+    const uint8_t* w;
+    const float* scales;
+    const float* biases;
+    uint32_t N, K;  // N: output features computed by this call (rows of w it reads)
+    int layout, qmode;
+    const void* x;
+    int x_dtype;
+    uint32_t M;
+    void* y;
+    int y_dtype;
+    uint32_t ldy;    // row stride of y in elements (>= N)
+    uint32_t y_col0; // first output column written (for shards writing into a wider y)
+};
+
+bool gemv_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
+int launch_gemv(rusty_cuda_ctx* ctx, const QLinearArgs& a);
+
+// Tensor-core (tcgen05 / TMEM) path.
+bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
+uint32_t tc_min_rows();
+int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
+
+const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
+// Forward into columns [y_col0, y_col0 + N) of a y whose rows are ldy elements apart.
+int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
+                         uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0);
+
+}  // namespace rusty
+
+#define RUSTY_REQUIRE_CTX(ctx)                                                                            \
+    do {                                                                                                  \
+        if (!(ctx)) return rusty::fail(nullptr, RUSTY_CUDA_ERR_INVALID_OPERATION, "%s: null context", __func__); \
+    } while (0)

@@ -1,0 +1,150 @@
+// Fused quantised Linear: object, shape checks and kernel selection.
+//
+// Stands in for the reference's Linear::forward over a quantised weight
+// (rusty-graph/src/lib.rs:69-70), which there is "dequantise once at load
+// (rusty-loader/src/lib.rs:155-218), then an f32 matmul per call".
+#include <cstring>
+
+#include "internal.h"
+
+using namespace rusty;
+
+namespace rusty {
+
+static size_t dtype_size(int dt) {
+    switch (dt) {
+        case RUSTY_CUDA_F32: return 4;
+        case RUSTY_CUDA_BF16: return 2;
+        default: return 0;
+    }
+}
+
+// Which kernel a forward of this shape runs.
+const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype) {
+    QLinearArgs a{};
+    a.N = ql->N;
+    a.K = ql->K;
+    a.layout = ql->layout;
+    a.qmode = ql->qmode;
+    a.x_dtype = x_dtype;
+    a.y_dtype = y_dtype;
+    a.M = M;
+    if (tc_supported(ql->ctx, a) && M >= tc_min_rows()) return "tcgen05";
+    if (gemv_supported(ql->ctx, a)) return "gemv";
+    return "unsupported";
+}
+
+int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
+                         uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0) {
+    if (!ql || !x || !y) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: null argument");
+    if (ql->ctx != ctx) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: object belongs to another context");
+    size_t xs = dtype_size(x_dtype), ys = dtype_size(y_dtype);
+    if (!xs || !ys)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DATA_TYPE, "qlinear_forward: x/y must be f32 or bf16 (got %d, %d)", x_dtype,
+                    y_dtype);
+    if (ldy < y_col0 + ql->N)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward: row stride %u < first column %u + N %u", ldy,
+                    y_col0, ql->N);
+    if (x->bytes < (size_t)M * ql->K * xs)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward: x holds %zu bytes, [%u,%u] needs %zu", x->bytes, M,
+                    ql->K, (size_t)M * ql->K * xs);
+    if (y->bytes < (size_t)M * ldy * ys)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward: y holds %zu bytes, [%u,%u] needs %zu", y->bytes, M,
+                    ldy, (size_t)M * ldy * ys);
+    if (M == 0 || ql->N == 0) return RUSTY_CUDA_OK;
+    QLinearArgs a{};
+    a.w = (const uint8_t*)ql->weight->ptr;
+    a.scales = (const float*)ql->scales->ptr;
+    a.biases = ql->biases ? (const float*)ql->biases->ptr : nullptr;
+    a.N = ql->N;
+    a.K = ql->K;
+    a.layout = ql->layout;
+    a.qmode = ql->qmode;
+    a.x = x->ptr;
+    a.x_dtype = x_dtype;
+    a.M = M;
+    a.y = y->ptr;
+    a.y_dtype = y_dtype;
+    a.ldy = ldy;
+    a.y_col0 = y_col0;
+    DeviceGuard g(ctx->device);
+    if (tc_supported(ctx, a) && M >= tc_min_rows()) return launch_tc(ctx, a);
+    if (gemv_supported(ctx, a)) return launch_gemv(ctx, a);
+    return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED,
+                "qlinear_forward: no kernel for N=%u K=%u layout=%d (K %% 16 == 0 for [N,K], N %% 16 == 0 for [K,N])", ql->N,
+                ql->K, ql->layout);
+}
+
+}  // namespace rusty
+
+extern "C" {
+
+int rusty_cuda_qlinear_create(rusty_cuda_ctx* ctx, rusty_cuda_buf* weight, rusty_cuda_buf* scales, rusty_cuda_buf* biases,
+                              uint32_t N, uint32_t K, int layout, int qmode, rusty_cuda_qlinear** out) {
+    RUSTY_REQUIRE_CTX(ctx);
+    if (!out) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_create: null out pointer");
+    *out = nullptr;
+    if (!weight || !scales) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_create: weight and scales are required");
+    if (layout != RUSTY_CUDA_LAYOUT_NK && layout != RUSTY_CUDA_LAYOUT_KN)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_create: unknown layout %d", layout);
+    const size_t n = (size_t)N * K;
+    if (weight->bytes < n)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_create: weight holds %zu bytes, [%u,%u] needs %zu",
+                    weight->bytes, N, K, n);
+    if (qmode == RUSTY_CUDA_QMODE_AFFINE_G64) {
+        if (!biases) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_create: AFFINE_G64 needs biases");
+        // A 64-group must not straddle two rows of the stored matrix.
+        uint32_t inner = layout == RUSTY_CUDA_LAYOUT_NK ? K : N;
+        if (inner % 64 != 0)
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS,
+                        "qlinear_create: AFFINE_G64 needs the contiguous dimension (%u) to be a multiple of 64", inner);
+        size_t gbytes = n / 64 * 4;
+        if (scales->bytes < gbytes || biases->bytes < gbytes)
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_create: scales/biases need %zu bytes each", gbytes);
+    } else if (qmode == RUSTY_CUDA_QMODE_SYM_ROW) {
+        if (biases) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_create: SYM_ROW takes no biases");
+        if (scales->bytes < (size_t)N * 4)
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_create: scales need %zu bytes", (size_t)N * 4);
+    } else {
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_create: unknown qmode %d", qmode);
+    }
+    rusty_cuda_qlinear* q = new (std::nothrow) rusty_cuda_qlinear();
+    if (!q) return fail(ctx, RUSTY_CUDA_ERR_MEMORY_ALLOCATION, "qlinear_create: host allocation failed");
+    q->ctx = ctx;
+    q->weight = weight;
+    q->scales = scales;
+    q->biases = biases;
+    q->N = N;
+    q->K = K;
+    q->layout = layout;
+    q->qmode = qmode;
+    rusty_cuda_buf_retain(weight);
+    rusty_cuda_buf_retain(scales);
+    if (biases) rusty_cuda_buf_retain(biases);
+    *out = q;
+    return RUSTY_CUDA_OK;
+}
+
+int rusty_cuda_qlinear_destroy(rusty_cuda_qlinear* ql) {
+    if (!ql) return RUSTY_CUDA_OK;
+    rusty_cuda_buf_release(ql->weight);
+    rusty_cuda_buf_release(ql->scales);
+    if (ql->biases) rusty_cuda_buf_release(ql->biases);
+    delete ql;
+    return RUSTY_CUDA_OK;
+}
+
+int rusty_cuda_qlinear_forward(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
+                               uint32_t M, rusty_cuda_buf* y, int y_dtype) {
+    RUSTY_REQUIRE_CTX(ctx);
+    if (!ql) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: null qlinear");
+    return qlinear_forward_cols(ctx, ql, x, x_dtype, M, y, y_dtype, ql->N, 0);
+}
+
+int rusty_cuda_qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype, char* dst, size_t dst_len) {
+    if (!ql || !dst || !dst_len) return fail(nullptr, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_plan: null argument");
+    snprintf(dst, dst_len, "%s", qlinear_plan(ql, x_dtype, M, y_dtype));
+    return RUSTY_CUDA_OK;
+}
+
+}  // extern "C"

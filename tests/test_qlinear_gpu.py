@@ -1,0 +1,193 @@
+"""GPU parity of the fused int8 linear against the reference's own
+dequantise-then-matmul composition (the oracle), through the C ABI."""
+import numpy as np
+import pytest
+
+from parity import TOL_BF16, TOL_FP32, assert_bits_equal, rel_err
+from rusty_b200 import BackendError, ComputeEngine, DType, Linear, LoRAAdapter, QLinear, UnifiedTensor
+from rusty_b200 import capi
+from rusty_b200.backend import bf16_bits_to_f32, f32_to_bf16_bits
+from rusty_b200.workloads import affine_g64_from_sym, sym_row_linear
+
+pytestmark = pytest.mark.gpu
+
+
+def _forward(ctx, engine, ql, x, x_dtype=DType.FP32, y_dtype=DType.FP32):
+    M = x.shape[0]
+    xt = UnifiedTensor.from_bf16(ctx, x, list(x.shape)) if x_dtype == DType.BF16 else UnifiedTensor.new(ctx, x, list(x.shape))
+    y = UnifiedTensor.empty_with_dtype(ctx, [M, ql.N], y_dtype)
+    engine.qlinear(ctx, xt, ql, y)
+    return y.to_vec(ctx).reshape(M, ql.N)
+
+
+def _oracle_band(oracle, x, wf, y_ref):
+    """How far the reference arithmetic itself sits from the exact sums."""
+    return rel_err(y_ref, oracle.matmul_bt_f64(x, wf))
+
+
+def test_golden_small_all_modes(ctx, engine, kat):
+    x, q, s = kat["ql_x"], kat["ql_q"], kat["ql_s"]
+    got = _forward(ctx, engine, QLinear.from_host(ctx, q, s), x)
+    assert rel_err(got, kat["ql_y_nk"]) <= TOL_FP32
+    got = _forward(ctx, engine, QLinear.from_host(ctx, np.ascontiguousarray(q.T), s, layout=capi.LAYOUT_KN), x)
+    assert rel_err(got, kat["ql_y_kn"]) <= TOL_FP32
+    x2 = kat["qa_x"]
+    got = _forward(ctx, engine, QLinear.from_host(ctx, kat["qa_u"], kat["qa_s"], kat["qa_b"]), x2)
+    assert rel_err(got, kat["qa_y_nk"]) <= TOL_FP32
+    got = _forward(ctx, engine, QLinear.from_host(ctx, kat["qa_ukn"], kat["qa_s"], kat["qa_b"], layout=capi.LAYOUT_KN), x2)
+    assert rel_err(got, kat["qa_y_kn"]) <= TOL_FP32
+
+
+def test_config1_gemv_sym_row(ctx, engine, oracle):
+    """x f32 [1,4096] . int8 W[4096,4096], per-row scales, seed 0."""
+    x, q, s = sym_row_linear(0, 1, 4096, 4096)
+    ql = QLinear.from_host(ctx, q, s)
+    assert ql.plan(1) == "gemv"
+    got = _forward(ctx, engine, ql, x)
+    wf = oracle.dequantize_rowscale(q, s)
+    ref = oracle.matmul_bt(x, wf)
+    assert rel_err(got, ref) <= TOL_FP32
+    # no farther from the exact sums than the reference's own arithmetic is
+    assert rel_err(got, oracle.matmul_bt_f64(x, wf)) <= max(_oracle_band(oracle, x, wf, ref), 1e-6) * 1.5
+
+
+def test_config1_gemv_affine_native_layout(ctx, engine, oracle):
+    x, q, _ = sym_row_linear(0, 1, 4096, 4096)
+    u, s, b = affine_g64_from_sym(q, 0)
+    got = _forward(ctx, engine, QLinear.from_host(ctx, u, s, b), x)
+    ref = oracle.qlinear_affine(x, u, s, b, u.shape)
+    assert rel_err(got, ref) <= TOL_FP32
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("K,N", [(4096, 11008), (11008, 4096), (1024, 130), (80, 17), (14336, 512)])
+def test_gemv_shapes_sym(ctx, engine, oracle, M, K, N):
+    x, q, s = sym_row_linear(K + N + M, M, K, N)
+    got = _forward(ctx, engine, QLinear.from_host(ctx, q, s), x)
+    ref = oracle.matmul_bt(x, oracle.dequantize_rowscale(q, s), mt=True)
+    assert rel_err(got, ref) <= TOL_FP32
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 1024), (3, 11008, 256), (4, 192, 19)])
+def test_gemv_shapes_affine(ctx, engine, oracle, M, K, N):
+    x, q, _ = sym_row_linear(K + N + M, M, K, N)
+    u, s, b = affine_g64_from_sym(q, K)
+    got = _forward(ctx, engine, QLinear.from_host(ctx, u, s, b), x)
+    ref = oracle.matmul_bt(x, oracle.affine_dequantize(u, s, b, mt=True).reshape(N, K), mt=True)
+    assert rel_err(got, ref) <= TOL_FP32
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (2, 1000, 320), (3, 11008, 4096)])
+def test_gemv_kn_layout(ctx, engine, oracle, M, K, N):
+    """rusty's own Linear orientation: weight stored [in, out]."""
+    x, q, s = sym_row_linear(K * 3 + N, M, K, N)
+    qkn = np.ascontiguousarray(q.T)
+    got = _forward(ctx, engine, QLinear.from_host(ctx, qkn, s, layout=capi.LAYOUT_KN), x)
+    ref = oracle.matmul_bt(x, oracle.dequantize_rowscale(q, s), mt=True)
+    assert rel_err(got, ref) <= TOL_FP32
+    if N % 64 == 0:
+        rng = np.random.default_rng(K)
+        ukn = (qkn.astype(np.int16) + 128).astype(np.uint8)
+        sg = rng.uniform(0.001, 0.02, size=K * N // 64).astype(np.float32)
+        bg = rng.uniform(-1, 1, size=K * N // 64).astype(np.float32)
+        got = _forward(ctx, engine, QLinear.from_host(ctx, ukn, sg, bg, layout=capi.LAYOUT_KN), x)
+        wkn = oracle.affine_dequantize(ukn, sg, bg, mt=True).reshape(K, N)
+        ref = oracle.matmul_bt(x, np.ascontiguousarray(wkn.T), mt=True)
+        assert rel_err(got, ref) <= TOL_FP32
+
+
+def test_bf16_activations_and_outputs(ctx, engine, oracle):
+    """bf16 x is consumed exactly (the oracle sees the rounded values); a bf16 y
+    is the f32 result rounded once."""
+    x, q, s = sym_row_linear(21, 2, 4096, 1024)
+    xb = bf16_bits_to_f32(f32_to_bf16_bits(x))
+    ql = QLinear.from_host(ctx, q, s)
+    ref = oracle.matmul_bt(xb, oracle.dequantize_rowscale(q, s), mt=True)
+    got = _forward(ctx, engine, ql, x, x_dtype=DType.BF16)
+    assert rel_err(got, ref) <= TOL_FP32
+    got16 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.BF16)
+    assert rel_err(got16, ref) <= TOL_BF16
+    assert np.array_equal(f32_to_bf16_bits(got16), f32_to_bf16_bits(got))  # exactly one rounding of the f32 result
+
+
+def test_weight_values_cover_all_256_bytes(ctx, engine, oracle):
+    """Every int8 value (including -128) and every u8 value dequantises exactly:
+    with x = one-hot rows the output IS the dequantised weight."""
+    K, N = 256, 64
+    q = np.tile(np.arange(-128, 128, dtype=np.int8), (N, 1))
+    q = np.roll(q, 3, axis=1)
+    s = np.ones(N, np.float32)
+    for k0 in (0, 3, 131, 255):
+        x = np.zeros((1, K), np.float32)
+        x[0, k0] = 1.0
+        got = _forward(ctx, engine, QLinear.from_host(ctx, q, s), x)
+        assert np.array_equal(got[0], q[:, k0].astype(np.float32))
+    u = (q.astype(np.int16) + 128).astype(np.uint8)
+    sg = np.ones(N * K // 64, np.float32)
+    bg = np.zeros(N * K // 64, np.float32)
+    x = np.zeros((1, K), np.float32)
+    x[0, 7] = 1.0
+    got = _forward(ctx, engine, QLinear.from_host(ctx, u, sg, bg), x)
+    assert np.array_equal(got[0], u[:, 7].astype(np.float32))
+
+
+def test_linearity_and_row_independence(ctx, engine):
+    """Size-independent properties at a full-size shape: f(a+b) = f(a)+f(b) within
+    rounding, and each activation row's result does not depend on its neighbours."""
+    x, q, s = sym_row_linear(33, 4, 4096, 14336)
+    ql = QLinear.from_host(ctx, q, s)
+    y = _forward(ctx, engine, ql, x)
+    y0 = _forward(ctx, engine, ql, x[:1])
+    assert_bits_equal(y[:1], y0)
+    ysum = _forward(ctx, engine, ql, (x[0:1] + x[1:2]))
+    assert rel_err(ysum, y[0:1] + y[1:2]) <= TOL_FP32
+
+
+def test_linear_api_quantized_and_lora(ctx, engine, oracle):
+    """Linear.forward keeps the reference contract: x . W[in,out] (+ (x.A).B)."""
+    rng = np.random.default_rng(5)
+    K, N, M = 256, 192, 3
+    w = rng.standard_normal((K, N)).astype(np.float32)
+    x = rng.standard_normal((2, M, K)).astype(np.float32)            # leading dims are flattened
+    lin = Linear.new(ctx, UnifiedTensor.new(ctx, w, [K, N]))
+    xt = UnifiedTensor.new(ctx, x, list(x.shape))
+    y = lin.forward(engine, xt)
+    assert y.shape == [2, M, N]
+    ref = oracle.matmul_tiled(x.reshape(-1, K), w)
+    assert rel_err(y.to_vec(ctx).reshape(-1, N), ref) <= TOL_FP32
+    # LoRA branch: A = 0.01, B = 0 at construction (no change), then a non-zero B
+    lora = LoRAAdapter(ctx, K, N, rank=4, alpha=16.0)
+    y2 = Linear.with_lora(ctx, lin.weight, lora).forward(engine, xt)
+    assert_bits_equal(y2.to_vec(ctx), y.to_vec(ctx))
+    bmat = rng.standard_normal((4, N)).astype(np.float32)
+    lora.b.write_data(ctx, bmat)
+    y3 = Linear.with_lora(ctx, lin.weight, lora).forward(engine, xt)
+    a = np.full((K, 4), 0.01, np.float32)
+    ref3 = ref + oracle.matmul_tiled(oracle.matmul_tiled(x.reshape(-1, K), a), bmat)
+    assert rel_err(y3.to_vec(ctx).reshape(-1, N), ref3) <= TOL_FP32
+    # the same Linear over a quantised weight
+    _, q, s = sym_row_linear(9, 1, K, N)
+    qlin = Linear.from_quantized(ctx, QLinear.from_host(ctx, q, s))
+    yq = qlin.forward(engine, xt)
+    refq = oracle.matmul_bt(x.reshape(-1, K), oracle.dequantize_rowscale(q, s))
+    assert yq.shape == [2, M, N] and rel_err(yq.to_vec(ctx).reshape(-1, N), refq) <= TOL_FP32
+
+
+def test_empty_and_invalid(ctx, engine):
+    _, q, s = sym_row_linear(1, 1, 64, 16)
+    ql = QLinear.from_host(ctx, q, s)
+    x0 = UnifiedTensor.empty(ctx, [0, 64])
+    y0 = UnifiedTensor.empty(ctx, [0, 16])
+    engine.qlinear(ctx, x0, ql, y0)  # M = 0: nothing to do, no error
+    x = UnifiedTensor.new(ctx, np.zeros((2, 64), np.float32), [2, 64])
+    with pytest.raises(BackendError) as e:
+        engine.qlinear(ctx, x, ql, UnifiedTensor.empty(ctx, [1, 16]))
+    assert e.value.kind == "InvalidDimensions"
+    with pytest.raises(BackendError) as e:
+        QLinear.from_host(ctx, np.zeros((16, 72), np.uint8), np.zeros(18, np.float32), np.zeros(18, np.float32))
+    assert e.value.kind == "InvalidDimensions"   # a 64-group would straddle rows
+    with pytest.raises(BackendError) as e:
+        xi = UnifiedTensor.from_bytes_with_dtype(ctx, np.zeros(128, np.uint8), [2, 64], DType.I8)
+        engine.qlinear(ctx, xi, ql, UnifiedTensor.empty(ctx, [2, 16]))
+    assert e.value.kind == "InvalidDataType"
+    ctx.sync()
