@@ -1,0 +1,355 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantised-linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one pass of the Llama-shaped stack of int8 Linears (every q/k/v/o,
+gate/up/down and the LM head once) over one batch of synthetic activations.
+Prints ONE JSON line (rank 0).  Metric: decode tokens/s; the same line carries
+the dominant kernel's HBM roofline, the single-Linear GEMV GB/s and prefill GEMM
+TFLOP/s figures, an end-to-end number with host<->device copies in the timed
+region, the sampled clocks and a CPU baseline.
+
+Under torchrun (N > 1) every Linear is sharded by output features across the
+ranks and its output all-gathered; total work is fixed ("strong" scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (stack, batch rows M, description)
+    "llama3-8b-decode32": ("llama3-8b", 32, "Llama-3-8B-shaped GQA linear stack, random int8 weights, batch-32 decode"),
+    "llama7b-decode1": ("llama7b", 1, "Llama-7B-shaped linear stack, random int8 weights, batch-1 decode"),
+    "llama2-70b-decode64": ("llama2-70b", 64, "Llama-2-70B-shaped linear stack, random int8 weights, batch-64 decode"),
+}
+DEFAULT_WORKLOAD = "llama3-8b-decode32"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.f = None
+        self.p = None
+
+    def start(self):
+        try:
+            self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                       "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.p is None:
+            return out
+        try:
+            self.p.terminate()
+            self.p.wait(timeout=5)
+        except Exception:
+            pass
+        try:
+            self.f.flush()
+            rows = [r.strip().split(", ") for r in open(self.f.name) if r.strip()]
+            os.unlink(self.f.name)
+        except Exception:
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[5:9]):
+                if v.strip().lower() == "active":
+                    reasons.add(nm)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the oracle's threaded restatement of the reference arithmetic.
+# ----------------------------------------------------------------------------
+class CpuSample:
+    """ONE layer (q,k,v,o,gate,up,down at batch M) of the stack on the host cores.
+    two_step = the reference's own per-forward work: an f32 matmul over weights
+    dequantised beforehand (untimed, as at its load time); fused = int8 read +
+    dequant inside the dot product."""
+
+    def __init__(self, stack_name: str, M: int):
+        from oracle import oracle as O
+        from rusty_b200.workloads import STACKS
+        self.O = O
+        self.M = M
+        shape = STACKS[stack_name]
+        rng = np.random.default_rng(0)
+        self.per_layer = shape.per_layer()
+        self.ws = {}
+        for _p, n, k in self.per_layer:
+            if (n, k) not in self.ws:
+                q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+                s = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+                self.ws[(n, k)] = (q, s, O.dequantize_rowscale(q, s))
+        self.xs = {k: rng.standard_normal((M, k), dtype=np.float32) for _p, _n, k in self.per_layer}
+        self.sample_weights = sum(n * k for _p, n, k in self.per_layer)
+        self.total_weights = shape.weight_bytes()
+        self.threads = O.num_threads()
+
+    def two_step(self) -> float:
+        t0 = time.perf_counter()
+        for _p, n, k in self.per_layer:
+            self.O.time_matmul_bt_mt(self.xs[k], self.ws[(n, k)][2], simd=True)
+        return time.perf_counter() - t0
+
+    def fused(self) -> float:
+        t0 = time.perf_counter()
+        for _p, n, k in self.per_layer:
+            self.O.qlinear_rowscale_fused_mt(self.xs[k], self.ws[(n, k)][0], self.ws[(n, k)][1], simd=True)
+        return time.perf_counter() - t0
+
+    def tokens_per_s(self, seconds_per_sample: float) -> float:
+        return self.M / (seconds_per_sample * self.total_weights / self.sample_weights)
+
+    def describe(self) -> str:
+        return ("one layer (q,k,v,o,gate,up,down) at batch %d per step, scaled to the whole stack by weight bytes "
+                "(%d / %d); f32 matmul over pre-dequantised weights = the reference's per-forward work"
+                % (self.M, self.total_weights, self.sample_weights))
+
+
+def run_reference(args, rank: int):
+    """--impl reference: the reference's own arithmetic for the path on the host
+    cores (the oracle port; the Rust + WGSL original cannot be built or run on a
+    box without a Rust toolchain and a graphics stack)."""
+    if rank != 0:
+        return
+    stack_name, M, desc = WORKLOADS[args.workload]
+    cs = CpuSample(stack_name, M)
+    for _ in range(args.warmup):
+        cs.two_step()
+    times = [cs.two_step() for _ in range(args.steps)]
+    t_sample = sum(times) / len(times)
+    val = cs.tokens_per_s(t_sample)
+    step_s = M / val
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "desc": desc, "batch_rows": M},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cs.threads, "kind": "port", "sample": cs.describe()},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------
+# single-Linear figures (rank 0, N = 1): GEMV GB/s and GEMM TFLOP/s
+# ----------------------------------------------------------------------------
+def bench_single_linear(ctx, eng, M, K, N, x_dtype, y_dtype, iters, warm, l2_bytes=126 * 2**20):
+    """Average device time per launch over `iters` launches that rotate through
+    enough distinct weight copies to exceed L2 (so every launch streams HBM)."""
+    from rusty_b200 import QLinear, UnifiedTensor
+    from rusty_b200.backend import Event
+    from rusty_b200.workloads import sym_row_linear
+    x, q, s = sym_row_linear(0, M, K, N)
+    copies = max(2, int(np.ceil(1.5 * l2_bytes / (N * K))) + 1)
+    qls = [QLinear.from_host(ctx, q, s) for _ in range(copies)]
+    from rusty_b200 import DType
+    xt = UnifiedTensor.from_bf16(ctx, x, [M, K]) if x_dtype == DType.BF16 else UnifiedTensor.new(ctx, x, [M, K])
+    y = UnifiedTensor.empty_with_dtype(ctx, [M, N], y_dtype)
+    for i in range(warm):
+        eng.qlinear(ctx, xt, qls[i % copies], y)
+    ctx.sync()
+    e0, e1 = Event(ctx), Event(ctx)
+    e0.record()
+    for i in range(iters):
+        eng.qlinear(ctx, xt, qls[i % copies], y)
+    e1.record()
+    ms = e0.elapsed_ms(e1) / iters
+    plan = qls[0].plan(M, x_dtype, y_dtype)
+    alg_bytes = N * K + N * 4 + M * K * x_dtype.size_bytes() + M * N * y_dtype.size_bytes()
+    del qls
+    return {"M": M, "K": K, "N": N, "kernel": plan, "us_per_launch": ms * 1e3, "algorithmic_bytes": alg_bytes,
+            "gbs": alg_bytes / (ms * 1e-3) / 1e9, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "weight_copies": copies}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers (for profiling captures only)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-Linear and CPU legs")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.layers is None:
+        args.warmup = 3
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    stack_name, M, desc = WORKLOADS[args.workload]
+    peaks = load_peaks()
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    import rusty_b200
+    from rusty_b200 import DType
+    from rusty_b200.backend import Event, PinnedArray, download_async, upload_async
+    from rusty_b200.stack import LinearStack
+    from rusty_b200.workloads import STACKS
+
+    ctx = rusty_b200.CudaContext(local_rank)
+    eng = rusty_b200.ComputeEngine(ctx)
+    shape = STACKS[stack_name]
+    stack = LinearStack(ctx, shape, M, DType.FP32, DType.FP32, seed=0, rank=rank, world=world, layers=args.layers)
+    if world > 1:
+        from rusty_b200.shard import ShardedStack
+        runner = ShardedStack(stack, dist)
+    else:
+        runner = stack
+    runner.capture()
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(v: float) -> float:
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-timed region: inputs resident in HBM ----
+    for _ in range(args.warmup):
+        runner.replay()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = ctx.launch_count()
+    e0, e1 = Event(ctx), Event(ctx)
+    e0.record()
+    for _ in range(args.steps):
+        runner.replay()
+    e1.record()
+    ms_total = e0.elapsed_ms(e1)
+    barrier()
+    launches = ctx.launch_count() - l0
+    ms_step = max_over_ranks(ms_total / args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end-to-end: host activations in, host logits out, every step ----
+    d_in = shape.d
+    x_host = PinnedArray((M, d_in), np.float32)
+    x_host.array[...] = stack.host_inputs[d_in]
+    logits_t = runner.full_logits() if world > 1 else stack.logits
+    y_host = PinnedArray((M, logits_t.shape[1]), np.float32)
+    for _ in range(2):
+        upload_async(ctx, stack.inputs[d_in], x_host)
+        runner.replay()
+        download_async(ctx, logits_t, y_host)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        upload_async(ctx, stack.inputs[d_in], x_host)
+        runner.replay()
+        download_async(ctx, logits_t, y_host)
+        ctx.sync()
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / args.steps)
+    barrier()
+    finite = bool(np.isfinite(y_host.array).all())
+
+    value = M / (ms_step * 1e-3)
+    alg_bytes = stack.algorithmic_bytes()
+    achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    line = {
+        "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "desc": desc, "batch_rows": M, "linears_per_step": stack.num_linears(),
+                   "weights": "int8 [out,in], f32 scale per output row", "activations": "f32 in, f32 out, fp32 accumulate",
+                   "parallelism": "1 GPU" if world == 1 else f"output-feature shards x{world} + all-gather",
+                   "l2": "inputs larger than L2: each step streams %.2f GB of weights per GPU" % (stack.weight_bytes() / 1e9),
+                   "kernels": runner.plans(), "layers": stack.layers},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "algorithmic_bytes_per_step_per_gpu": alg_bytes,
+                     "note": "whole step (all launches of the fused linear kernel) / device time, per GPU"},
+        "e2e": {"value": M / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": x_host.nbytes,
+                "d2h_bytes_per_step": y_host.nbytes, "ms_per_step": e2e_s * 1e3, "logits_finite": finite},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        # single-Linear figures of the metric: GEMV GB/s, prefill GEMM TFLOP/s
+        g1 = bench_single_linear(ctx, eng, 1, 4096, 4096, DType.FP32, DType.FP32, 200, 20)
+        g2 = bench_single_linear(ctx, eng, 1, 4096, 11008, DType.BF16, DType.BF16, 200, 20)
+        g1["frac_of_hbm_peak"] = g1["gbs"] / peaks["hbm_gbs"]
+        g2["frac_of_hbm_peak"] = g2["gbs"] / peaks["hbm_gbs"]
+        mm = bench_single_linear(ctx, eng, 512, 4096, 11008, DType.BF16, DType.BF16, 30, 5)
+        mm["frac_of_bf16_peak"] = mm["tflops"] / peaks["bf16_tflops"]
+        line["gemv"] = {"config0_f32_1x4096x4096": g1, "config1_bf16_1x4096x11008": g2}
+        line["gemm"] = {"config1_bf16_512x4096x11008": mm, "peak_tflops": peaks["bf16_tflops"]}
+        cs = CpuSample(stack_name, M)
+        cs.two_step()
+        t2 = min(cs.two_step() for _ in range(3))
+        tf = min(cs.fused() for _ in range(3))
+        line["cpu_baseline"] = {"value": cs.tokens_per_s(t2), "unit": "tokens/s", "cores": cs.threads, "kind": "port",
+                                "fused_int8_value": cs.tokens_per_s(tf), "sample": cs.describe()}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    x_host.free()
+    y_host.free()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

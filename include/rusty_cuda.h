@@ -196,6 +196,39 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward(rusty_cuda_ctx* ctx, const rusty_c
 RUSTY_CUDA_API int rusty_cuda_qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype,
                                            char* dst, size_t dst_len);
 
+/* The loop of Linear::forward calls a model forward makes
+ * (rusty-graph/src/lib.rs:199-201, :270, :318-322, :435) in one host call:
+ * forward i uses qls[i], xs[i], ys[i]; all share M and the dtypes.  Same
+ * kernels, same order, as n separate rusty_cuda_qlinear_forward calls. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t n,
+                                                    const rusty_cuda_qlinear* const* qls,
+                                                    const rusty_cuda_buf* const* xs, int x_dtype, uint32_t M,
+                                                    rusty_cuda_buf* const* ys, int y_dtype);
+
+/* ---- stream capture and timing ---------------------------------------------
+ * rusty submits one command buffer per op (lib.rs:4452); a decode step here is
+ * hundreds of short kernels, so the sequence can be recorded once into a CUDA
+ * graph and replayed with one launch.  Between begin and end, operator calls
+ * on this context are captured instead of executed; uploads, downloads and
+ * sync are not allowed. */
+RUSTY_CUDA_API int rusty_cuda_graph_begin(rusty_cuda_ctx* ctx);
+RUSTY_CUDA_API int rusty_cuda_graph_end(rusty_cuda_ctx* ctx, rusty_cuda_graph** out);
+RUSTY_CUDA_API int rusty_cuda_graph_launch(rusty_cuda_ctx* ctx, rusty_cuda_graph* graph);
+RUSTY_CUDA_API int rusty_cuda_graph_destroy(rusty_cuda_graph* graph);
+/* Device timestamps on the context's stream (the reference's benchmarks use
+ * host wall-clock around submit + poll, benchmarks/src/main.rs:99-106). */
+typedef struct rusty_cuda_event rusty_cuda_event;
+RUSTY_CUDA_API int rusty_cuda_event_create(rusty_cuda_ctx* ctx, rusty_cuda_event** out);
+RUSTY_CUDA_API int rusty_cuda_event_record(rusty_cuda_ctx* ctx, rusty_cuda_event* ev);
+/* Waits for `stop`, then returns the device time from `start` to `stop`. */
+RUSTY_CUDA_API int rusty_cuda_event_elapsed_ms(rusty_cuda_ctx* ctx, rusty_cuda_event* start, rusty_cuda_event* stop,
+                                               float* ms);
+RUSTY_CUDA_API int rusty_cuda_event_destroy(rusty_cuda_event* ev);
+/* Overwrite `bytes` bytes at `offset` with `value` (cudaMemsetAsync); used by
+ * harnesses to flush L2 between timed iterations and to clear outputs. */
+RUSTY_CUDA_API int rusty_cuda_buf_fill_u8(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf, size_t offset, int value,
+                                          size_t bytes);
+
 #ifdef __cplusplus
 }
 #endif

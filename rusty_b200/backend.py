@@ -282,3 +282,101 @@ class ComputeEngine:
         m = int(np.prod(x.shape[:-1], dtype=np.int64))
         check(lib().rusty_cuda_qlinear_forward(ctx.handle, w._h, x.buffer(), int(x.dtype), m, out.buffer(),
                                                int(out.dtype)), ctx.handle)
+
+
+class Event:
+    """Device timestamp on the context's stream."""
+
+    def __init__(self, ctx: CudaContext):
+        h = C.c_void_p()
+        check(lib().rusty_cuda_event_create(ctx.handle, C.byref(h)), ctx.handle)
+        self._h, self.ctx = h, ctx
+
+    def record(self) -> None:
+        check(lib().rusty_cuda_event_record(self.ctx.handle, self._h), self.ctx.handle)
+
+    def elapsed_ms(self, stop: "Event") -> float:
+        ms = C.c_float()
+        check(lib().rusty_cuda_event_elapsed_ms(self.ctx.handle, self._h, stop._h, C.byref(ms)), self.ctx.handle)
+        return float(ms.value)
+
+    def __del__(self):
+        try:
+            if self._h is not None and self.ctx._h is not None:
+                lib().rusty_cuda_event_destroy(self._h)
+        except Exception:
+            pass
+        self._h = None
+
+
+class Graph:
+    """A recorded sequence of operator calls, replayed with one launch."""
+
+    def __init__(self, ctx: CudaContext):
+        self.ctx = ctx
+        self._h = None
+
+    def __enter__(self) -> "Graph":
+        check(lib().rusty_cuda_graph_begin(self.ctx.handle), self.ctx.handle)
+        return self
+
+    def __exit__(self, et, ev, tb) -> bool:
+        h = C.c_void_p()
+        rc = lib().rusty_cuda_graph_end(self.ctx.handle, C.byref(h))
+        if et is None:
+            check(rc, self.ctx.handle)
+            self._h = h
+        return False
+
+    def launch(self) -> None:
+        check(lib().rusty_cuda_graph_launch(self.ctx.handle, self._h), self.ctx.handle)
+
+    def __del__(self):
+        try:
+            if self._h is not None and self.ctx._h is not None:
+                lib().rusty_cuda_graph_destroy(self._h)
+        except Exception:
+            pass
+        self._h = None
+
+
+class PinnedArray:
+    """Page-locked host memory viewed as a numpy array (for asynchronous copies)."""
+
+    def __init__(self, shape, dtype):
+        self.nbytes = int(np.prod(shape, dtype=np.int64)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        check(lib().rusty_cuda_host_alloc(self.nbytes, C.byref(p)))
+        self._p = p
+        buf = (C.c_uint8 * max(self.nbytes, 1)).from_address(p.value)
+        self.array = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape, dtype=np.int64))).reshape(shape)
+
+    def ptr(self) -> C.c_void_p:
+        return self._p
+
+    def free(self) -> None:
+        if self._p is not None:
+            self.array = None
+            lib().rusty_cuda_host_free(self._p)
+            self._p = None
+
+
+def upload_async(ctx: CudaContext, dst: UnifiedTensor, src: PinnedArray, offset: int = 0) -> None:
+    check(lib().rusty_cuda_buf_upload_async(ctx.handle, dst.buffer(), offset, src.ptr(), src.nbytes), ctx.handle)
+
+
+def download_async(ctx: CudaContext, src: UnifiedTensor, dst: PinnedArray, offset: int = 0) -> None:
+    check(lib().rusty_cuda_buf_download_async(ctx.handle, src.buffer(), offset, dst.ptr(), dst.nbytes), ctx.handle)
+
+
+def fill_u8(ctx: CudaContext, t: UnifiedTensor, value: int = 0) -> None:
+    check(lib().rusty_cuda_buf_fill_u8(ctx.handle, t.buffer(), 0, value, t.size_in_bytes()), ctx.handle)
+
+
+def qlinear_forward_batch(ctx: CudaContext, qls, xs, ys, M: int, x_dtype: DType, y_dtype: DType) -> None:
+    """One host call for a sequence of fused linears (a model forward's Linear loop)."""
+    n = len(qls)
+    arr = C.c_void_p * n
+    check(lib().rusty_cuda_qlinear_forward_batch(
+        ctx.handle, n, arr(*[q._h for q in qls]), arr(*[x.buffer() for x in xs]), int(x_dtype), M,
+        arr(*[y.buffer() for y in ys]), int(y_dtype)), ctx.handle)

@@ -74,6 +74,16 @@ SIGNATURES = {
     "rusty_cuda_qlinear_create": ([_vp, _vp, _vp, _vp, _u32, _u32, _int, _int, _vpp], _int),
     "rusty_cuda_qlinear_destroy": ([_vp], _int),
     "rusty_cuda_qlinear_forward": ([_vp, _vp, _vp, _int, _u32, _vp, _int], _int),
+    "rusty_cuda_qlinear_forward_batch": ([_vp, _sz, _vpp, _vpp, _int, _u32, _vpp, _int], _int),
+    "rusty_cuda_graph_begin": ([_vp], _int),
+    "rusty_cuda_graph_end": ([_vp, _vpp], _int),
+    "rusty_cuda_graph_launch": ([_vp, _vp], _int),
+    "rusty_cuda_graph_destroy": ([_vp], _int),
+    "rusty_cuda_event_create": ([_vp, _vpp], _int),
+    "rusty_cuda_event_record": ([_vp, _vp], _int),
+    "rusty_cuda_event_elapsed_ms": ([_vp, _vp, _vp, C.POINTER(C.c_float)], _int),
+    "rusty_cuda_event_destroy": ([_vp], _int),
+    "rusty_cuda_buf_fill_u8": ([_vp, _vp, _sz, _int, _sz], _int),
     "rusty_cuda_qlinear_plan": ([_vp, _int, _u32, _int, C.c_char_p, _sz], _int),
 }
 

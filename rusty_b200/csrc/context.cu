@@ -144,8 +144,15 @@ const char* rusty_cuda_last_error(rusty_cuda_ctx* ctx) {
     return t_scratch.c_str();
 }
 
+#define RUSTY_NOT_CAPTURING(ctx, what)                                                                        \
+    do {                                                                                                      \
+        if ((ctx)->capturing)                                                                                 \
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, what ": not allowed while a graph capture is open"); \
+    } while (0)
+
 int rusty_cuda_sync(rusty_cuda_ctx* ctx) {
     RUSTY_REQUIRE_CTX(ctx);
+    RUSTY_NOT_CAPTURING(ctx, "sync");
     DeviceGuard g(ctx->device);
     int rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
     if (rc) return rc;
@@ -264,6 +271,7 @@ static int range_check(rusty_cuda_ctx* ctx, const char* what, const rusty_cuda_b
 int rusty_cuda_buf_upload_async(rusty_cuda_ctx* ctx, rusty_cuda_buf* dst, size_t dst_offset, const void* src,
                                 size_t bytes) {
     RUSTY_REQUIRE_CTX(ctx);
+    RUSTY_NOT_CAPTURING(ctx, "buf_upload");
     int rc = range_check(ctx, "buf_upload", dst, dst_offset, bytes);
     if (rc) return rc;
     if (bytes == 0) return RUSTY_CUDA_OK;
@@ -288,6 +296,7 @@ int rusty_cuda_buf_upload(rusty_cuda_ctx* ctx, rusty_cuda_buf* dst, size_t dst_o
 int rusty_cuda_buf_download_async(rusty_cuda_ctx* ctx, const rusty_cuda_buf* src, size_t src_offset, void* dst,
                                   size_t bytes) {
     RUSTY_REQUIRE_CTX(ctx);
+    RUSTY_NOT_CAPTURING(ctx, "buf_download");
     int rc = range_check(ctx, "buf_download", src, src_offset, bytes);
     if (rc) return rc;
     if (bytes == 0) return RUSTY_CUDA_OK;

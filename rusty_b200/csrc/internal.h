@@ -39,6 +39,9 @@ struct rusty_cuda_ctx {
     // device-visible status word (pinned + mapped)
     rusty_cuda_dev_status* status_host = nullptr;
     rusty_cuda_dev_status* status_dev = nullptr;
+    // stream capture in progress (rusty_cuda_graph_begin .. _end)
+    bool capturing = false;
+    uint64_t launches_at_capture = 0;
 };
 
 struct rusty_cuda_buf {
@@ -48,6 +51,18 @@ struct rusty_cuda_buf {
     bool pooled = false;
     bool borrowed = false;  // storage owned by someone else (IPC import / wrap)
     std::atomic<int> refs{1};
+};
+
+struct rusty_cuda_graph {
+    rusty_cuda_ctx* ctx = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;  // kernel launches recorded in the graph
+};
+
+struct rusty_cuda_event {
+    rusty_cuda_ctx* ctx = nullptr;
+    cudaEvent_t ev = nullptr;
 };
 
 struct rusty_cuda_qlinear {

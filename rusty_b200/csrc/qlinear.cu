@@ -141,6 +141,19 @@ int rusty_cuda_qlinear_forward(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql
     return qlinear_forward_cols(ctx, ql, x, x_dtype, M, y, y_dtype, ql->N, 0);
 }
 
+int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t n, const rusty_cuda_qlinear* const* qls,
+                                     const rusty_cuda_buf* const* xs, int x_dtype, uint32_t M, rusty_cuda_buf* const* ys,
+                                     int y_dtype) {
+    RUSTY_REQUIRE_CTX(ctx);
+    if (n && (!qls || !xs || !ys)) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_batch: null array");
+    for (size_t i = 0; i < n; ++i) {
+        if (!qls[i]) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_batch: entry %zu is null", i);
+        int rc = qlinear_forward_cols(ctx, qls[i], xs[i], x_dtype, M, ys[i], y_dtype, qls[i]->N, 0);
+        if (rc) return rc;
+    }
+    return RUSTY_CUDA_OK;
+}
+
 int rusty_cuda_qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype, char* dst, size_t dst_len) {
     if (!ql || !dst || !dst_len) return fail(nullptr, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_plan: null argument");
     snprintf(dst, dst_len, "%s", qlinear_plan(ql, x_dtype, M, y_dtype));

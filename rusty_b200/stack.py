@@ -1,0 +1,117 @@
+"""The Llama-shaped stack of quantised Linears a decode / prefill step runs.
+
+Mirrors the order in which rusty-graph calls Linear::forward during
+LlamaModel::forward (rusty-graph/src/lib.rs:420-436): per layer q, k, v, o
+(Attention::forward :199-201, :270) then gate, up, down (MLP::forward :318-322),
+and lm_head after the last layer (:435).  Only the Linears are run: rope,
+attention, SiLU, RMSNorm and the residual adds between them are other
+components.  Every Linear therefore reads a fixed, normalised activation buffer
+of its input width ([M, d], [M, q] or [M, ffn]) and writes its own output
+buffer, so values stay finite over 32-80 layers of random weights; the bytes
+moved and the kernels launched are those of the real chain.
+
+Weights: random int8 in [-127,127] with per-output-row f32 scales in
+U(0.001,0.02) (QMODE_SYM_ROW, [out,in] storage).  One host array per distinct
+(N,K) shape is drawn and uploaded into a separate device buffer per layer, so a
+step streams every layer's weights from HBM.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+
+from . import capi
+from .backend import (ComputeEngine, CudaContext, DType, Graph, QLinear, UnifiedTensor, qlinear_forward_batch)
+from .workloads import StackShape
+
+
+class LinearStack:
+    def __init__(self, ctx: CudaContext, shape: StackShape, M: int, x_dtype: DType = DType.FP32,
+                 y_dtype: DType = DType.FP32, seed: int = 0, rank: int = 0, world: int = 1,
+                 layers: Optional[int] = None):
+        self.ctx, self.shape, self.M = ctx, shape, M
+        self.x_dtype, self.y_dtype = x_dtype, y_dtype
+        self.rank, self.world = rank, world
+        self.layers = shape.layers if layers is None else layers
+        rng = np.random.default_rng(seed)
+        host_w: Dict[Tuple[int, int], Tuple[np.ndarray, np.ndarray]] = {}
+        self.qls: List[QLinear] = []
+        self.names: List[str] = []
+        self.dims: List[Tuple[int, int]] = []   # (N_local, K)
+        self.full_n: List[int] = []
+
+        def draw(n: int, k: int):
+            if (n, k) not in host_w:
+                q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+                s = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+                host_w[(n, k)] = (q, s)
+            return host_w[(n, k)]
+
+        linears = []
+        for l in range(self.layers):
+            linears += [(f"l{l}.{p}", n, k) for p, n, k in shape.per_layer()]
+        linears.append(("lm_head", shape.vocab, shape.d))
+        for name, n, k in linears:
+            assert n % world == 0, f"{name}: N={n} not divisible by {world} ranks"
+            nl = n // world
+            q, s = draw(n, k)
+            lo = rank * nl
+            self.qls.append(QLinear.from_host(ctx, q[lo:lo + nl], s[lo:lo + nl]))
+            self.names.append(name)
+            self.dims.append((nl, k))
+            self.full_n.append(n)
+        # activations: one fixed input per distinct K, N(0,1) like the benchmark's x
+        self.inputs: Dict[int, UnifiedTensor] = {}
+        self.host_inputs: Dict[int, np.ndarray] = {}
+        for k in sorted({k for _, k in self.dims}):
+            xh = rng.standard_normal((M, k), dtype=np.float32)
+            self.host_inputs[k] = xh
+            self.inputs[k] = (UnifiedTensor.from_bf16(ctx, xh, [M, k]) if x_dtype == DType.BF16
+                              else UnifiedTensor.new(ctx, xh, [M, k]))
+        # outputs: one buffer per distinct local N (reused across layers), logits separate
+        self.outputs: Dict[int, UnifiedTensor] = {}
+        for (nl, _k), name in zip(self.dims, self.names):
+            key = -1 if name == "lm_head" else nl
+            if key not in self.outputs:
+                self.outputs[key] = UnifiedTensor.empty_with_dtype(ctx, [M, nl], y_dtype)
+        self.logits = self.outputs[-1]
+        self._xs = [self.inputs[k] for _, k in self.dims]
+        self._ys = [self.outputs[-1 if nm == "lm_head" else nl] for (nl, _), nm in zip(self.dims, self.names)]
+        self.graph: Optional[Graph] = None
+
+    # ---- accounting (algorithmic bytes / flops of ONE step on this rank) ----
+    def weight_bytes(self) -> int:
+        return sum(n * k for n, k in self.dims)
+
+    def algorithmic_bytes(self) -> int:
+        xs, ys = self.x_dtype.size_bytes(), self.y_dtype.size_bytes()
+        return sum(n * k + n * 4 + self.M * k * xs + self.M * n * ys for n, k in self.dims)
+
+    def flops(self) -> int:
+        return sum(2 * self.M * n * k for n, k in self.dims)
+
+    def num_linears(self) -> int:
+        return len(self.qls)
+
+    # ---- execution ----
+    def step(self) -> None:
+        """Enqueue every Linear of the stack once (one host call)."""
+        qlinear_forward_batch(self.ctx, self.qls, self._xs, self._ys, self.M, self.x_dtype, self.y_dtype)
+
+    def capture(self) -> Graph:
+        g = Graph(self.ctx)
+        with g:
+            self.step()
+        self.graph = g
+        return g
+
+    def replay(self) -> None:
+        self.graph.launch()
+
+    def plans(self) -> Dict[str, int]:
+        out: Dict[str, int] = {}
+        for q in self.qls:
+            p = q.plan(self.M, self.x_dtype, self.y_dtype)
+            out[p] = out.get(p, 0) + 1
+        return out
