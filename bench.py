@@ -188,13 +188,19 @@ def bench_single_linear(ctx, eng, M, K, N, x_dtype, y_dtype, iters, warm, l2_byt
     from rusty_b200 import DType
     xt = UnifiedTensor.from_bf16(ctx, x, [M, K]) if x_dtype == DType.BF16 else UnifiedTensor.new(ctx, x, [M, K])
     y = UnifiedTensor.empty_with_dtype(ctx, [M, N], y_dtype)
+    from rusty_b200.backend import Graph
     for i in range(warm):
         eng.qlinear(ctx, xt, qls[i % copies], y)
     ctx.sync()
+    g = Graph(ctx)          # the launches are replayed from a graph so host call overhead is not what is timed
+    with g:
+        for i in range(iters):
+            eng.qlinear(ctx, xt, qls[i % copies], y)
+    g.launch()
+    ctx.sync()
     e0, e1 = Event(ctx), Event(ctx)
     e0.record()
-    for i in range(iters):
-        eng.qlinear(ctx, xt, qls[i % copies], y)
+    g.launch()
     e1.record()
     ms = e0.elapsed_ms(e1) / iters
     plan = qls[0].plan(M, x_dtype, y_dtype)

@@ -124,6 +124,7 @@ int rusty_cuda_ctx_destroy(rusty_cuda_ctx* ctx) {
     DeviceGuard g(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     rusty_cuda_pool_clear(ctx);
+    tc_workspace_release(ctx);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     cudaStreamDestroy(ctx->stream);
     delete ctx;

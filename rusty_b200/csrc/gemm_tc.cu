@@ -1,7 +1,671 @@
-// placeholder until the tcgen05 kernel lands
+// Fused int8-weight linear on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Replaces the reference's "dequantise once at load, f32 tiled matmul per
+// forward" (rusty-loader/src/lib.rs:155-218, rusty-backend/src/kernels.wgsl:16-54,
+// :234-242) for batches of activation rows: y[M,N] = x[M,K] . (q[N,K] * scale[N])^T.
+//
+// Arithmetic.  The weights stay int8 all the way into the tensor core
+// (tcgen05.mma kind::i8, int32 accumulation in tensor memory); nothing is
+// dequantised in the main loop.  The activations are decomposed EXACTLY into
+// D signed 7-bit digits relative to one power-of-two scale per row,
+//     x[m,k] * s_m = d0 + d1/128 + d2/128^2 (+ d3/128^3),  |d0| <= 127, |d1..| <= 64,
+// by a small pre-pass; each digit plane is one column block of the B operand.
+// The integer dot products are exact, the digit planes are recombined in
+// double precision and multiplied by 1/s_m and scale[n] once, so the result is
+// the correctly rounded value of the dot product of the (digit-truncated)
+// activations: D=4 keeps 28 bits below the row maximum (f32 inputs lose
+// nothing that matters), D=3 keeps 21.  Results do not depend on how K is
+// split over CTAs: integer partial sums are order-independent.
+//
+// Data movement per CTA (persistent, one per SM, warp-specialised):
+//   warp 0  : TMA producer — 128x128-byte weight tiles (HBM, read once) and the
+//             matching NBx128-byte digit tiles (L2) into an 8-stage smem ring,
+//             128-byte swizzle, mbarrier complete_tx;
+//   warp 1  : allocates TMEM, issues tcgen05.mma (M=128, N=NB, K=32) from one
+//             elected lane, frees ring slots with tcgen05.commit;
+//   warps 2-5: epilogue — tcgen05.ld the int32 accumulators (double-buffered in
+//             TMEM), combine digits, scale, store y; or, when K is split over
+//             several CTAs, add partial sums into an int32 scratch with
+//             red.global and let the last CTA of a tile finalise.
+// Every mbarrier wait is bounded by a wall-clock limit; on expiry the kernel
+// raises the context's timeout flag, drains and frees its TMEM.
+#include <cuda.h>
+
+#include <cstring>
+
 #include "internal.h"
-namespace rusty {
-bool tc_supported(const rusty_cuda_ctx*, const QLinearArgs&) { return false; }
-uint32_t tc_min_rows() { return 5; }
-int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs&) { return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tcgen05 path not built"); }
+
+namespace {
+
+constexpr int BM = 128;            // weight rows per tile = UMMA M
+constexpr int BK = 128;            // k-elements (bytes) per pipeline stage
+constexpr int UMMA_K = 32;         // k-elements per tcgen05.mma kind::i8
+constexpr int TC_THREADS = 192;    // producer warp, MMA warp, 4 epilogue warps
+constexpr int EPI_THREADS = 128;
+constexpr int A_STAGE_BYTES = BM * BK;
+constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // 4 s
+
+// ----------------------------------------------------------------------------
+// PTX wrappers
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false (after raising the status word) when the limit
+// expires or another role of this CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          rusty_cuda_dev_status* status, unsigned site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                if (atomicExch(&status->timeout_flag, 1u) == 0u) status->timeout_where = site;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint64_t* bar,
+                                            uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, int8 x int8 -> int32
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// mbarrier arrives once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, int32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart (descriptor version 1 = Blackwell).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address
+    d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                         // version
+    d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+    return d;
+}
+
+template <typename T>
+__device__ __forceinline__ void store_y(T* p, float v);
+template <>
+__device__ __forceinline__ void store_y<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// ----------------------------------------------------------------------------
+// Pre-pass: activations -> digit planes.
+// xq is [D*Mpad, K] int8, row d*Mpad + m; inv_s[m] = 1 / s_m.  One block per m
+// (rows M..Mpad-1 are written as zeros).
+// ----------------------------------------------------------------------------
+template <typename XT>
+__device__ __forceinline__ float x_to_f32(XT v);
+template <>
+__device__ __forceinline__ float x_to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float x_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename XT, int D>
+__global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ x, int8_t* __restrict__ xq,
+                                                         float* __restrict__ inv_s, int M, int Mpad, int K) {
+    const int m = blockIdx.x;
+    __shared__ float red[8];
+    __shared__ float s_scale;
+    const int tid = threadIdx.x;
+    if (m >= M) {
+        for (int k = tid * 4; k < K; k += 256 * 4)
+#pragma unroll
+            for (int d = 0; d < D; ++d) *reinterpret_cast<uint32_t*>(xq + (size_t)(d * Mpad + m) * K + k) = 0u;
+        return;
+    }
+    const XT* xr = x + (size_t)m * K;
+    float mx = 0.0f;
+    for (int k = tid; k < K; k += 256) {
+        float a = fabsf(x_to_f32<XT>(xr[k]));
+        mx = (a <= 3.0e38f) ? fmaxf(mx, a) : __int_as_float(0x7f800000);  // NaN or inf anywhere poisons the row
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    if (tid == 0) {
+        float v = red[0];
+        for (int i = 1; i < 8; ++i) v = fmaxf(v, red[i]);
+        float s = 1.0f;
+        if (v > 0.0f && v <= 3.0e38f) {
+            int e;
+            frexpf(v, &e);            // v = f * 2^e, f in [0.5, 1)
+            s = ldexpf(1.0f, 7 - e);  // v*s in [64, 128)
+            if (v * s > 127.0f) s *= 0.5f;
+        }
+        s_scale = s;
+        inv_s[m] = (v <= 3.0e38f) ? 1.0f / s : __int_as_float(0x7fc00000);  // inf/nan activations poison the row
+    }
+    __syncthreads();
+    const float s = s_scale;
+    for (int k = tid * 4; k < K; k += 256 * 4) {  // K % 4 == 0 (K % 16 == 0 is required by the caller)
+        uint32_t packed[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) packed[d] = 0u;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float r = x_to_f32<XT>(xr[k + e]) * s;  // exact: s is a power of two
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                float q = rintf(r);
+                packed[d] |= ((uint32_t)(int)q & 0xFFu) << (8 * e);
+                r = (r - q) * 128.0f;  // exact
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < D; ++d) *reinterpret_cast<uint32_t*>(xq + (size_t)(d * Mpad + m) * K + k) = packed[d];
+    }
+}
+
+// ----------------------------------------------------------------------------
+// Main kernel
+// ----------------------------------------------------------------------------
+struct TcParams {
+    const float* scales;   // [N]
+    const float* inv_s;    // [Mpad]
+    int32_t* acc;          // split-K scratch, [NB][Npad] column-major (zero between uses)
+    unsigned int* counters;  // [tiles] arrivals per row tile (zero between uses)
+    void* y;
+    int M, Mpad, D, NB;    // NB = UMMA N = roundup16(D*Mpad)
+    int N, K, Npad;
+    int tiles, kb_total;   // row tiles, k-blocks per row tile
+    int work, per_cta;     // work = tiles*kb_total k-blocks in all, dealt out in contiguous runs of per_cta
+    int ldy, y_col0;
+    int stages;
+    uint32_t idesc;
+    uint32_t tmem_cols;
+    rusty_cuda_dev_status* status;
+};
+
+template <typename YT>
+__device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, const int32_t* c /*[D]*/, float scale_n) {
+    double v = 0.0;
+    for (int d = p.D - 1; d >= 0; --d) v = v * (1.0 / 128.0) + (double)c[d];
+    v *= (double)p.inv_s[m];
+    v *= (double)scale_n;
+    store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, (float)v);
+}
+
+template <typename YT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // carve: [A stages][B stages][barriers]
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int b_stage_bytes = p.NB * BK;
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + (size_t)p.stages * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + (size_t)p.stages * b_stage_bytes);
+    uint64_t* full = bars;                      // [stages]
+    uint64_t* empty = bars + p.stages;          // [stages]
+    uint64_t* acc_full = bars + 2 * p.stages;   // [2]
+    uint64_t* acc_empty = acc_full + 2;         // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Stream-K: the tiles*kb_total k-blocks of the whole problem are one linear
+    // index space g = tile*kb_total + kb; this CTA owns the contiguous run
+    // [g_begin, g_end).  A run crosses tile borders, so it is cut into segments
+    // (tile, [kb0, kb1)); a tile cut over several CTAs is summed in the scratch.
+    const int g_begin = blockIdx.x * p.per_cta;
+    const int g_end = min(p.work, g_begin + p.per_cta);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 4);
+        }
+        *abort_flag = 0;
+        *last_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, p.tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+            int stage = 0;
+            uint32_t phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int g = g_begin; g < g_end && ok; ++g) {
+                const int t = g / p.kb_total, kb = g % p.kb_total;
+                if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                mbar_expect_tx(&full[stage], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
+                tma_load_2d(sA + (size_t)stage * A_STAGE_BYTES, &map_w, kb * BK, t * BM, &full[stage], pol_w);
+                tma_load_2d(sB + (size_t)stage * b_stage_bytes, &map_x, kb * BK, 0, &full[stage], pol_x);
+                ++issued;
+                if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+            }
+            if (!ok) {
+                // give the copies still in flight a bounded chance to land before the CTA tears down
+                for (int j = 0; j < p.stages && j < issued; ++j) {
+                    const int idx = issued - 1 - j;
+                    uint64_t* bar = &full[idx % p.stages];
+                    const uint32_t par = (uint32_t)(idx / p.stages) & 1u;
+                    const uint64_t t0 = global_ns();
+                    while (!mbar_try_wait(bar, par) && global_ns() - t0 < 2000000ull) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int i = 0;
+            bool ok = true;
+            for (int g = g_begin; g < g_end && ok; ++i) {
+                const int kb0 = g % p.kb_total;
+                const int kb1 = min(p.kb_total, kb0 + (g_end - g));
+                const int ab = i & 1;
+                if (!mbar_wait(&acc_empty[ab], (((uint32_t)i >> 1) & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(ab * p.NB);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t da = make_smem_desc(smem_u32(sA + (size_t)stage * A_STAGE_BYTES));
+                    const uint64_t db = make_smem_desc(smem_u32(sB + (size_t)stage * b_stage_bytes));
+#pragma unroll
+                    for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+                        // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
+                        umma_i8(d_tmem, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), p.idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(&acc_full[ab]);
+                g += kb1 - kb0;
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const int r = q * 32 + lane;            // row inside the tile
+        YT* y = reinterpret_cast<YT*>(p.y);
+        int i = 0;
+        bool ok = true;
+        for (int g = g_begin; g < g_end && ok; ++i) {
+            const int t = g / p.kb_total;
+            const int kb0 = g % p.kb_total;
+            const int kb1 = min(p.kb_total, kb0 + (g_end - g));
+            g += kb1 - kb0;
+            // how many CTAs hold a piece of this tile
+            const int first_cta = (t * p.kb_total) / p.per_cta;
+            const int last_cta = ((t + 1) * p.kb_total - 1) / p.per_cta;
+            const int nseg = last_cta - first_cta + 1;
+            const int ab = i & 1;
+            const int n = t * BM + r;
+            const bool row_ok = n < p.N;
+            if (!mbar_wait(&acc_full[ab], ((uint32_t)i >> 1) & 1u, abort_flag, p.status, 4)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * p.NB);
+            if (nseg == 1) {
+                const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+                for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
+                    int32_t c[4][8];
+#pragma unroll
+                    for (int d = 0; d < 4; ++d) {
+                        if (d < p.D) {
+                            tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c[d]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) c[d][e] = 0;
+                        }
+                    }
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int mm = 0; mm < 8; ++mm) {
+                            const int m = m0 + mm;
+                            if (m < p.M) {
+                                int32_t cd[4] = {c[0][mm], c[1][mm], c[2][mm], c[3][mm]};
+                                finalize_store<YT>(p, y, n, m, cd, sc);
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
+            } else {
+                // partial sums of this K slice -> scratch (exact integer adds, any order)
+                for (int j0 = 0; j0 < p.D * p.Mpad; j0 += 8) {
+                    int32_t c[8];
+                    tmem_ld8(taddr + (uint32_t)j0, c);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) {
+                            const int j = j0 + jj;
+                            if ((j % p.Mpad) < p.M) atomicAdd(p.acc + (size_t)j * p.Npad + n, c[jj]);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                // the last CTA to arrive for this row tile turns the sums into y
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                if (threadIdx.x == 64) {
+                    unsigned prev = atomicAdd(p.counters + t, 1u);
+                    *reinterpret_cast<volatile int*>(last_flag) = (prev == (unsigned)(nseg - 1)) ? 1 : 0;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                const bool last = *reinterpret_cast<volatile int*>(last_flag) != 0;
+                if (last) {
+                    __threadfence();
+                    if (row_ok) {
+                        const float sc = __ldg(p.scales + n);
+                        for (int m0 = 0; m0 < p.M; m0 += 8) {
+                            // all loads of the chunk first (independent, in flight together), then the zeroing stores
+                            int32_t v[4][8];
+#pragma unroll
+                            for (int d = 0; d < 4; ++d)
+#pragma unroll
+                                for (int mm = 0; mm < 8; ++mm)
+                                    v[d][mm] = (d < p.D && m0 + mm < p.M)
+                                                   ? __ldcg(p.acc + (size_t)(d * p.Mpad + m0 + mm) * p.Npad + n)
+                                                   : 0;
+#pragma unroll
+                            for (int d = 0; d < 4; ++d)
+#pragma unroll
+                                for (int mm = 0; mm < 8; ++mm)
+                                    if (d < p.D && m0 + mm < p.M) __stcg(p.acc + (size_t)(d * p.Mpad + m0 + mm) * p.Npad + n, 0);
+#pragma unroll
+                            for (int mm = 0; mm < 8; ++mm)
+                                if (m0 + mm < p.M) {
+                                    int32_t cd[4] = {v[0][mm], v[1][mm], v[2][mm], v[3][mm]};
+                                    finalize_store<YT>(p, y, n, m0 + mm, cd, sc);
+                                }
+                        }
+                    }
+                    if (threadIdx.x == 64) p.counters[t] = 0u;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // last_flag is reused by the next segment
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, p.tmem_cols);
+    }
+}
+
+// ----------------------------------------------------------------------------
+// Host side
+// ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// [rows, K] uint8 row-major, boxes of box_rows x 128 bytes, 128-byte swizzle, zero fill outside.
+bool make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows, CUtensorMapL2promotion promo) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {K};
+    cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+constexpr size_t WS_XQ_BYTES = 24u << 20;      // digit planes: up to 256 rows x K <= 96K
+constexpr size_t WS_INVS_BYTES = 4096;
+constexpr size_t WS_ACC_BYTES = 48u << 20;     // split-K partial sums
+constexpr size_t WS_CNT_BYTES = 64u << 10;
+constexpr size_t WS_TOTAL = WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES + WS_CNT_BYTES;
+
+int pick_digits(int x_dtype, uint32_t rows) {
+    // 4 digits (28 bits under the row maximum) while the B operand stays narrow, else 3 (21 bits).
+    uint32_t mpad = (rows + 7) / 8 * 8;
+    return (x_dtype == RUSTY_CUDA_F32 && mpad * 4 <= 64) ? 4 : 3;
+}
+
+template <typename XT>
+void launch_digitize(rusty_cuda_ctx* ctx, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D) {
+    if (D == 4)
+        digitize_x_kernel<XT, 4><<<Mpad, 256, 0, ctx->stream>>>((const XT*)x, xq, inv_s, M, Mpad, K);
+    else
+        digitize_x_kernel<XT, 3><<<Mpad, 256, 0, ctx->stream>>>((const XT*)x, xq, inv_s, M, Mpad, K);
+}
+
+}  // namespace
+
+namespace rusty {
+
+int tc_workspace_reserve(rusty_cuda_ctx* ctx) {
+    if (ctx->tc_ws) return RUSTY_CUDA_OK;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, WS_TOTAL);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ctx, RUSTY_CUDA_ERR_MEMORY_ALLOCATION, "tensor-core workspace: cudaMalloc(%zu) failed", (size_t)WS_TOTAL);
+    }
+    e = cudaMemsetAsync(p, 0, WS_TOTAL, ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return check_cuda(ctx, e, "tensor-core workspace: memset");
+    }
+    ctx->tc_ws = p;
+    ctx->tc_ws_bytes = WS_TOTAL;
+    return RUSTY_CUDA_OK;
+}
+
+void tc_workspace_release(rusty_cuda_ctx* ctx) {
+    if (ctx->tc_ws) cudaFree(ctx->tc_ws);
+    ctx->tc_ws = nullptr;
+    ctx->tc_ws_bytes = 0;
+}
+
+uint32_t tc_min_rows() { return 5; }
+
+bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a) {
+    if (!ctx->tc_ws || !encode_tiled_fn()) return false;
+    if (a.layout != RUSTY_CUDA_LAYOUT_NK || a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
+    if (a.K % 16 != 0 || a.K > 96 * 1024) return false;
+    if ((reinterpret_cast<uintptr_t>(a.w) & 15) != 0) return false;
+    return true;
+}
+
+// One launch pair (digitise + GEMM) for up to 64 activation rows.
+static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void* x, void* y, uint32_t rows) {
+    const int M = (int)rows, Mpad = (M + 7) / 8 * 8;
+    const int D = pick_digits(a.x_dtype, rows);
+    const int NB = (D * Mpad + 15) / 16 * 16;
+    uint8_t* ws = (uint8_t*)ctx->tc_ws;
+    int8_t* xq = (int8_t*)ws;
+    float* inv_s = (float*)(ws + WS_XQ_BYTES);
+    int32_t* acc = (int32_t*)(ws + WS_XQ_BYTES + WS_INVS_BYTES);
+    unsigned int* counters = (unsigned int*)(ws + WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES);
+    if ((size_t)D * Mpad * a.K > WS_XQ_BYTES)
+        return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: %d digit rows x K=%u exceed the workspace", D * Mpad, a.K);
+
+    if (a.x_dtype == RUSTY_CUDA_BF16)
+        launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D);
+    else
+        launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D);
+    int rc = after_launch(ctx, "digitize_x");
+    if (rc) return rc;
+
+    TcParams p{};
+    p.scales = a.scales;
+    p.inv_s = inv_s;
+    p.acc = acc;
+    p.counters = counters;
+    p.y = y;
+    p.M = M;
+    p.Mpad = Mpad;
+    p.D = D;
+    p.NB = NB;
+    p.N = (int)a.N;
+    p.K = (int)a.K;
+    p.tiles = (p.N + BM - 1) / BM;
+    p.Npad = p.tiles * BM;
+    p.kb_total = (p.K + BK - 1) / BK;
+    // stream-K: deal the tiles*kb_total k-blocks out evenly, at least 4 per CTA
+    p.work = p.tiles * p.kb_total;
+    int grid = ctx->sm_count;
+    if (grid > p.work / 4) grid = p.work / 4 > 0 ? p.work / 4 : 1;
+    p.per_cta = (p.work + grid - 1) / grid;
+    grid = (p.work + p.per_cta - 1) / p.per_cta;
+    // a tile cut across CTAs needs the scratch; if the scratch is too small fall back to whole tiles per CTA
+    if ((size_t)NB * p.Npad * 4 > WS_ACC_BYTES || (size_t)p.tiles * 4 > WS_CNT_BYTES) {
+        int tiles_per_cta = (p.tiles + ctx->sm_count - 1) / ctx->sm_count;
+        p.per_cta = tiles_per_cta * p.kb_total;
+        grid = (p.work + p.per_cta - 1) / p.per_cta;
+    }
+    p.ldy = (int)a.ldy;
+    p.y_col0 = (int)a.y_col0;
+    p.status = ctx->status_dev;
+    // int8 x int8 -> int32, both K-major: c_format=S32(2)@4, a_format=INT8(1)@7, b_format=INT8(1)@10, N>>3 @17, M>>4 @24
+    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    uint32_t cols = 32;
+    while (cols < (uint32_t)(2 * NB)) cols <<= 1;
+    p.tmem_cols = cols;
+    const int b_stage = NB * BK;
+    const size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
+    int stages = (int)((budget - 1024 - 256) / (size_t)(A_STAGE_BYTES + b_stage));
+    if (stages > 8) stages = 8;
+    if (stages < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: tile does not fit shared memory");
+    p.stages = stages;
+    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + (size_t)(2 * stages + 4) * 8 + 64;
+
+    CUtensorMap map_w, map_x;
+    if (!make_map_u8(&map_w, a.w, a.N, a.K, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
+        !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, a.K, (uint32_t)NB, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+        return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "tensor-core path: cuTensorMapEncodeTiled failed");
+
+    const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
+    auto kern = yb ? qlinear_i8_tc_kernel<__nv_bfloat16> : qlinear_i8_tc_kernel<float>;
+    static size_t smem_set[2][16] = {{0}};
+    size_t& cur = smem_set[yb ? 1 : 0][ctx->device & 15];
+    if (smem > cur) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_i8_tc: cudaFuncSetAttribute");
+        cur = smem;
+    }
+    kern<<<grid, TC_THREADS, smem, ctx->stream>>>(map_w, map_x, p);
+    return after_launch(ctx, "qlinear_i8_tc");
+}
+
+int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
+    const size_t xs = a.x_dtype == RUSTY_CUDA_BF16 ? 2 : 4, ys = a.y_dtype == RUSTY_CUDA_BF16 ? 2 : 4;
+    for (uint32_t m0 = 0; m0 < a.M; m0 += 64) {
+        uint32_t rows = a.M - m0 < 64 ? a.M - m0 : 64;
+        int rc = launch_tc_rows(ctx, a, (const char*)a.x + (size_t)m0 * a.K * xs, (char*)a.y + (size_t)m0 * a.ldy * ys, rows);
+        if (rc) return rc;
+    }
+    return RUSTY_CUDA_OK;
+}
+
+}  // namespace rusty

@@ -39,6 +39,10 @@ struct rusty_cuda_ctx {
     // device-visible status word (pinned + mapped)
     rusty_cuda_dev_status* status_host = nullptr;
     rusty_cuda_dev_status* status_dev = nullptr;
+    // workspace of the tensor-core path (digit planes, split-K sums); reserved when
+    // the first fused linear is created, never inside a forward call
+    void* tc_ws = nullptr;
+    size_t tc_ws_bytes = 0;
     // stream capture in progress (rusty_cuda_graph_begin .. _end)
     bool capturing = false;
     uint64_t launches_at_capture = 0;
@@ -128,6 +132,8 @@ int launch_gemv(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 // Tensor-core (tcgen05 / TMEM) path.
 bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 uint32_t tc_min_rows();
+int tc_workspace_reserve(rusty_cuda_ctx* ctx);
+void tc_workspace_release(rusty_cuda_ctx* ctx);
 int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 
 const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);

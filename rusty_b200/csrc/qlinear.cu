@@ -108,6 +108,11 @@ int rusty_cuda_qlinear_create(rusty_cuda_ctx* ctx, rusty_cuda_buf* weight, rusty
     } else {
         return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_create: unknown qmode %d", qmode);
     }
+    {
+        DeviceGuard g(ctx->device);
+        int rc = tc_workspace_reserve(ctx);
+        if (rc) return rc;
+    }
     rusty_cuda_qlinear* q = new (std::nothrow) rusty_cuda_qlinear();
     if (!q) return fail(ctx, RUSTY_CUDA_ERR_MEMORY_ALLOCATION, "qlinear_create: host allocation failed");
     q->ctx = ctx;

@@ -191,3 +191,81 @@ def test_empty_and_invalid(ctx, engine):
         engine.qlinear(ctx, xi, ql, UnifiedTensor.empty(ctx, [2, 16]))
     assert e.value.kind == "InvalidDataType"
     ctx.sync()
+
+
+# ---- tensor-core (tcgen05 / TMEM) path: batches of activation rows ----
+
+@pytest.mark.parametrize("M,K,N", [(5, 256, 128), (8, 4096, 4096), (32, 4096, 1024), (32, 4096, 14336), (17, 1024, 130),
+                                   (64, 8192, 1024), (32, 14336, 4096), (100, 512, 384), (6, 80, 24), (33, 4096, 128256)])
+def test_tc_shapes_f32(ctx, engine, oracle, M, K, N):
+    x, q, s = sym_row_linear(K + 3 * N + M, M, K, N)
+    ql = QLinear.from_host(ctx, q, s)
+    assert ql.plan(M) == "tcgen05"
+    got = _forward(ctx, engine, ql, x)
+    ctx.sync()  # also surfaces a device-side wait that gave up
+    if N * K * M > 2e10:
+        rows = [0, M // 2, M - 1]  # full-size LM head: a few activation rows against the scalar oracle
+        ref = oracle.matmul_bt(x[rows], oracle.dequantize_rowscale(q, s), mt=True)
+        assert rel_err(got[rows], ref) <= TOL_FP32
+        assert np.isfinite(got).all()
+    else:
+        ref = oracle.matmul_bt(x, oracle.dequantize_rowscale(q, s), mt=True)
+        assert rel_err(got, ref) <= TOL_FP32
+
+
+def test_tc_is_closer_to_exact_than_the_reference_arithmetic(ctx, engine, oracle):
+    """Integer tensor-core sums are exact; the result sits nearer the float64
+    dot products than the reference's own sequential f32 accumulation does."""
+    x, q, s = sym_row_linear(77, 16, 4096, 2048)
+    wf = oracle.dequantize_rowscale(q, s)
+    got = _forward(ctx, engine, QLinear.from_host(ctx, q, s), x)
+    exact = oracle.matmul_bt_f64(x, wf)
+    ref = oracle.matmul_bt(x, wf, mt=True)
+    assert rel_err(got, exact) <= 2e-7
+    assert rel_err(got, exact) <= rel_err(ref, exact)
+
+
+def test_tc_bf16_in_out(ctx, engine, oracle):
+    x, q, s = sym_row_linear(78, 32, 4096, 4096)
+    xb = bf16_bits_to_f32(f32_to_bf16_bits(x))
+    ql = QLinear.from_host(ctx, q, s)
+    ref = oracle.matmul_bt(xb, oracle.dequantize_rowscale(q, s), mt=True)
+    got = _forward(ctx, engine, ql, x, x_dtype=DType.BF16)
+    assert rel_err(got, ref) <= TOL_FP32
+    got16 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.BF16)
+    assert rel_err(got16, ref) <= TOL_BF16
+
+
+def test_tc_split_k_is_deterministic_and_leaves_scratch_clean(ctx, engine):
+    """K split over CTAs sums integers, so repeated calls give identical bits,
+    and the shared scratch is zero again for the next call of another shape."""
+    x, q, s = sym_row_linear(79, 32, 4096, 1024)   # 8 row tiles -> every tile is cut over several CTAs
+    ql = QLinear.from_host(ctx, q, s)
+    a = _forward(ctx, engine, ql, x)
+    for _ in range(3):
+        assert_bits_equal(_forward(ctx, engine, ql, x), a)
+    x2, q2, s2 = sym_row_linear(80, 8, 2048, 512)
+    ql2 = QLinear.from_host(ctx, q2, s2)
+    b = _forward(ctx, engine, ql2, x2)
+    assert_bits_equal(_forward(ctx, engine, ql, x), a)
+    assert_bits_equal(_forward(ctx, engine, ql2, x2), b)
+
+
+def test_tc_rows_do_not_interact(ctx, engine):
+    x, q, s = sym_row_linear(81, 32, 4096, 4096)
+    x[3] *= 1000.0      # rows have their own digit scale
+    x[7] = 0.0          # an all-zero row
+    ql = QLinear.from_host(ctx, q, s)
+    y = _forward(ctx, engine, ql, x)
+    assert np.all(y[7] == 0.0)
+    y24 = _forward(ctx, engine, ql, x[:24])      # same digit count as the 32-row call: identical bits
+    assert_bits_equal(y[:24], y24)
+    y8 = _forward(ctx, engine, ql, x[:8])        # narrower batch keeps one more digit: equal within tolerance
+    assert rel_err(y8, y[:8]) <= TOL_FP32
+
+
+def test_tc_nonfinite_activation_poisons_its_row_only(ctx, engine):
+    x, q, s = sym_row_linear(82, 8, 1024, 256)
+    x[2, 5] = np.nan
+    y = _forward(ctx, engine, QLinear.from_host(ctx, q, s), x)
+    assert np.isnan(y[2]).all() and np.isfinite(np.delete(y, 2, axis=0)).all()
