@@ -31,6 +31,7 @@
 // raises the context's timeout flag, drains and frees its TMEM.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "internal.h"
@@ -43,7 +44,7 @@ constexpr int UMMA_K = 32;         // k-elements per tcgen05.mma kind::i8
 constexpr int TC_THREADS = 192;    // producer warp, MMA warp, 4 epilogue warps
 constexpr int EPI_THREADS = 128;
 constexpr int A_STAGE_BYTES = BM * BK;
-constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // 4 s
+constexpr long long WAIT_LIMIT_CYCLES = 8000000000ll;  // ~4 s of SM clock
 
 // ----------------------------------------------------------------------------
 // PTX wrappers
@@ -70,22 +71,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ uint64_t global_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 // Bounded wait.  Returns false (after raising the status word) when the limit
 // expires or another role of this CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           rusty_cuda_dev_status* status, unsigned site) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_ns();
+    long long t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 63u) {
+        if ((it & 255u) == 255u) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            if (t0 == 0) t0 = clock64();
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
                 if (atomicExch(&status->timeout_flag, 1u) == 0u) status->timeout_where = site;
                 return false;
@@ -167,7 +163,7 @@ __device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16* p, float v
 
 // ----------------------------------------------------------------------------
 // Pre-pass: activations -> digit planes.
-// xq is [D*Mpad, K] int8, row d*Mpad + m; inv_s[m] = 1 / s_m.  One block per m
+// xq is [D*Mpad, K] int8, row d*Mpad + m; inv_s[m] = 1 / (s_m * 128^(D-1)).  One block per m
 // (rows M..Mpad-1 are written as zeros).
 // ----------------------------------------------------------------------------
 template <typename XT>
@@ -211,7 +207,8 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
             if (v * s > 127.0f) s *= 0.5f;
         }
         s_scale = s;
-        inv_s[m] = (v <= 3.0e38f) ? 1.0f / s : __int_as_float(0x7fc00000);  // inf/nan activations poison the row
+        // 1/s_m * 128^-(D-1): both powers of two, so the product is exact
+        inv_s[m] = (v <= 3.0e38f) ? ldexpf(1.0f / s, -7 * (D - 1)) : __int_as_float(0x7fc00000);  // inf/nan poisons the row
     }
     __syncthreads();
     const float s = s_scale;
@@ -238,30 +235,85 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
 // Main kernel
 // ----------------------------------------------------------------------------
 struct TcParams {
-    const float* scales;   // [N]
-    const float* inv_s;    // [Mpad]
-    int32_t* acc;          // split-K scratch, [NB][Npad] column-major (zero between uses)
-    unsigned int* counters;  // [tiles] arrivals per row tile (zero between uses)
+    const float* scales;     // [N]
+    const float* row_factor; // [Mpad]: 1/s_m * 128^-(D-1)
+    int32_t* part;           // partial sums of tiles cut across CTAs: [2*grid slots][D*Mpad][128]
+    unsigned int* counters;  // [tiles] arrivals per cut tile (zero between uses)
     void* y;
-    int M, Mpad, D, NB;    // NB = UMMA N = roundup16(D*Mpad)
-    int N, K, Npad;
-    int tiles, kb_total;   // row tiles, k-blocks per row tile
-    int work, per_cta;     // work = tiles*kb_total k-blocks in all, dealt out in contiguous runs of per_cta
+    int M, Mpad, D, NB;      // NB = UMMA N = roundup16(D*Mpad)
+    int N, K;
+    int tiles, kb_total;     // row tiles, k-blocks per row tile
+    // Schedule.  The last `sk_tiles` row tiles are cut stream-K fashion: their
+    // sk_tiles*kb_total k-blocks form one linear space dealt out in contiguous
+    // runs of `sk_per_cta` to the first `sk_ctas` CTAs.  The other tiles are
+    // taken whole, tile = cta, cta + grid, ...
+    int dp_tiles, sk_tiles, sk_per_cta, sk_ctas;
     int ldy, y_col0;
     int stages;
     uint32_t idesc;
     uint32_t tmem_cols;
     rusty_cuda_dev_status* status;
+    long long* dbg;          // optional per-CTA timeline (16 slots each), null in normal use
 };
 
+// One piece of work: k-blocks [kb0, kb1) of row tile t.  nseg > 1: the tile is
+// shared with other CTAs; `slot` is where this CTA parks its partial sums.
+struct Segment {
+    int t, kb0, kb1, nseg, slot, first_cta;
+};
+
+// Every role of the CTA walks the same segment list.
+struct Sched {
+    const TcParams& p;
+    int g, g_end;   // position inside the stream-K space
+    int dp_next;    // next whole tile
+    int seg_index;
+    __device__ Sched(const TcParams& pp) : p(pp) {
+        const int c = blockIdx.x;
+        g = c < p.sk_ctas ? c * p.sk_per_cta : 0;
+        g_end = c < p.sk_ctas ? min(p.sk_tiles * p.kb_total, g + p.sk_per_cta) : 0;
+        dp_next = c;
+        seg_index = 0;
+    }
+    __device__ bool next(Segment& s) {
+        if (g < g_end) {  // stream-K part first: its cross-CTA fix-up then overlaps the whole tiles that follow
+            const int lt = g / p.kb_total;
+            s.t = p.dp_tiles + lt;
+            s.kb0 = g % p.kb_total;
+            s.kb1 = min(p.kb_total, s.kb0 + (g_end - g));
+            s.first_cta = (lt * p.kb_total) / p.sk_per_cta;
+            const int last_cta = ((lt + 1) * p.kb_total - 1) / p.sk_per_cta;
+            s.nseg = last_cta - s.first_cta + 1;
+            // head piece (the CTA's run starts inside this tile) -> even slot, tail piece -> odd slot
+            s.slot = 2 * (int)blockIdx.x + ((int)blockIdx.x * p.sk_per_cta >= lt * p.kb_total ? 0 : 1);
+            g += s.kb1 - s.kb0;
+            ++seg_index;
+            return true;
+        }
+        if (dp_next < p.dp_tiles) {
+            s.t = dp_next;
+            s.kb0 = 0;
+            s.kb1 = p.kb_total;
+            s.nseg = 1;
+            s.slot = 0;
+            s.first_cta = 0;
+            dp_next += gridDim.x;
+            ++seg_index;
+            return true;
+        }
+        return false;
+    }
+};
+
+// Digits -> one exact 64-bit integer -> f32 (one rounding) -> row factor (a power
+// of two, exact) -> weight scale (one rounding).
 template <typename YT>
-__device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, const int32_t* c /*[D]*/, float scale_n) {
-    double v = 0.0;
-    for (int d = p.D - 1; d >= 0; --d) v = v * (1.0 / 128.0) + (double)c[d];
-    v *= (double)p.inv_s[m];
-    v *= (double)scale_n;
-    store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, (float)v);
+__device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n) {
+    const float v = __ll2float_rn(acc) * __ldg(p.row_factor + m);
+    store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, v * scale_n);
 }
+
+#define DBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
 
 template <typename YT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -282,12 +334,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Stream-K: the tiles*kb_total k-blocks of the whole problem are one linear
-    // index space g = tile*kb_total + kb; this CTA owns the contiguous run
-    // [g_begin, g_end).  A run crosses tile borders, so it is cut into segments
-    // (tile, [kb0, kb1)); a tile cut over several CTAs is summed in the scratch.
-    const int g_begin = blockIdx.x * p.per_cta;
-    const int g_end = min(p.work, g_begin + p.per_cta);
+    if (threadIdx.x == 0) DBG(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -307,6 +354,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) DBG(1);
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -316,23 +364,28 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             uint32_t phase = 0;
             int issued = 0;
             bool ok = true;
-            for (int g = g_begin; g < g_end && ok; ++g) {
-                const int t = g / p.kb_total, kb = g % p.kb_total;
-                if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
-                mbar_expect_tx(&full[stage], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
-                tma_load_2d(sA + (size_t)stage * A_STAGE_BYTES, &map_w, kb * BK, t * BM, &full[stage], pol_w);
-                tma_load_2d(sB + (size_t)stage * b_stage_bytes, &map_x, kb * BK, 0, &full[stage], pol_x);
-                ++issued;
-                if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+            Sched sched(p);
+            Segment sg;
+            while (ok && sched.next(sg)) {
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                    mbar_expect_tx(&full[stage], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
+                    tma_load_2d(sA + (size_t)stage * A_STAGE_BYTES, &map_w, kb * BK, sg.t * BM, &full[stage], pol_w);
+                    tma_load_2d(sB + (size_t)stage * b_stage_bytes, &map_x, kb * BK, 0, &full[stage], pol_x);
+                    ++issued;
+                    if (issued == 1) DBG(2);
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
             }
+            DBG(3);
             if (!ok) {
                 // give the copies still in flight a bounded chance to land before the CTA tears down
                 for (int j = 0; j < p.stages && j < issued; ++j) {
                     const int idx = issued - 1 - j;
                     uint64_t* bar = &full[idx % p.stages];
                     const uint32_t par = (uint32_t)(idx / p.stages) & 1u;
-                    const uint64_t t0 = global_ns();
-                    while (!mbar_try_wait(bar, par) && global_ns() - t0 < 2000000ull) {}
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(bar, par) && clock64() - t0 < 4000000ll) {}
                 }
             }
         }
@@ -341,30 +394,30 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            int i = 0;
             bool ok = true;
-            for (int g = g_begin; g < g_end && ok; ++i) {
-                const int kb0 = g % p.kb_total;
-                const int kb1 = min(p.kb_total, kb0 + (g_end - g));
+            Sched sched(p);
+            Segment sg;
+            for (int i = 0; ok && sched.next(sg); ++i) {
                 const int ab = i & 1;
                 if (!mbar_wait(&acc_empty[ab], (((uint32_t)i >> 1) & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(ab * p.NB);
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
                     if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
                     tc_fence_after();
+                    if (kb == sg.kb0 && i == 0) DBG(4);
                     const uint64_t da = make_smem_desc(smem_u32(sA + (size_t)stage * A_STAGE_BYTES));
                     const uint64_t db = make_smem_desc(smem_u32(sB + (size_t)stage * b_stage_bytes));
 #pragma unroll
                     for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
                         // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
-                        umma_i8(d_tmem, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), p.idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+                        umma_i8(d_tmem, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), p.idesc, (kb > sg.kb0 || k4 > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty[stage]);
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) umma_commit(&acc_full[ab]);
-                g += kb1 - kb0;
+                DBG(5);
             }
         }
     } else {
@@ -372,44 +425,35 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
         const int r = q * 32 + lane;            // row inside the tile
         YT* y = reinterpret_cast<YT*>(p.y);
-        int i = 0;
+        const int ncol = p.D * p.Mpad;          // accumulator columns in use
         bool ok = true;
-        for (int g = g_begin; g < g_end && ok; ++i) {
-            const int t = g / p.kb_total;
-            const int kb0 = g % p.kb_total;
-            const int kb1 = min(p.kb_total, kb0 + (g_end - g));
-            g += kb1 - kb0;
-            // how many CTAs hold a piece of this tile
-            const int first_cta = (t * p.kb_total) / p.per_cta;
-            const int last_cta = ((t + 1) * p.kb_total - 1) / p.per_cta;
-            const int nseg = last_cta - first_cta + 1;
+        Sched sched(p);
+        Segment sg;
+        for (int i = 0; ok && sched.next(sg); ++i) {
             const int ab = i & 1;
-            const int n = t * BM + r;
+            const int n = sg.t * BM + r;
             const bool row_ok = n < p.N;
             if (!mbar_wait(&acc_full[ab], ((uint32_t)i >> 1) & 1u, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
+            if (threadIdx.x == 64) DBG(6 + 4 * (i & 1));
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * p.NB);
-            if (nseg == 1) {
+            if (sg.nseg == 1) {
                 const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
                 for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
                     int32_t c[4][8];
 #pragma unroll
-                    for (int d = 0; d < 4; ++d) {
-                        if (d < p.D) {
-                            tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c[d]);
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) c[d][e] = 0;
-                        }
-                    }
+                    for (int d = 0; d < 4; ++d)
+                        if (d < p.D) tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c[d]);
                     tmem_ld_wait();
                     if (row_ok) {
 #pragma unroll
                         for (int mm = 0; mm < 8; ++mm) {
-                            const int m = m0 + mm;
-                            if (m < p.M) {
-                                int32_t cd[4] = {c[0][mm], c[1][mm], c[2][mm], c[3][mm]};
-                                finalize_store<YT>(p, y, n, m, cd, sc);
+                            if (m0 + mm < p.M) {
+                                long long acc = c[0][mm];
+#pragma unroll
+                                for (int d = 1; d < 4; ++d)
+                                    if (d < p.D) acc = acc * 128 + c[d][mm];
+                                finalize_store<YT>(p, y, n, m0 + mm, acc, sc);
                             }
                         }
                     }
@@ -418,71 +462,97 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[ab]);
             } else {
-                // partial sums of this K slice -> scratch (exact integer adds, any order)
-                for (int j0 = 0; j0 < p.D * p.Mpad; j0 += 8) {
-                    int32_t c[8];
-                    tmem_ld8(taddr + (uint32_t)j0, c);
-                    tmem_ld_wait();
-                    if (row_ok) {
-#pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) {
-                            const int j = j0 + jj;
-                            if ((j % p.Mpad) < p.M) atomicAdd(p.acc + (size_t)j * p.Npad + n, c[jj]);
-                        }
+                // this CTA's piece of a shared tile: park the partial sums.  Layout per slot:
+                // [m/4][d][row][4 consecutive m] so a thread moves 16 bytes and a warp 512 contiguous bytes.
+                int4* mine = reinterpret_cast<int4*>(p.part) + (size_t)sg.slot * (ncol / 4) * BM;
+                for (int d = 0; d < p.D; ++d)
+                    for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
+                        int32_t c[8];
+                        tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c);
+                        tmem_ld_wait();
+                        const int mg = m0 / 4;
+                        __stcg(mine + (size_t)(mg * p.D + d) * BM + r, make_int4(c[0], c[1], c[2], c[3]));
+                        __stcg(mine + (size_t)((mg + 1) * p.D + d) * BM + r, make_int4(c[4], c[5], c[6], c[7]));
                     }
-                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[ab]);
-                // the last CTA to arrive for this row tile turns the sums into y
+                if (threadIdx.x == 64) DBG(7 + 4 * (i & 1));
+                // the last CTA to arrive for this row tile adds the pieces (integers: any order, same bits)
                 __threadfence();
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (threadIdx.x == 64) {
-                    unsigned prev = atomicAdd(p.counters + t, 1u);
-                    *reinterpret_cast<volatile int*>(last_flag) = (prev == (unsigned)(nseg - 1)) ? 1 : 0;
+                    unsigned prev = atomicAdd(p.counters + sg.t, 1u);
+                    *reinterpret_cast<volatile int*>(last_flag) = (prev == (unsigned)(sg.nseg - 1)) ? 1 : 0;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 const bool last = *reinterpret_cast<volatile int*>(last_flag) != 0;
+                if (threadIdx.x == 64) DBG(8 + 4 * (i & 1));
                 if (last) {
                     __threadfence();
                     if (row_ok) {
                         const float sc = __ldg(p.scales + n);
-                        for (int m0 = 0; m0 < p.M; m0 += 8) {
-                            // all loads of the chunk first (independent, in flight together), then the zeroing stores
-                            int32_t v[4][8];
+                        const int lt = sg.t - p.dp_tiles;
+                        // four activation rows at a time: up to 8 pieces x D digit planes of 16-byte loads in flight
+                        for (int mg = 0; mg * 4 < p.M; ++mg) {
+                            int4 v[4];
 #pragma unroll
-                            for (int d = 0; d < 4; ++d)
+                            for (int d = 0; d < 4; ++d) v[d] = make_int4(0, 0, 0, 0);
+                            for (int s0 = 0; s0 < sg.nseg; s0 += 8) {
+                                int4 ld[8][4];
 #pragma unroll
-                                for (int mm = 0; mm < 8; ++mm)
-                                    v[d][mm] = (d < p.D && m0 + mm < p.M)
-                                                   ? __ldcg(p.acc + (size_t)(d * p.Mpad + m0 + mm) * p.Npad + n)
-                                                   : 0;
+                                for (int u = 0; u < 8; ++u) {
+                                    const int cta = sg.first_cta + s0 + u;
+                                    const int slot = 2 * cta + (cta * p.sk_per_cta >= lt * p.kb_total ? 0 : 1);
+                                    const int4* src = reinterpret_cast<const int4*>(p.part) + (size_t)slot * (ncol / 4) * BM + r;
 #pragma unroll
-                            for (int d = 0; d < 4; ++d)
-#pragma unroll
-                                for (int mm = 0; mm < 8; ++mm)
-                                    if (d < p.D && m0 + mm < p.M) __stcg(p.acc + (size_t)(d * p.Mpad + m0 + mm) * p.Npad + n, 0);
-#pragma unroll
-                            for (int mm = 0; mm < 8; ++mm)
-                                if (m0 + mm < p.M) {
-                                    int32_t cd[4] = {v[0][mm], v[1][mm], v[2][mm], v[3][mm]};
-                                    finalize_store<YT>(p, y, n, m0 + mm, cd, sc);
+                                    for (int d = 0; d < 4; ++d)
+                                        ld[u][d] = (s0 + u < sg.nseg && d < p.D) ? __ldcg(src + (size_t)(mg * p.D + d) * BM)
+                                                                                 : make_int4(0, 0, 0, 0);
                                 }
+#pragma unroll
+                                for (int u = 0; u < 8; ++u)
+#pragma unroll
+                                    for (int d = 0; d < 4; ++d) {
+                                        v[d].x += ld[u][d].x;
+                                        v[d].y += ld[u][d].y;
+                                        v[d].z += ld[u][d].z;
+                                        v[d].w += ld[u][d].w;
+                                    }
+                            }
+#pragma unroll
+                            for (int mm = 0; mm < 4; ++mm) {
+                                const int m = mg * 4 + mm;
+                                if (m < p.M) {
+                                    const int32_t c0 = mm == 0 ? v[0].x : mm == 1 ? v[0].y : mm == 2 ? v[0].z : v[0].w;
+                                    long long acc = c0;
+#pragma unroll
+                                    for (int d = 1; d < 4; ++d)
+                                        if (d < p.D) {
+                                            const int32_t cd = mm == 0 ? v[d].x : mm == 1 ? v[d].y : mm == 2 ? v[d].z : v[d].w;
+                                            acc = acc * 128 + cd;
+                                        }
+                                    finalize_store<YT>(p, y, n, m, acc, sc);
+                                }
+                            }
                         }
                     }
-                    if (threadIdx.x == 64) p.counters[t] = 0u;
+                    if (threadIdx.x == 64) p.counters[sg.t] = 0u;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // last_flag is reused by the next segment
+                if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
             }
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) DBG(14);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, p.tmem_cols);
     }
+    if (threadIdx.x == 32) DBG(15);
 }
 
 // ----------------------------------------------------------------------------
@@ -567,7 +637,16 @@ void tc_workspace_release(rusty_cuda_ctx* ctx) {
     ctx->tc_ws_bytes = 0;
 }
 
-uint32_t tc_min_rows() { return 5; }
+uint32_t tc_min_rows() {
+    // RUSTY_TC_MIN_ROWS overrides the crossover between the CUDA-core GEMV and the tensor-core kernel (tuning aid).
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RUSTY_TC_MIN_ROWS");
+        v = e ? atoi(e) : 5;
+        if (v < 1) v = 1;
+    }
+    return (uint32_t)v;
+}
 
 bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     if (!ctx->tc_ws || !encode_tiled_fn()) return false;
@@ -599,8 +678,8 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
 
     TcParams p{};
     p.scales = a.scales;
-    p.inv_s = inv_s;
-    p.acc = acc;
+    p.row_factor = inv_s;
+    p.part = acc;
     p.counters = counters;
     p.y = y;
     p.M = M;
@@ -610,23 +689,36 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.N = (int)a.N;
     p.K = (int)a.K;
     p.tiles = (p.N + BM - 1) / BM;
-    p.Npad = p.tiles * BM;
     p.kb_total = (p.K + BK - 1) / BK;
-    // stream-K: deal the tiles*kb_total k-blocks out evenly, at least 4 per CTA
-    p.work = p.tiles * p.kb_total;
+    // Whole waves of row tiles are taken tile-per-CTA; the remainder (fewer tiles
+    // than SMs) is cut stream-K fashion so every SM streams the same number of
+    // k-blocks.  A cut needs >= 4 k-blocks per CTA, a counter per tile and room
+    // for two parked partial tiles per CTA; otherwise the remainder is taken whole too.
     int grid = ctx->sm_count;
-    if (grid > p.work / 4) grid = p.work / 4 > 0 ? p.work / 4 : 1;
-    p.per_cta = (p.work + grid - 1) / grid;
-    grid = (p.work + p.per_cta - 1) / p.per_cta;
-    // a tile cut across CTAs needs the scratch; if the scratch is too small fall back to whole tiles per CTA
-    if ((size_t)NB * p.Npad * 4 > WS_ACC_BYTES || (size_t)p.tiles * 4 > WS_CNT_BYTES) {
-        int tiles_per_cta = (p.tiles + ctx->sm_count - 1) / ctx->sm_count;
-        p.per_cta = tiles_per_cta * p.kb_total;
-        grid = (p.work + p.per_cta - 1) / p.per_cta;
+    if (grid > p.tiles * p.kb_total / 4) grid = p.tiles * p.kb_total / 4 > 0 ? p.tiles * p.kb_total / 4 : 1;
+    p.sk_tiles = p.tiles % grid;
+    p.dp_tiles = p.tiles - p.sk_tiles;
+    p.sk_per_cta = 0;
+    p.sk_ctas = 0;
+    if (p.sk_tiles > 0) {
+        const int sk_work = p.sk_tiles * p.kb_total;
+        p.sk_per_cta = (sk_work + grid - 1) / grid;
+        if (p.sk_per_cta < 4) p.sk_per_cta = 4;
+        p.sk_ctas = (sk_work + p.sk_per_cta - 1) / p.sk_per_cta;
+        const size_t need = (size_t)2 * grid * D * Mpad * BM * 4;
+        if (need > WS_ACC_BYTES || (size_t)p.tiles * 4 > WS_CNT_BYTES) {
+            p.dp_tiles = p.tiles;  // no room to park partial tiles: whole tiles only
+            p.sk_tiles = 0;
+            p.sk_per_cta = 0;
+            p.sk_ctas = 0;
+            if (grid > p.tiles) grid = p.tiles;
+        }
     }
+    if (p.dp_tiles == 0 && p.sk_ctas > 0) grid = p.sk_ctas;
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
     p.status = ctx->status_dev;
+    p.dbg = (long long*)ctx->tc_dbg;
     // int8 x int8 -> int32, both K-major: c_format=S32(2)@4, a_format=INT8(1)@7, b_format=INT8(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     uint32_t cols = 32;
@@ -646,6 +738,7 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
         return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "tensor-core path: cuTensorMapEncodeTiled failed");
 
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
+
     auto kern = yb ? qlinear_i8_tc_kernel<__nv_bfloat16> : qlinear_i8_tc_kernel<float>;
     static size_t smem_set[2][16] = {{0}};
     size_t& cur = smem_set[yb ? 1 : 0][ctx->device & 15];
@@ -669,3 +762,11 @@ int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
 }
 
 }  // namespace rusty
+
+// Development aid: point the tensor-core kernel's per-CTA timeline at a caller
+// buffer (148 CTAs x 16 clock64 slots), or detach it with NULL.
+extern "C" RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf) {
+    if (!ctx) return RUSTY_CUDA_ERR_INVALID_OPERATION;
+    ctx->tc_dbg = buf ? buf->ptr : nullptr;
+    return RUSTY_CUDA_OK;
+}

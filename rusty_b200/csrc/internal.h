@@ -43,6 +43,7 @@ struct rusty_cuda_ctx {
     // the first fused linear is created, never inside a forward call
     void* tc_ws = nullptr;
     size_t tc_ws_bytes = 0;
+    void* tc_dbg = nullptr;  // optional kernel timeline buffer (development aid)
     // stream capture in progress (rusty_cuda_graph_begin .. _end)
     bool capturing = false;
     uint64_t launches_at_capture = 0;
