@@ -319,7 +319,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "desc": desc, "batch_rows": M, "linears_per_step": stack.num_linears(),
-                   "weights": "int8 [out,in], f32 scale per output row", "activations": "f32 in, f32 out, fp32 accumulate",
+                   "weights": "int8 [out,in], f32 scale per output row; q|k|v and gate|up stored back to back and run as one Linear each", "activations": "f32 in, f32 out, fp32 accumulate",
                    "parallelism": "1 GPU" if world == 1 else f"output-feature shards x{world} + all-gather",
                    "l2": "inputs larger than L2: each step streams %.2f GB of weights per GPU" % (stack.weight_bytes() / 1e9),
                    "kernels": runner.plans(), "layers": stack.layers},

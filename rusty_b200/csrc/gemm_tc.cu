@@ -89,6 +89,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         }
     }
 }
+// Programmatic dependent launch: let the next kernel in the stream start its
+// prologue now / wait until everything earlier in the stream has finished and
+// its writes are visible.  Both are no-ops for a kernel launched the plain way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -180,6 +186,8 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
     __shared__ float red[8];
     __shared__ float s_scale;
     const int tid = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();  // x may come from the previous kernel, and that kernel may still be reading the digit planes
     if (m >= M) {
         for (int k = tid * 4; k < K; k += 256 * 4)
 #pragma unroll
@@ -237,7 +245,7 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
 struct TcParams {
     const float* scales;     // [N]
     const float* row_factor; // [Mpad]: 1/s_m * 128^-(D-1)
-    int32_t* part;           // partial sums of tiles cut across CTAs: [2*grid slots][D*Mpad][128]
+    int32_t* part;           // sums of tiles cut across CTAs: [sk_tiles][Mpad/2][128] x 16 bytes (two int64), zero between uses
     unsigned int* counters;  // [tiles] arrivals per cut tile (zero between uses)
     void* y;
     int M, Mpad, D, NB;      // NB = UMMA N = roundup16(D*Mpad)
@@ -316,7 +324,7 @@ __device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, 
 #define DBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
 
 template <typename YT>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // carve: [A stages][B stages][barriers]
@@ -324,7 +332,9 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     const int b_stage_bytes = p.NB * BK;
     uint8_t* sA = smem;
     uint8_t* sB = smem + (size_t)p.stages * A_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + (size_t)p.stages * b_stage_bytes);
+    // epilogue staging for the bulk reduce-add of a partial tile: [Mpad/2][128] x 16 bytes
+    int4* stage_red = reinterpret_cast<int4*>(sB + (size_t)p.stages * b_stage_bytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (size_t)p.Mpad * 8 * BM);
     uint64_t* full = bars;                      // [stages]
     uint64_t* empty = bars + p.stages;          // [stages]
     uint64_t* acc_full = bars + 2 * p.stages;   // [2]
@@ -335,6 +345,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) DBG(0);
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -366,16 +377,41 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             bool ok = true;
             Sched sched(p);
             Segment sg;
+            // The weights do not depend on earlier kernels: start streaming them at once.  The digit planes do, so
+            // the first ring-full of stages gets its weight tile now and its digit tile after pdl_wait().
+            int early = 0;           // stages whose weight tile is already in flight
+            int early_kb[8];
+            bool waited = false;
             while (ok && sched.next(sg)) {
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+                    if (!waited && early < p.stages) {
+                        mbar_expect_tx(&full[early], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
+                        tma_load_2d(sA + (size_t)early * A_STAGE_BYTES, &map_w, kb * BK, sg.t * BM, &full[early], pol_w);
+                        early_kb[early] = kb;
+                        ++early;
+                        ++issued;
+                        if (issued == 1) DBG(2);
+                        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
+                    if (!waited) {
+                        pdl_wait();
+                        for (int e = 0; e < early; ++e)
+                            tma_load_2d(sB + (size_t)e * b_stage_bytes, &map_x, early_kb[e] * BK, 0, &full[e], pol_x);
+                        waited = true;
+                    }
                     if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                     mbar_expect_tx(&full[stage], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
                     tma_load_2d(sA + (size_t)stage * A_STAGE_BYTES, &map_w, kb * BK, sg.t * BM, &full[stage], pol_w);
                     tma_load_2d(sB + (size_t)stage * b_stage_bytes, &map_x, kb * BK, 0, &full[stage], pol_x);
                     ++issued;
-                    if (issued == 1) DBG(2);
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
+            }
+            if (!waited) {  // fewer k-blocks than ring slots
+                pdl_wait();
+                for (int e = 0; e < early; ++e)
+                    tma_load_2d(sB + (size_t)e * b_stage_bytes, &map_x, early_kb[e] * BK, 0, &full[e], pol_x);
             }
             DBG(3);
             if (!ok) {
@@ -426,6 +462,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const int r = q * 32 + lane;            // row inside the tile
         YT* y = reinterpret_cast<YT*>(p.y);
         const int ncol = p.D * p.Mpad;          // accumulator columns in use
+        pdl_wait();                             // y, the parked partials and the counters belong to earlier kernels until now
         bool ok = true;
         Sched sched(p);
         Segment sg;
@@ -462,26 +499,49 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[ab]);
             } else {
-                // this CTA's piece of a shared tile: park the partial sums.  Layout per slot:
-                // [m/4][d][row][4 consecutive m] so a thread moves 16 bytes and a warp 512 contiguous bytes.
-                int4* mine = reinterpret_cast<int4*>(p.part) + (size_t)sg.slot * (ncol / 4) * BM;
-                for (int d = 0; d < p.D; ++d)
-                    for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
-                        int32_t c[8];
-                        tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c);
-                        tmem_ld_wait();
-                        const int mg = m0 / 4;
-                        __stcg(mine + (size_t)(mg * p.D + d) * BM + r, make_int4(c[0], c[1], c[2], c[3]));
-                        __stcg(mine + (size_t)((mg + 1) * p.D + d) * BM + r, make_int4(c[4], c[5], c[6], c[7]));
+                // This CTA's piece of a shared tile: fold the digit planes into one exact 64-bit integer per output,
+                // stage the piece in shared memory ([m/2][row] x 16 bytes) and add it into the tile's sum in global
+                // memory with ONE bulk reduce (cp.reduce.async.bulk ... add.u64: the adds happen in L2 at line rate).
+                for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
+                    int32_t c[4][8];
+#pragma unroll
+                    for (int d = 0; d < 4; ++d)
+                        if (d < p.D) tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c[d]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        long long a0 = c[0][2 * h], a1 = c[0][2 * h + 1];
+#pragma unroll
+                        for (int d = 1; d < 4; ++d)
+                            if (d < p.D) {
+                                a0 = a0 * 128 + c[d][2 * h];
+                                a1 = a1 * 128 + c[d][2 * h + 1];
+                            }
+                        if (!row_ok) a0 = a1 = 0;
+                        int4 v;
+                        v.x = (int)(a0 & 0xffffffffll);
+                        v.y = (int)(a0 >> 32);
+                        v.z = (int)(a1 & 0xffffffffll);
+                        v.w = (int)(a1 >> 32);
+                        stage_red[(size_t)(m0 / 2 + h) * BM + r] = v;
                     }
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[ab]);
                 if (threadIdx.x == 64) DBG(7 + 4 * (i & 1));
-                // the last CTA to arrive for this row tile adds the pieces (integers: any order, same bits)
-                __threadfence();
+                const int lt = sg.t - p.dp_tiles;
+                int4* tile_sum = reinterpret_cast<int4*>(p.part) + (size_t)lt * (p.Mpad / 2) * BM;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // staged values -> visible to the bulk-copy engine
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (threadIdx.x == 64) {
+                    const uint32_t bytes = (uint32_t)(p.Mpad * 8 * BM);
+                    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.u64 [%0], [%1], %2;" ::"l"(tile_sum),
+                                 "r"(smem_u32(stage_red)), "r"(bytes)
+                                 : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the adds have been performed
+                    __threadfence();
                     unsigned prev = atomicAdd(p.counters + sg.t, 1u);
                     *reinterpret_cast<volatile int*>(last_flag) = (prev == (unsigned)(sg.nseg - 1)) ? 1 : 0;
                 }
@@ -489,51 +549,23 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 const bool last = *reinterpret_cast<volatile int*>(last_flag) != 0;
                 if (threadIdx.x == 64) DBG(8 + 4 * (i & 1));
                 if (last) {
+                    // every piece has been added: turn the sums into y and leave zeros behind for the next use
                     __threadfence();
-                    if (row_ok) {
-                        const float sc = __ldg(p.scales + n);
-                        const int lt = sg.t - p.dp_tiles;
-                        // four activation rows at a time: up to 8 pieces x D digit planes of 16-byte loads in flight
-                        for (int mg = 0; mg * 4 < p.M; ++mg) {
-                            int4 v[4];
+                    const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+                    for (int mp0 = 0; mp0 * 2 < p.Mpad; mp0 += 8) {
+                        int4 ld[8];
 #pragma unroll
-                            for (int d = 0; d < 4; ++d) v[d] = make_int4(0, 0, 0, 0);
-                            for (int s0 = 0; s0 < sg.nseg; s0 += 8) {
-                                int4 ld[8][4];
+                        for (int h = 0; h < 8; ++h)
+                            ld[h] = (mp0 + h) * 2 < p.Mpad ? __ldcg(tile_sum + (size_t)(mp0 + h) * BM + r) : make_int4(0, 0, 0, 0);
 #pragma unroll
-                                for (int u = 0; u < 8; ++u) {
-                                    const int cta = sg.first_cta + s0 + u;
-                                    const int slot = 2 * cta + (cta * p.sk_per_cta >= lt * p.kb_total ? 0 : 1);
-                                    const int4* src = reinterpret_cast<const int4*>(p.part) + (size_t)slot * (ncol / 4) * BM + r;
+                        for (int h = 0; h < 8; ++h)
+                            if ((mp0 + h) * 2 < p.Mpad) __stcg(tile_sum + (size_t)(mp0 + h) * BM + r, make_int4(0, 0, 0, 0));
+                        if (row_ok) {
 #pragma unroll
-                                    for (int d = 0; d < 4; ++d)
-                                        ld[u][d] = (s0 + u < sg.nseg && d < p.D) ? __ldcg(src + (size_t)(mg * p.D + d) * BM)
-                                                                                 : make_int4(0, 0, 0, 0);
-                                }
-#pragma unroll
-                                for (int u = 0; u < 8; ++u)
-#pragma unroll
-                                    for (int d = 0; d < 4; ++d) {
-                                        v[d].x += ld[u][d].x;
-                                        v[d].y += ld[u][d].y;
-                                        v[d].z += ld[u][d].z;
-                                        v[d].w += ld[u][d].w;
-                                    }
-                            }
-#pragma unroll
-                            for (int mm = 0; mm < 4; ++mm) {
-                                const int m = mg * 4 + mm;
-                                if (m < p.M) {
-                                    const int32_t c0 = mm == 0 ? v[0].x : mm == 1 ? v[0].y : mm == 2 ? v[0].z : v[0].w;
-                                    long long acc = c0;
-#pragma unroll
-                                    for (int d = 1; d < 4; ++d)
-                                        if (d < p.D) {
-                                            const int32_t cd = mm == 0 ? v[d].x : mm == 1 ? v[d].y : mm == 2 ? v[d].z : v[d].w;
-                                            acc = acc * 128 + cd;
-                                        }
-                                    finalize_store<YT>(p, y, n, m, acc, sc);
-                                }
+                            for (int h = 0; h < 8; ++h) {
+                                const int m = (mp0 + h) * 2;
+                                if (m < p.M) finalize_store<YT>(p, y, n, m, ((long long)ld[h].y << 32) | (unsigned int)ld[h].x, sc);
+                                if (m + 1 < p.M) finalize_store<YT>(p, y, n, m + 1, ((long long)ld[h].w << 32) | (unsigned int)ld[h].z, sc);
                             }
                         }
                     }
@@ -601,12 +633,29 @@ int pick_digits(int x_dtype, uint32_t rows) {
     return (x_dtype == RUSTY_CUDA_F32 && mpad * 4 <= 64) ? 4 : 3;
 }
 
+// Launch with programmatic stream serialisation: the kernel may begin while its
+// predecessor in the stream is still draining; it orders itself with
+// griddepcontrol.wait.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename XT>
-void launch_digitize(rusty_cuda_ctx* ctx, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D) {
+cudaError_t launch_digitize(rusty_cuda_ctx* ctx, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D) {
     if (D == 4)
-        digitize_x_kernel<XT, 4><<<Mpad, 256, 0, ctx->stream>>>((const XT*)x, xq, inv_s, M, Mpad, K);
-    else
-        digitize_x_kernel<XT, 3><<<Mpad, 256, 0, ctx->stream>>>((const XT*)x, xq, inv_s, M, Mpad, K);
+        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K);
+    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K);
 }
 
 }  // namespace
@@ -669,10 +718,9 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     if ((size_t)D * Mpad * a.K > WS_XQ_BYTES)
         return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: %d digit rows x K=%u exceed the workspace", D * Mpad, a.K);
 
-    if (a.x_dtype == RUSTY_CUDA_BF16)
-        launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D);
-    else
-        launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D);
+    cudaError_t le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D)
+                                                  : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D);
+    if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
     int rc = after_launch(ctx, "digitize_x");
     if (rc) return rc;
 
@@ -704,8 +752,15 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
         const int sk_work = p.sk_tiles * p.kb_total;
         p.sk_per_cta = (sk_work + grid - 1) / grid;
         if (p.sk_per_cta < 4) p.sk_per_cta = 4;
+        // Prefer cuts that line up with tile borders (every CTA then holds one piece and a tile has exactly
+        // `ways` pieces) when that keeps at least 85% of the SMs busy.
+        const int ways = grid / p.sk_tiles;
+        if (ways >= 1) {
+            const int aligned = (p.kb_total + ways - 1) / ways;
+            if (aligned >= 4 && (long long)p.sk_per_cta * 100 >= (long long)aligned * 85) p.sk_per_cta = aligned;
+        }
         p.sk_ctas = (sk_work + p.sk_per_cta - 1) / p.sk_per_cta;
-        const size_t need = (size_t)2 * grid * D * Mpad * BM * 4;
+        const size_t need = (size_t)p.sk_tiles * Mpad * BM * 8;
         if (need > WS_ACC_BYTES || (size_t)p.tiles * 4 > WS_CNT_BYTES) {
             p.dp_tiles = p.tiles;  // no room to park partial tiles: whole tiles only
             p.sk_tiles = 0;
@@ -725,12 +780,17 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     while (cols < (uint32_t)(2 * NB)) cols <<= 1;
     p.tmem_cols = cols;
     const int b_stage = NB * BK;
-    const size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
-    int stages = (int)((budget - 1024 - 256) / (size_t)(A_STAGE_BYTES + b_stage));
+    // Half of the SM's shared memory at most, so that the next kernel's CTA can move in beside this one and
+    // prefetch its weights while this one drains (RUSTY_TC_FULL_SMEM=1: take it all, 8 stages).
+    static const bool full_smem = getenv("RUSTY_TC_FULL_SMEM") != nullptr;
+    size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
+    if (!full_smem && NB <= 32) budget = budget / 2 - 1024;  // narrow batches: 5 stages are enough to cover HBM latency
+    const size_t red_bytes = (size_t)Mpad * 8 * BM;  // epilogue staging of a partial tile
+    int stages = budget > red_bytes + 2048 ? (int)((budget - 1024 - 256 - red_bytes) / (size_t)(A_STAGE_BYTES + b_stage)) : 0;
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: tile does not fit shared memory");
     p.stages = stages;
-    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + (size_t)(2 * stages + 4) * 8 + 64;
+    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 64;
 
     CUtensorMap map_w, map_x;
     if (!make_map_u8(&map_w, a.w, a.N, a.K, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
@@ -747,7 +807,8 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
         if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_i8_tc: cudaFuncSetAttribute");
         cur = smem;
     }
-    kern<<<grid, TC_THREADS, smem, ctx->stream>>>(map_w, map_x, p);
+    le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, ctx->stream, map_w, map_x, p);
+    if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_i8_tc");
     return after_launch(ctx, "qlinear_i8_tc");
 }
 

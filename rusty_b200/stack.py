@@ -29,7 +29,7 @@ from .workloads import StackShape
 class LinearStack:
     def __init__(self, ctx: CudaContext, shape: StackShape, M: int, x_dtype: DType = DType.FP32,
                  y_dtype: DType = DType.FP32, seed: int = 0, rank: int = 0, world: int = 1,
-                 layers: Optional[int] = None):
+                 layers: Optional[int] = None, fuse: bool = True):
         self.ctx, self.shape, self.M = ctx, shape, M
         self.x_dtype, self.y_dtype = x_dtype, y_dtype
         self.rank, self.world = rank, world
@@ -48,19 +48,33 @@ class LinearStack:
                 host_w[(n, k)] = (q, s)
             return host_w[(n, k)]
 
+        # Projections that read the same activation are stored back to back and run as ONE Linear
+        # (q|k|v -> [M, q+2kv], gate|up -> [M, 2*ffn]); a shard keeps its slice of each member.
+        self.fuse = fuse
+        if fuse:
+            groups = [("qkv", ["q", "k", "v"]), ("o", ["o"]), ("gate_up", ["gate", "up"]), ("down", ["down"])]
+        else:
+            groups = [(p, [p]) for p, _n, _k in shape.per_layer()]
+        dims = {p: (n, k) for p, n, k in shape.per_layer()}
         linears = []
         for l in range(self.layers):
-            linears += [(f"l{l}.{p}", n, k) for p, n, k in shape.per_layer()]
-        linears.append(("lm_head", shape.vocab, shape.d))
-        for name, n, k in linears:
-            assert n % world == 0, f"{name}: N={n} not divisible by {world} ranks"
-            nl = n // world
-            q, s = draw(n, k)
-            lo = rank * nl
-            self.qls.append(QLinear.from_host(ctx, q[lo:lo + nl], s[lo:lo + nl]))
+            linears += [(f"l{l}.{g}", [dims[m] for m in members]) for g, members in groups]
+        linears.append(("lm_head", [(shape.vocab, shape.d)]))
+        for name, members in linears:
+            k = members[0][1]
+            qs, ss = [], []
+            for n, kk in members:
+                assert kk == k and n % world == 0, f"{name}: N={n} not divisible by {world} ranks"
+                nl = n // world
+                q, s = draw(n, k)
+                qs.append(q[rank * nl:(rank + 1) * nl])
+                ss.append(s[rank * nl:(rank + 1) * nl])
+            qcat = qs[0] if len(qs) == 1 else np.concatenate(qs, axis=0)
+            scat = ss[0] if len(ss) == 1 else np.concatenate(ss)
+            self.qls.append(QLinear.from_host(ctx, qcat, scat))
             self.names.append(name)
-            self.dims.append((nl, k))
-            self.full_n.append(n)
+            self.dims.append((qcat.shape[0], k))
+            self.full_n.append(sum(n for n, _ in members))
         # activations: one fixed input per distinct K, N(0,1) like the benchmark's x
         self.inputs: Dict[int, UnifiedTensor] = {}
         self.host_inputs: Dict[int, np.ndarray] = {}
