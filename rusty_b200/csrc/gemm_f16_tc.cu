@@ -1,0 +1,320 @@
+// Prefill GEMM over int8 weights on tcgen05 / TMEM with bf16 operands.
+//
+// Replaces, for many activation rows at once, the reference's "dequantise once
+// at load, f32 tiled matmul per forward" (rusty-loader/src/lib.rs:155-218,
+// rusty-backend/src/kernels.wgsl:16-54, :234-242):
+//     y[m,n] = scale[n] * sum_k x[m,k] * q[n,k]        x bf16, q int8, fp32 accumulation
+//
+// The weight rows are the M side of the MMA (128 rows per tile), the activation
+// rows the N side (up to 256 per tile), so the accumulator tile is y^T.
+//   * int8 weight tiles (128 rows x 128 k, 16 KB) arrive by TMA with the 128-byte
+//     swizzle; four converter warps (one thread per weight row) read their row
+//     conflict-free, turn bytes into bf16 pairs (byte-permute into the mantissa of
+//     2^23, subtract, packed convert: exact since |q| <= 128), and write them
+//     straight into TENSOR MEMORY with tcgen05.st — the A operand never goes back
+//     through shared memory;
+//   * bf16 activation tiles (up to 256 rows x 64 k) arrive by TMA as the B operand;
+//   * one elected thread issues tcgen05.mma kind::f16 (A bf16 from TMEM, B bf16
+//     from shared memory, fp32 accumulators in TMEM); bf16 x bf16 products are
+//     exact in the fp32 accumulate, so the only rounding is the summation;
+//   * four epilogue warps read the accumulators, apply the per-row weight scale and
+//     store y (bf16 or f32) while the converters already work on the next tile.
+// Persistent CTAs, one per SM; every mbarrier wait is bounded.
+#include <cstdlib>
+#include <cstring>
+
+#include "tc_common.cuh"
+
+using namespace rusty_tc;
+
+namespace {
+
+constexpr int BM = 128;          // weight rows per tile (UMMA M)
+constexpr int WK = 128;          // k per weight stage (bytes per row)
+constexpr int XK = 64;           // k per activation stage (128 bytes of bf16 per row)
+constexpr int W_STAGES = 3;
+constexpr int A_BUFS = 3;        // converted-weight buffers in tensor memory, 64 columns each
+constexpr int A_COLS = WK / 2;   // two 16-bit values per 32-bit column
+constexpr int D_COLS = 256;      // accumulator columns reserved
+constexpr int F16_THREADS = 320; // producer, MMA, 4 converter, 4 epilogue warps
+constexpr int W_STAGE_BYTES = BM * WK;
+
+struct F16Params {
+    const float* scales;  // [N]
+    void* y;
+    int Mx, N, K;
+    int BN;               // activation rows per tile (multiple of 16, <= 256)
+    int tiles_w, tiles_n, nws;  // weight-row tiles, activation-row tiles, weight stages per tile
+    int x_stages;
+    int ldy, y_col0;
+    uint32_t idesc;
+    rusty_cuda_dev_status* status;
+};
+
+template <typename T>
+__device__ __forceinline__ void store_y(T* p, float v);
+template <>
+__device__ __forceinline__ void store_y<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// 16 int8 (one 128-bit word) -> 8 registers of packed bf16 pairs (low half = even k).
+// u = q ^ 0x80 is q + 128; dropping u into the low mantissa byte of 2^23 and subtracting 2^23 + 128 leaves q
+// exactly as an f32, and |q| <= 128 fits bf16's 8 significant bits, so the packed conversion is exact too.
+__device__ __forceinline__ void int8x16_to_bf16x2(const uint4& w, uint32_t* out) {
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t u = words[i] ^ 0x80808080u;
+        const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+        const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+        const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+        const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+        __nv_bfloat162 a = __floats2bfloat162_rn(f0, f1);
+        __nv_bfloat162 b = __floats2bfloat162_rn(f2, f3);
+        out[2 * i] = *reinterpret_cast<uint32_t*>(&a);
+        out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
+    }
+}
+
+template <typename YT>
+__global__ void __launch_bounds__(F16_THREADS, 1)
+qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const F16Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int x_stage_bytes = p.BN * XK * 2;
+    uint8_t* sW = smem;
+    uint8_t* sX = smem + (size_t)W_STAGES * W_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sX + (size_t)p.x_stages * x_stage_bytes);
+    uint64_t* w_full = bars;                   // [W_STAGES]
+    uint64_t* w_empty = w_full + W_STAGES;     // [W_STAGES]
+    uint64_t* a_full = w_empty + W_STAGES;     // [A_BUFS]
+    uint64_t* a_empty = a_full + A_BUFS;       // [A_BUFS]
+    uint64_t* d_full = a_empty + A_BUFS;       // [1]
+    uint64_t* d_empty = d_full + 1;            // [1]
+    uint64_t* x_full = d_empty + 1;            // [x_stages]
+    uint64_t* x_empty = x_full + p.x_stages;   // [x_stages]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_empty + p.x_stages);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int units = p.tiles_w * p.tiles_n;
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < W_STAGES; ++s) {
+            mbar_init(&w_full[s], 1);
+            mbar_init(&w_empty[s], 4);
+        }
+        for (int s = 0; s < A_BUFS; ++s) {
+            mbar_init(&a_full[s], 4);
+            mbar_init(&a_empty[s], 1);
+        }
+        mbar_init(d_full, 1);
+        mbar_init(d_empty, 4);
+        for (int s = 0; s < p.x_stages; ++s) {
+            mbar_init(&x_full[s], 1);
+            mbar_init(&x_empty[s], 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a0 = tmem_base + D_COLS;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+            int ws = 0, xs = 0;
+            uint32_t wph = 0, xph = 0;
+            bool ok = true, waited = false;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const int t = u % p.tiles_w, j = u / p.tiles_w;
+                for (int s = 0; s < p.nws && ok; ++s) {
+                    if (!mbar_wait(&w_empty[ws], wph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+                    mbar_expect_tx(&w_full[ws], (uint32_t)W_STAGE_BYTES);
+                    tma_load_2d(sW + (size_t)ws * W_STAGE_BYTES, &map_w, s * WK, t * BM, &w_full[ws], pol_w);
+                    if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
+                    if (!waited) {  // the weights never depend on earlier kernels; the activations may
+                        pdl_wait();
+                        waited = true;
+                    }
+                    for (int h = 0; h < WK / XK; ++h) {
+                        if (!mbar_wait(&x_empty[xs], xph ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
+                        mbar_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
+                        tma_load_2d(sX + (size_t)xs * x_stage_bytes, &map_x, s * WK + h * XK, j * p.BN, &x_full[xs], pol_x);
+                        if (++xs == p.x_stages) { xs = 0; xph ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int ab = 0, xs = 0;
+            uint32_t aph = 0, xph = 0;
+            bool ok = true;
+            int i = 0;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++i) {
+                if (!mbar_wait(d_empty, ((uint32_t)i & 1u) ^ 1u, abort_flag, p.status, 13)) { ok = false; break; }
+                tc_fence_after();
+                for (int s = 0; s < p.nws && ok; ++s) {
+                    if (!mbar_wait(&a_full[ab], aph, abort_flag, p.status, 14)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_tmem = tmem_a0 + (uint32_t)(ab * A_COLS);
+                    for (int h = 0; h < WK / XK; ++h) {
+                        if (!mbar_wait(&x_full[xs], xph, abort_flag, p.status, 15)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint64_t db = make_smem_desc(smem_u32(sX + (size_t)xs * x_stage_bytes));
+#pragma unroll
+                        for (int k16 = 0; k16 < XK / 16; ++k16)
+                            umma_f16_ts(tmem_base, a_tmem + (uint32_t)((h * (XK / 16) + k16) * 8), db + (uint64_t)(2 * k16), p.idesc,
+                                        (s > 0 || h > 0 || k16 > 0) ? 1u : 0u);
+                        umma_commit(&x_empty[xs]);
+                        if (++xs == p.x_stages) { xs = 0; xph ^= 1u; }
+                    }
+                    umma_commit(&a_empty[ab]);
+                    if (++ab == A_BUFS) { ab = 0; aph ^= 1u; }
+                }
+                if (ok) umma_commit(d_full);
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------ converters --------------------------------
+        const int q = warp & 3;
+        const int r = q * 32 + lane;  // weight row inside the tile = TMEM lane
+        int ws = 0, ab = 0;
+        uint32_t wph = 0, aph = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            for (int s = 0; s < p.nws && ok; ++s) {
+                if (!mbar_wait(&w_full[ws], wph, abort_flag, p.status, 16)) { ok = false; break; }
+                // row r of the swizzled tile: logical 16-byte chunk c sits at physical chunk c ^ (r & 7)
+                const uint4* row = reinterpret_cast<const uint4*>(sW + (size_t)ws * W_STAGE_BYTES + (size_t)r * WK);
+                uint4 raw[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) raw[c] = row[c ^ (r & 7)];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&w_empty[ws]);  // the tile is in registers: the slot may be refilled
+                if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
+                uint32_t lo[32], hi[32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[c], lo + 8 * c);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[4 + c], hi + 8 * c);
+                if (!mbar_wait(&a_empty[ab], aph ^ 1u, abort_flag, p.status, 17)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_tmem = tmem_a0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * A_COLS);
+                tmem_st32(a_tmem, lo);
+                tmem_st32(a_tmem + 32, hi);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[ab]);
+                if (++ab == A_BUFS) { ab = 0; aph ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        YT* y = reinterpret_cast<YT*>(p.y);
+        pdl_wait();
+        bool ok = true;
+        int i = 0;
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++i) {
+            const int t = u % p.tiles_w, j = u / p.tiles_w;
+            const int n = t * BM + r;
+            const bool row_ok = n < p.N;
+            const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+            if (!mbar_wait(d_full, (uint32_t)i & 1u, abort_flag, p.status, 18)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+            for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(taddr + (uint32_t)c0, v);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int m = j * p.BN + c0 + e;
+                        if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, __uint_as_float(v[e]) * sc);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(d_empty);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace
+
+namespace rusty {
+
+bool f16tc_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
+    if (!encode_tiled_fn()) return false;
+    if (a.layout != RUSTY_CUDA_LAYOUT_NK || a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
+    if (a.x_dtype != RUSTY_CUDA_BF16) return false;
+    if (a.K % 16 != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(a.w) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return false;
+    return true;
+}
+
+int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
+    F16Params p{};
+    p.scales = a.scales;
+    p.y = a.y;
+    p.Mx = (int)a.M;
+    p.N = (int)a.N;
+    p.K = (int)a.K;
+    p.BN = a.M >= 256 ? 256 : (int)((a.M + 15) / 16 * 16);
+    p.tiles_w = (p.N + BM - 1) / BM;
+    p.tiles_n = (p.Mx + p.BN - 1) / p.BN;
+    p.nws = (p.K + WK - 1) / WK;
+    p.ldy = (int)a.ldy;
+    p.y_col0 = (int)a.y_col0;
+    p.status = ctx->status_dev;
+    // bf16 A x bf16 B -> f32: c_format=F32(1)@4, a_format=BF16(1)@7, b_format=BF16(1)@10, N>>3 @17, M>>4 @24
+    p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    const size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
+    const size_t x_stage = (size_t)p.BN * XK * 2;
+    int xs = (int)((budget - 1024 - 512 - (size_t)W_STAGES * W_STAGE_BYTES) / x_stage);
+    if (xs > 8) xs = 8;
+    if (xs < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "f16 tensor-core path: tile does not fit shared memory");
+    p.x_stages = xs;
+    const size_t smem = 1024 + (size_t)W_STAGES * W_STAGE_BYTES + (size_t)xs * x_stage + (size_t)(2 * W_STAGES + 2 * A_BUFS + 2 + 2 * xs) * 8 + 64;
+
+    CUtensorMap map_w, map_x;
+    if (!make_map_u8(&map_w, a.w, a.N, a.K, BM) || !make_map_bf16(&map_x, a.x, a.M, a.K, (uint32_t)p.BN))
+        return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "f16 tensor-core path: cuTensorMapEncodeTiled failed");
+    const int units = p.tiles_w * p.tiles_n;
+    const int grid = units < ctx->sm_count ? units : ctx->sm_count;
+    const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
+    auto kern = yb ? qlinear_f16_tc_kernel<__nv_bfloat16> : qlinear_f16_tc_kernel<float>;
+    static size_t smem_set[2][16] = {{0}};
+    size_t& cur = smem_set[yb ? 1 : 0][ctx->device & 15];
+    if (smem > cur) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_f16_tc: cudaFuncSetAttribute");
+        cur = smem;
+    }
+    cudaError_t le = launch_pdl(kern, dim3(grid), dim3(F16_THREADS), smem, ctx->stream, map_w, map_x, p);
+    if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_f16_tc");
+    return after_launch(ctx, "qlinear_f16_tc");
+}
+
+}  // namespace rusty

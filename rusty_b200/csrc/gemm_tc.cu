@@ -29,12 +29,12 @@
 //             red.global and let the last CTA of a tile finalise.
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the kernel
 // raises the context's timeout flag, drains and frees its TMEM.
-#include <cuda.h>
-
 #include <cstdlib>
 #include <cstring>
 
-#include "internal.h"
+#include "tc_common.cuh"
+
+using namespace rusty_tc;
 
 namespace {
 
@@ -44,121 +44,6 @@ constexpr int UMMA_K = 32;         // k-elements per tcgen05.mma kind::i8
 constexpr int TC_THREADS = 192;    // producer warp, MMA warp, 4 epilogue warps
 constexpr int EPI_THREADS = 128;
 constexpr int A_STAGE_BYTES = BM * BK;
-constexpr long long WAIT_LIMIT_CYCLES = 8000000000ll;  // ~4 s of SM clock
-
-// ----------------------------------------------------------------------------
-// PTX wrappers
-// ----------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false (after raising the status word) when the limit
-// expires or another role of this CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          rusty_cuda_dev_status* status, unsigned site) {
-    long long t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 255u) == 255u) {
-            if (*abort_flag) return false;
-            if (t0 == 0) t0 = clock64();
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                if (atomicExch(&status->timeout_flag, 1u) == 0u) status->timeout_where = site;
-                return false;
-            }
-        }
-    }
-}
-// Programmatic dependent launch: let the next kernel in the stream start its
-// prologue now / wait until everything earlier in the stream has finished and
-// its writes are visible.  Both are no-ops for a kernel launched the plain way.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint64_t* bar,
-                                            uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4}], [%2], %5;"
-        :
-        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
-        : "memory");
-}
-__device__ __forceinline__ uint64_t policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ uint64_t policy_evict_last() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(ncols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]^T, int8 x int8 -> int32
-__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        :
-        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// mbarrier arrives once every tcgen05.mma issued so far by this thread has completed
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t addr, int32_t (&v)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes,
-// 8-row groups 1024 bytes apart (descriptor version 1 = Blackwell).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address
-    d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                         // version
-    d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
-    return d;
-}
 
 template <typename T>
 __device__ __forceinline__ void store_y(T* p, float v);
@@ -590,37 +475,6 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 // ----------------------------------------------------------------------------
 // Host side
 // ----------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// [rows, K] uint8 row-major, boxes of box_rows x 128 bytes, 128-byte swizzle, zero fill outside.
-bool make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows, CUtensorMapL2promotion promo) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {K, rows};
-    cuuint64_t strides[1] = {K};
-    cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
-}
-
 constexpr size_t WS_XQ_BYTES = 24u << 20;      // digit planes: up to 256 rows x K <= 96K
 constexpr size_t WS_INVS_BYTES = 4096;
 constexpr size_t WS_ACC_BYTES = 48u << 20;     // split-K partial sums
@@ -631,24 +485,6 @@ int pick_digits(int x_dtype, uint32_t rows) {
     // 4 digits (28 bits under the row maximum) while the B operand stays narrow, else 3 (21 bits).
     uint32_t mpad = (rows + 7) / 8 * 8;
     return (x_dtype == RUSTY_CUDA_F32 && mpad * 4 <= 64) ? 4 : 3;
-}
-
-// Launch with programmatic stream serialisation: the kernel may begin while its
-// predecessor in the stream is still draining; it orders itself with
-// griddepcontrol.wait.
-template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 template <typename XT>
@@ -793,8 +629,8 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 64;
 
     CUtensorMap map_w, map_x;
-    if (!make_map_u8(&map_w, a.w, a.N, a.K, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
-        !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, a.K, (uint32_t)NB, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+    if (!make_map_u8(&map_w, a.w, a.N, a.K, BM) ||
+        !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, a.K, (uint32_t)NB))
         return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "tensor-core path: cuTensorMapEncodeTiled failed");
 
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;

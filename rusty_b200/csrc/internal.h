@@ -137,6 +137,11 @@ int tc_workspace_reserve(rusty_cuda_ctx* ctx);
 void tc_workspace_release(rusty_cuda_ctx* ctx);
 int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 
+// Prefill path: int8 -> fp16 into tensor memory, bf16 activations (tcgen05 kind::f16).
+bool f16tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
+int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
+uint32_t f16tc_min_rows();
+
 const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 // Forward into columns [y_col0, y_col0 + N) of a y whose rows are ldy elements apart.
 int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,

@@ -3,6 +3,7 @@
 // Stands in for the reference's Linear::forward over a quantised weight
 // (rusty-graph/src/lib.rs:69-70), which there is "dequantise once at load
 // (rusty-loader/src/lib.rs:155-218), then an f32 matmul per call".
+#include <cstdlib>
 #include <cstring>
 
 #include "internal.h"
@@ -19,6 +20,17 @@ static size_t dtype_size(int dt) {
     }
 }
 
+uint32_t f16tc_min_rows() {
+    // RUSTY_F16_MIN_ROWS overrides the batch size from which bf16 activations take the fp16/bf16 MMA kernel (tuning aid).
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RUSTY_F16_MIN_ROWS");
+        v = e ? atoi(e) : 65;
+        if (v < 1) v = 1;
+    }
+    return (uint32_t)v;
+}
+
 // Which kernel a forward of this shape runs.
 const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype) {
     QLinearArgs a{};
@@ -29,6 +41,7 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
     a.x_dtype = x_dtype;
     a.y_dtype = y_dtype;
     a.M = M;
+    if (f16tc_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16";
     if (tc_supported(ql->ctx, a) && M >= tc_min_rows()) return "tcgen05";
     if (gemv_supported(ql->ctx, a)) return "gemv";
     return "unsupported";
@@ -68,6 +81,7 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
     a.ldy = ldy;
     a.y_col0 = y_col0;
     DeviceGuard g(ctx->device);
+    if (f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
     if (tc_supported(ctx, a) && M >= tc_min_rows()) return launch_tc(ctx, a);
     if (gemv_supported(ctx, a)) return launch_gemv(ctx, a);
     return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED,

@@ -269,3 +269,25 @@ def test_tc_nonfinite_activation_poisons_its_row_only(ctx, engine):
     x[2, 5] = np.nan
     y = _forward(ctx, engine, QLinear.from_host(ctx, q, s), x)
     assert np.isnan(y[2]).all() and np.isfinite(np.delete(y, 2, axis=0)).all()
+
+
+# ---- prefill path: fp16 weights in tensor memory x bf16 activations ----
+
+@pytest.mark.parametrize("M,K,N", [(128, 512, 256), (512, 4096, 1024), (200, 1024, 130), (96, 4096, 4096), (300, 80, 24),
+                                   (512, 4096, 11008)])
+def test_prefill_f16_shapes(ctx, engine, oracle, M, K, N):
+    x, q, s = sym_row_linear(5 * K + N + M, M, K, N)
+    xb = bf16_bits_to_f32(f32_to_bf16_bits(x))
+    ql = QLinear.from_host(ctx, q, s)
+    assert ql.plan(M, DType.BF16, DType.BF16) == "tcgen05_f16"
+    got32 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.FP32)
+    got16 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.BF16)
+    ctx.sync()
+    wf = oracle.dequantize_rowscale(q, s)
+    rows = slice(None) if M * N * K < 3e9 else [0, 1, M // 2, M - 1]
+    ref = oracle.matmul_bt(xb[rows], wf, mt=True)
+    assert rel_err(got32[rows], ref) <= TOL_FP32         # products are exact, accumulation is fp32
+    assert rel_err(got16[rows], ref) <= TOL_BF16
+    exact = xb.astype(np.float64) @ wf.astype(np.float64).T
+    assert rel_err(got32, exact) <= TOL_FP32
+    assert np.array_equal(f32_to_bf16_bits(got16), f32_to_bf16_bits(got32))
