@@ -205,6 +205,30 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t 
                                                     const rusty_cuda_buf* const* xs, int x_dtype, uint32_t M,
                                                     rusty_cuda_buf* const* ys, int y_dtype);
 
+/* ---- output-feature sharding across the GPUs of one node -------------------
+ * No counterpart in the reference (single device, no collective anywhere); this
+ * is Linear::forward (rusty-graph/src/lib.rs:69-70) for a weight whose rows
+ * [r*N/G, (r+1)*N/G) live on rank r.  x is replicated; every rank receives the
+ * whole y[M,N].  One process per GPU; the 128-byte id comes from rank 0
+ * (rusty_cuda_comm_unique_id) and reaches the others by the launcher's own means. */
+RUSTY_CUDA_API int rusty_cuda_comm_unique_id(void* out128);
+RUSTY_CUDA_API int rusty_cuda_comm_create(rusty_cuda_ctx* ctx, int nranks, int rank, const void* id128,
+                                          rusty_cuda_comm** out);
+RUSTY_CUDA_API int rusty_cuda_comm_destroy(rusty_cuda_comm* comm);
+/* Host-side watchdog hook: reports an asynchronous NCCL error without blocking. */
+RUSTY_CUDA_API int rusty_cuda_comm_check(rusty_cuda_comm* comm);
+/* y_full[M, G*Nl] = all-gather over ranks of x[M,K] . shard^T.  `gather_ws` is a
+ * caller-owned buffer of G*M*Nl elements of y_dtype used for the exchange. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_forward_sharded(rusty_cuda_ctx* ctx, rusty_cuda_comm* comm,
+                                                      const rusty_cuda_qlinear* ql_shard, const rusty_cuda_buf* x,
+                                                      int x_dtype, uint32_t M, rusty_cuda_buf* gather_ws,
+                                                      rusty_cuda_buf* y_full, int y_dtype);
+RUSTY_CUDA_API int rusty_cuda_qlinear_forward_sharded_batch(rusty_cuda_ctx* ctx, rusty_cuda_comm* comm, size_t n,
+                                                            const rusty_cuda_qlinear* const* ql_shards,
+                                                            const rusty_cuda_buf* const* xs, int x_dtype, uint32_t M,
+                                                            rusty_cuda_buf* gather_ws, rusty_cuda_buf* const* ys,
+                                                            int y_dtype);
+
 /* ---- stream capture and timing ---------------------------------------------
  * rusty submits one command buffer per op (lib.rs:4452); a decode step here is
  * hundreds of short kernels, so the sequence can be recorded once into a CUDA

@@ -36,7 +36,8 @@ constexpr int W_STAGES = 3;
 constexpr int A_BUFS = 3;        // converted-weight buffers in tensor memory, 64 columns each
 constexpr int A_COLS = WK / 2;   // two 16-bit values per 32-bit column
 constexpr int D_COLS = 256;      // accumulator columns reserved
-constexpr int F16_THREADS = 320; // producer, MMA, 4 converter, 4 epilogue warps
+constexpr int CONV_WARPS = 8;     // two per TMEM lane quarter, each takes half of a stage's k range
+constexpr int F16_THREADS = 32 * (2 + CONV_WARPS + 4);  // producer, MMA, converter and 4 epilogue warps
 constexpr int W_STAGE_BYTES = BM * WK;
 
 struct F16Params {
@@ -46,8 +47,15 @@ struct F16Params {
     int BN;               // activation rows per tile (multiple of 16, <= 256)
     int tiles_w, tiles_n, nws;  // weight-row tiles, activation-row tiles, weight stages per tile
     int x_stages;
+    // Schedule: units = tiles_w * tiles_n tiles of the output.  The last `sk_units` of them are cut along K
+    // (stream-K): their sk_units*nws weight stages form one linear space dealt out in contiguous runs of
+    // `sk_per_cta` to the first `sk_ctas` CTAs; the other units are taken whole, unit = cta, cta + grid, ...
+    int dp_units, sk_units, sk_per_cta, sk_ctas;
+    float* sums;              // [sk_units][BN/4][128] x float4: f32 sums of cut tiles (zero between uses)
+    unsigned int* counters;   // [sk_units] arrivals per cut tile (zero between uses)
     int ldy, y_col0;
     uint32_t idesc;
+    int dbg_mode;         // tuning aid (RUSTY_F16_DBG): 1 = converters skip their work, 2 = MMA thread issues nothing
     rusty_cuda_dev_status* status;
 };
 
@@ -77,6 +85,50 @@ __device__ __forceinline__ void int8x16_to_bf16x2(const uint4& w, uint32_t* out)
     }
 }
 
+// One piece of work: weight stages [s0, s1) of output tile `u`.  nseg > 1: the tile is shared with other CTAs.
+struct Piece {
+    int u, s0, s1, nseg, lu;
+};
+
+// Every role of the CTA walks the same list of pieces: the stream-K share first, whole tiles after it.
+struct PieceSched {
+    const F16Params& p;
+    int g, g_end, dp_next;
+    __device__ PieceSched(const F16Params& pp) : p(pp) {
+        const int c = blockIdx.x;
+        g = c < p.sk_ctas ? c * p.sk_per_cta : 0;
+        g_end = c < p.sk_ctas ? min(p.sk_units * p.nws, g + p.sk_per_cta) : 0;
+        dp_next = c;
+    }
+    __device__ bool next(Piece& q) {
+        if (g < g_end) {
+            q.lu = g / p.nws;
+            q.u = p.dp_units + q.lu;
+            q.s0 = g % p.nws;
+            q.s1 = min(p.nws, q.s0 + (g_end - g));
+            const int first = (q.lu * p.nws) / p.sk_per_cta;
+            const int last = ((q.lu + 1) * p.nws - 1) / p.sk_per_cta;
+            q.nseg = last - first + 1;
+            g += q.s1 - q.s0;
+            return true;
+        }
+        if (dp_next < p.dp_units) {
+            q.u = dp_next;
+            q.lu = 0;
+            q.s0 = 0;
+            q.s1 = p.nws;
+            q.nseg = 1;
+            dp_next += gridDim.x;
+            return true;
+        }
+        return false;
+    }
+};
+
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 template <typename YT>
 __global__ void __launch_bounds__(F16_THREADS, 1)
 qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const F16Params p) {
@@ -96,18 +148,18 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     uint64_t* x_empty = x_full + p.x_stages;   // [x_stages]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_empty + p.x_stages);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int units = p.tiles_w * p.tiles_n;
     pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < W_STAGES; ++s) {
             mbar_init(&w_full[s], 1);
-            mbar_init(&w_empty[s], 4);
+            mbar_init(&w_empty[s], CONV_WARPS);
         }
         for (int s = 0; s < A_BUFS; ++s) {
-            mbar_init(&a_full[s], 4);
+            mbar_init(&a_full[s], CONV_WARPS);
             mbar_init(&a_empty[s], 1);
         }
         mbar_init(d_full, 1);
@@ -133,9 +185,11 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             int ws = 0, xs = 0;
             uint32_t wph = 0, xph = 0;
             bool ok = true, waited = false;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                const int t = u % p.tiles_w, j = u / p.tiles_w;
-                for (int s = 0; s < p.nws && ok; ++s) {
+            PieceSched sched(p);
+            Piece pc;
+            while (ok && sched.next(pc)) {
+                const int t = pc.u % p.tiles_w, j = pc.u / p.tiles_w;
+                for (int s = pc.s0; s < pc.s1 && ok; ++s) {
                     if (!mbar_wait(&w_empty[ws], wph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
                     mbar_expect_tx(&w_full[ws], (uint32_t)W_STAGE_BYTES);
                     tma_load_2d(sW + (size_t)ws * W_STAGE_BYTES, &map_w, s * WK, t * BM, &w_full[ws], pol_w);
@@ -160,10 +214,12 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             uint32_t aph = 0, xph = 0;
             bool ok = true;
             int i = 0;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++i) {
+            PieceSched sched(p);
+            Piece pc;
+            for (; ok && sched.next(pc); ++i) {
                 if (!mbar_wait(d_empty, ((uint32_t)i & 1u) ^ 1u, abort_flag, p.status, 13)) { ok = false; break; }
                 tc_fence_after();
-                for (int s = 0; s < p.nws && ok; ++s) {
+                for (int s = pc.s0; s < pc.s1 && ok; ++s) {
                     if (!mbar_wait(&a_full[ab], aph, abort_flag, p.status, 14)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_tmem = tmem_a0 + (uint32_t)(ab * A_COLS);
@@ -173,8 +229,8 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                         const uint64_t db = make_smem_desc(smem_u32(sX + (size_t)xs * x_stage_bytes));
 #pragma unroll
                         for (int k16 = 0; k16 < XK / 16; ++k16)
-                            umma_f16_ts(tmem_base, a_tmem + (uint32_t)((h * (XK / 16) + k16) * 8), db + (uint64_t)(2 * k16), p.idesc,
-                                        (s > 0 || h > 0 || k16 > 0) ? 1u : 0u);
+                            if (p.dbg_mode != 2) umma_f16_ts(tmem_base, a_tmem + (uint32_t)((h * (XK / 16) + k16) * 8), db + (uint64_t)(2 * k16), p.idesc,
+                                        (s > pc.s0 || h > 0 || k16 > 0) ? 1u : 0u);
                         umma_commit(&x_empty[xs]);
                         if (++xs == p.x_stages) { xs = 0; xph ^= 1u; }
                     }
@@ -184,35 +240,44 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 if (ok) umma_commit(d_full);
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 2 + CONV_WARPS) {
         // ------------------------------ converters --------------------------------
+        // Warp pair (w, w+4) shares TMEM lane quarter q = w & 3; `half` picks k 0..63 or 64..127 of the stage.
         const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = q * 32 + lane;  // weight row inside the tile = TMEM lane
         int ws = 0, ab = 0;
         uint32_t wph = 0, aph = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-            for (int s = 0; s < p.nws && ok; ++s) {
+        PieceSched sched(p);
+        Piece pc;
+        while (ok && sched.next(pc)) {
+            for (int s = pc.s0; s < pc.s1 && ok; ++s) {
                 if (!mbar_wait(&w_full[ws], wph, abort_flag, p.status, 16)) { ok = false; break; }
                 // row r of the swizzled tile: logical 16-byte chunk c sits at physical chunk c ^ (r & 7)
                 const uint4* row = reinterpret_cast<const uint4*>(sW + (size_t)ws * W_STAGE_BYTES + (size_t)r * WK);
-                uint4 raw[8];
+                uint4 raw[4];
+                if (p.dbg_mode != 1) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) raw[c] = row[c ^ (r & 7)];
+                    for (int c = 0; c < 4; ++c) raw[c] = row[(half * 4 + c) ^ (r & 7)];
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) raw[c] = make_uint4(0, 0, 0, 0);
+                }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&w_empty[ws]);  // the tile is in registers: the slot may be refilled
+                if (lane == 0) mbar_arrive(&w_empty[ws]);  // this warp's share is in registers
                 if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
-                uint32_t lo[32], hi[32];
+                uint32_t cv[32];
+                if (p.dbg_mode != 1) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[c], lo + 8 * c);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[4 + c], hi + 8 * c);
+                    for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[c], cv + 8 * c);
+                }
                 if (!mbar_wait(&a_empty[ab], aph ^ 1u, abort_flag, p.status, 17)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t a_tmem = tmem_a0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * A_COLS);
-                tmem_st32(a_tmem, lo);
-                tmem_st32(a_tmem + 32, hi);
-                tmem_st_wait();
+                if (p.dbg_mode != 1) {
+                    tmem_st32(tmem_a0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * A_COLS + half * 32), cv);
+                    tmem_st_wait();
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[ab]);
@@ -227,29 +292,80 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         pdl_wait();
         bool ok = true;
         int i = 0;
-        for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++i) {
-            const int t = u % p.tiles_w, j = u / p.tiles_w;
+        PieceSched sched(p);
+        Piece pc;
+        for (; ok && sched.next(pc); ++i) {
+            const int t = pc.u % p.tiles_w, j = pc.u / p.tiles_w;
             const int n = t * BM + r;
             const bool row_ok = n < p.N;
             const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
             if (!mbar_wait(d_full, (uint32_t)i & 1u, abort_flag, p.status, 18)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-            for (int c0 = 0; c0 < p.BN; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(taddr + (uint32_t)c0, v);
-                tmem_ld_wait();
-                if (row_ok) {
+            if (pc.nseg == 1) {
+                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    if (row_ok) {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const int m = j * p.BN + c0 + e;
-                        if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, __uint_as_float(v[e]) * sc);
+                        for (int e = 0; e < 16; ++e) {
+                            const int m = j * p.BN + c0 + e;
+                            if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, __uint_as_float(v[e]) * sc);
+                        }
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(d_empty);
+            } else {
+                // a K-slice of a shared tile: add it into the tile's f32 sums ([col/4][row] x float4, so a warp's
+                // vector reductions cover 512 contiguous bytes); the last CTA to arrive writes y.
+                float* tile = p.sums + (size_t)pc.lu * p.BN * BM;
+                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + (uint32_t)c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; e += 4)
+                        red_add_f32x4(tile + ((size_t)((c0 + e) / 4) * BM + r) * 4, __uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                      __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(d_empty);
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 32 * (2 + CONV_WARPS)) {
+                    const unsigned prev = atomicAdd(p.counters + pc.lu, 1u);
+                    *last_flag = (prev == (unsigned)(pc.nseg - 1)) ? 1 : 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                        float4 f[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) f[e] = __ldcg(reinterpret_cast<const float4*>(tile) + (size_t)(c0 / 4 + e) * BM + r);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            __stcg(reinterpret_cast<float4*>(tile) + (size_t)(c0 / 4 + e) * BM + r, make_float4(0.f, 0.f, 0.f, 0.f));
+                        if (row_ok) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float vals[4] = {f[e].x, f[e].y, f[e].z, f[e].w};
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const int m = j * p.BN + c0 + e * 4 + k;
+                                    if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, vals[k] * sc);
+                                }
+                            }
+                        }
+                    }
+                    if (threadIdx.x == 32 * (2 + CONV_WARPS)) p.counters[pc.lu] = 0u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(d_empty);
         }
     }
 
@@ -288,6 +404,10 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
     p.status = ctx->status_dev;
+    {
+        static const int dbg = getenv("RUSTY_F16_DBG") ? atoi(getenv("RUSTY_F16_DBG")) : 0;
+        p.dbg_mode = dbg;
+    }
     // bf16 A x bf16 B -> f32: c_format=F32(1)@4, a_format=BF16(1)@7, b_format=BF16(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     const size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
@@ -302,7 +422,32 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     if (!make_map_u8(&map_w, a.w, a.N, a.K, BM) || !make_map_bf16(&map_x, a.x, a.M, a.K, (uint32_t)p.BN))
         return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "f16 tensor-core path: cuTensorMapEncodeTiled failed");
     const int units = p.tiles_w * p.tiles_n;
-    const int grid = units < ctx->sm_count ? units : ctx->sm_count;
+    int grid = units < ctx->sm_count ? units : ctx->sm_count;
+    // whole waves of tiles are taken tile-per-CTA; the remainder is cut along K over all CTAs (>= 4 stages each)
+    p.sk_units = units >= grid ? units % grid : 0;
+    p.dp_units = units - p.sk_units;
+    p.sk_per_cta = p.sk_ctas = 0;
+    p.sums = nullptr;
+    p.counters = nullptr;
+    if (p.sk_units > 0) {
+        float* sums = nullptr;
+        unsigned int* counters = nullptr;
+        size_t sums_bytes = 0, cnt_bytes = 0;
+        tc_workspace_sums(ctx, &sums, &sums_bytes, &counters, &cnt_bytes);
+        const size_t need = (size_t)p.sk_units * p.BN * BM * 4;
+        static const bool no_sk = getenv("RUSTY_F16_NO_STREAMK") != nullptr;
+        if (sums && need <= sums_bytes && (size_t)p.sk_units * 4 <= cnt_bytes && !no_sk) {
+            const int work = p.sk_units * p.nws;
+            p.sk_per_cta = (work + grid - 1) / grid;
+            if (p.sk_per_cta < 4) p.sk_per_cta = 4;
+            p.sk_ctas = (work + p.sk_per_cta - 1) / p.sk_per_cta;
+            p.sums = sums;
+            p.counters = counters;
+        } else {
+            p.dp_units = units;
+            p.sk_units = 0;
+        }
+    }
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
     auto kern = yb ? qlinear_f16_tc_kernel<__nv_bfloat16> : qlinear_f16_tc_kernel<float>;
     static size_t smem_set[2][16] = {{0}};

@@ -516,6 +516,16 @@ int tc_workspace_reserve(rusty_cuda_ctx* ctx) {
     return RUSTY_CUDA_OK;
 }
 
+// The zero-maintained part of the workspace (sums of cut tiles + arrival counters), shared by the tensor-core
+// kernels: both leave zeros behind, and kernels on one stream never overlap in their epilogues.
+void tc_workspace_sums(rusty_cuda_ctx* ctx, float** sums, size_t* sums_bytes, unsigned int** counters, size_t* cnt_bytes) {
+    uint8_t* ws = (uint8_t*)ctx->tc_ws;
+    *sums = ws ? (float*)(ws + WS_XQ_BYTES + WS_INVS_BYTES) : nullptr;
+    *sums_bytes = WS_ACC_BYTES;
+    *counters = ws ? (unsigned int*)(ws + WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES) : nullptr;
+    *cnt_bytes = WS_CNT_BYTES;
+}
+
 void tc_workspace_release(rusty_cuda_ctx* ctx) {
     if (ctx->tc_ws) cudaFree(ctx->tc_ws);
     ctx->tc_ws = nullptr;

@@ -290,4 +290,7 @@ def test_prefill_f16_shapes(ctx, engine, oracle, M, K, N):
     assert rel_err(got16[rows], ref) <= TOL_BF16
     exact = xb.astype(np.float64) @ wf.astype(np.float64).T
     assert rel_err(got32, exact) <= TOL_FP32
-    assert np.array_equal(f32_to_bf16_bits(got16), f32_to_bf16_bits(got32))
+    # a bf16 y is the f32 result rounded once; tiles cut along K add their f32 pieces in arrival order, so two
+    # runs may differ in the last f32 bit and, rarely, in the bf16 rounding that follows
+    a16, b16 = f32_to_bf16_bits(got16).astype(np.int32), f32_to_bf16_bits(got32).astype(np.int32)
+    assert np.max(np.abs(a16 - b16)) <= 1 and np.mean(a16 != b16) < 1e-3
