@@ -292,5 +292,5 @@ def test_prefill_f16_shapes(ctx, engine, oracle, M, K, N):
     assert rel_err(got32, exact) <= TOL_FP32
     # a bf16 y is the f32 result rounded once; tiles cut along K add their f32 pieces in arrival order, so two
     # runs may differ in the last f32 bit and, rarely, in the bf16 rounding that follows
-    a16, b16 = f32_to_bf16_bits(got16).astype(np.int32), f32_to_bf16_bits(got32).astype(np.int32)
-    assert np.max(np.abs(a16 - b16)) <= 1 and np.mean(a16 != b16) < 1e-3
+    assert rel_err(got16, got32) <= 2.0 ** -8      # half a bf16 ulp of the largest value, plus the f32 wobble
+    assert np.mean(f32_to_bf16_bits(got16) != f32_to_bf16_bits(got32)) < 1e-3
