@@ -205,6 +205,21 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t 
                                                     const rusty_cuda_buf* const* xs, int x_dtype, uint32_t M,
                                                     rusty_cuda_buf* const* ys, int y_dtype);
 
+/* Fused int8 linear for callers that must not allocate device memory (no counterpart in the reference,
+ * whose ops lean on wgpu's allocator).  Meant for hosts where cudaMalloc is off limits once serving has begun:
+ * a real-time loop whose device memory was carved up front, or a process whose own allocator owns the whole
+ * device.  Raw device pointers in, nothing allocated or freed, no context needed:
+ *     y[M,N] (f32) = x[M,K] (f32) . (w[N,K] (int8, row-major) * scales[N])^T      on `stream` (a cudaStream_t).
+ * The kernel's scratch is a fixed ~1.5 MiB array that lives inside the library on every GPU that loads it,
+ * which caps the shapes: M <= 8 rows and K <= 8192 (K % 16 == 0, w 16-byte aligned); larger calls are
+ * rejected with RUSTY_CUDA_ERR_INVALID_DIMENSIONS.  The current device must be the one the pointers belong
+ * to.  The first call on each device looks the array's address up; make that call before any stream capture.
+ * All calls share the one array: it is cleared where the kernel needs zeros, it otherwise keeps the previous
+ * call's contents, and two calls that overlap on the GPU (different streams) race on it. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w_i8, const float* scales, const float* x_f32,
+                                                        float* y_f32, uint32_t M, uint32_t N, uint32_t K,
+                                                        void* stream);
+
 /* ---- output-feature sharding across the GPUs of one node -------------------
  * No counterpart in the reference (single device, no collective anywhere); this
  * is Linear::forward (rusty-graph/src/lib.rs:69-70) for a weight whose rows

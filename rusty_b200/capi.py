@@ -75,6 +75,7 @@ SIGNATURES = {
     "rusty_cuda_qlinear_destroy": ([_vp], _int),
     "rusty_cuda_qlinear_forward": ([_vp, _vp, _vp, _int, _u32, _vp, _int], _int),
     "rusty_cuda_qlinear_forward_batch": ([_vp, _sz, _vpp, _vpp, _int, _u32, _vpp, _int], _int),
+    "rusty_cuda_qlinear_i8_forward_static": ([_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp], _int),
     "rusty_cuda_comm_unique_id": ([_vp], _int),
     "rusty_cuda_comm_create": ([_vp, _int, _int, _vp, _vpp], _int),
     "rusty_cuda_comm_destroy": ([_vp], _int),

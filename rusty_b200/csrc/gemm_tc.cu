@@ -677,3 +677,145 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx,
     ctx->tc_dbg = buf ? buf->ptr : nullptr;
     return RUSTY_CUDA_OK;
 }
+
+// ----------------------------------------------------------------------------
+// Entry point for callers that must not allocate device memory.
+//
+// Some hosts of this library run where cudaMalloc is off limits: inside a
+// latency-critical serving loop whose memory was carved up front, or under an
+// allocator that owns every byte of the device and treats a foreign allocation
+// as a leak.  For them the tensor-core kernel's scratch (digit planes of the
+// activations, per-row factors, sums of K-cut tiles, arrival counters, status
+// word) lives in the fixed array below, which every GPU that loads this library
+// holds until the process exits.
+// ----------------------------------------------------------------------------
+namespace {
+
+constexpr uint32_t STATIC_MAX_ROWS = 8;       // activation rows per call
+constexpr uint32_t STATIC_MAX_K = 8192;       // input features
+constexpr int STATIC_MAX_CTAS = 160;          // CTAs launched at most (one per SM)
+constexpr size_t ST_XQ_BYTES = (size_t)4 * 8 * STATIC_MAX_K;            // 4 digit planes x 8 padded rows
+constexpr size_t ST_FACTOR_BYTES = 256;
+constexpr size_t ST_SUMS_BYTES = (size_t)STATIC_MAX_CTAS * 8 * 8 * BM;  // one parked 8-row tile (int64) per cut tile
+constexpr size_t ST_CNT_BYTES = 1024;
+constexpr size_t ST_STATUS_BYTES = 256;
+constexpr size_t ST_TOTAL = ST_XQ_BYTES + ST_FACTOR_BYTES + ST_SUMS_BYTES + ST_CNT_BYTES + ST_STATUS_BYTES;  // ~1.5 MiB
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_static_scratch[ST_TOTAL];
+
+struct StaticDev {
+    bool ready = false;
+    unsigned char* base = nullptr;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+};
+std::mutex g_static_mu;
+StaticDev g_static_dev[64];
+
+}  // namespace
+
+extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w_i8, const float* scales, const float* x_f32,
+                                                                   float* y_f32, uint32_t M, uint32_t N, uint32_t K,
+                                                                   void* stream) {
+    using namespace rusty;
+    if (!w_i8 || !scales || !x_f32 || !y_f32)
+        return fail(nullptr, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_i8_forward_static: null pointer");
+    if (M == 0 || N == 0) return RUSTY_CUDA_OK;
+    if (M > STATIC_MAX_ROWS || K > STATIC_MAX_K || K == 0 || K % 16 != 0)
+        return fail(nullptr, RUSTY_CUDA_ERR_INVALID_DIMENSIONS,
+                    "qlinear_i8_forward_static: M=%u K=%u outside the fixed scratch (M <= %u, K <= %u, K %% 16 == 0)", M, K,
+                    STATIC_MAX_ROWS, STATIC_MAX_K);
+    if ((reinterpret_cast<uintptr_t>(w_i8) & 15) != 0)
+        return fail(nullptr, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_i8_forward_static: weights must be 16-byte aligned");
+    if (!encode_tiled_fn())
+        return fail(nullptr, RUSTY_CUDA_ERR_UNSUPPORTED, "qlinear_i8_forward_static: cuTensorMapEncodeTiled is not available");
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return check_cuda(nullptr, e == cudaSuccess ? cudaErrorInvalidDevice : e, "cudaGetDevice");
+    StaticDev sd;
+    {
+        // First call on a device: look up where the array lives ON THAT DEVICE (it must be current) and read
+        // two device attributes.  Nothing is allocated.  Do this once before any stream capture.
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        StaticDev& slot = g_static_dev[dev];
+        if (!slot.ready) {
+            void* ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+            if (e != cudaSuccess) return check_cuda(nullptr, e, "cudaGetSymbolAddress(static scratch)");
+            int sms = 0, optin = 0;
+            e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+            if (e != cudaSuccess) return check_cuda(nullptr, e, "cudaDeviceGetAttribute");
+            slot.base = (unsigned char*)ptr;
+            slot.sm_count = sms;
+            slot.smem_optin = (size_t)optin;
+            slot.ready = true;
+        }
+        sd = slot;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    int8_t* xq = (int8_t*)sd.base;
+    float* factor = (float*)(sd.base + ST_XQ_BYTES);
+    unsigned char* zeroed = sd.base + ST_XQ_BYTES + ST_FACTOR_BYTES;  // sums, counters, status: must start at zero
+    int32_t* sums = (int32_t*)zeroed;
+    unsigned int* counters = (unsigned int*)(zeroed + ST_SUMS_BYTES);
+    rusty_cuda_dev_status* status = (rusty_cuda_dev_status*)(zeroed + ST_SUMS_BYTES + ST_CNT_BYTES);
+    e = cudaMemsetAsync(zeroed, 0, ST_SUMS_BYTES + ST_CNT_BYTES + ST_STATUS_BYTES, st);
+    if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: clearing the scratch");
+
+    const int Mi = (int)M, Mpad = 8, D = 4, NB = 32;
+    e = launch_pdl(digitize_x_kernel<float, 4>, dim3(Mpad), dim3(256), 0, st, x_f32, xq, factor, Mi, Mpad, (int)K);
+    if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: digitize_x");
+
+    TcParams p{};
+    p.scales = scales;
+    p.row_factor = factor;
+    p.part = sums;
+    p.counters = counters;
+    p.y = y_f32;
+    p.M = Mi;
+    p.Mpad = Mpad;
+    p.D = D;
+    p.NB = NB;
+    p.N = (int)N;
+    p.K = (int)K;
+    p.tiles = (p.N + BM - 1) / BM;
+    p.kb_total = (p.K + BK - 1) / BK;
+    int grid = sd.sm_count < STATIC_MAX_CTAS ? sd.sm_count : STATIC_MAX_CTAS;
+    if (grid > p.tiles * p.kb_total / 4) grid = p.tiles * p.kb_total / 4 > 0 ? p.tiles * p.kb_total / 4 : 1;
+    p.sk_tiles = p.tiles % grid;  // < grid <= STATIC_MAX_CTAS parked tiles: fits ST_SUMS_BYTES by construction
+    p.dp_tiles = p.tiles - p.sk_tiles;
+    if (p.sk_tiles > 0) {
+        const int sk_work = p.sk_tiles * p.kb_total;
+        p.sk_per_cta = (sk_work + grid - 1) / grid;
+        if (p.sk_per_cta < 4) p.sk_per_cta = 4;
+        p.sk_ctas = (sk_work + p.sk_per_cta - 1) / p.sk_per_cta;
+    }
+    if (p.dp_tiles == 0 && p.sk_ctas > 0) grid = p.sk_ctas;
+    p.ldy = (int)N;
+    p.y_col0 = 0;
+    p.status = status;
+    p.dbg = nullptr;
+    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    p.tmem_cols = 64;
+    const int b_stage = NB * BK;
+    const size_t red_bytes = (size_t)Mpad * 8 * BM;
+    const size_t budget = (sd.smem_optin > 4096 ? sd.smem_optin - 4096 : 0) / 2;
+    int stages = budget > red_bytes + 4096 ? (int)((budget - 2048 - red_bytes) / (size_t)(A_STAGE_BYTES + b_stage)) : 0;
+    if (stages > 8) stages = 8;
+    if (stages < 2) return fail(nullptr, RUSTY_CUDA_ERR_UNSUPPORTED, "qlinear_i8_forward_static: shared memory too small");
+    p.stages = stages;
+    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 64;
+    CUtensorMap map_w, map_x;
+    if (!make_map_u8(&map_w, w_i8, N, K, BM) || !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, K, (uint32_t)NB))
+        return fail(nullptr, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "qlinear_i8_forward_static: cuTensorMapEncodeTiled failed");
+    auto kern = qlinear_i8_tc_kernel<float>;
+    // Raise the kernel's dynamic shared-memory limit to the device maximum: enough for this launch and never
+    // below what another entry point has asked for.
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sd.smem_optin);
+    if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: cudaFuncSetAttribute");
+    e = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, st, map_w, map_x, p);
+    if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: launch");
+    return RUSTY_CUDA_OK;
+}
