@@ -147,6 +147,11 @@ struct TcParams {
     uint32_t tmem_cols;
     rusty_cuda_dev_status* status;
     long long* dbg;          // optional per-CTA timeline (16 slots each), null in normal use
+    // Fused small-batch mode (M <= 4): no pre-pass and no digit planes in global memory.  The CTA finds the row
+    // maxima of x itself and its epilogue warps write the digit tile of every stage straight into shared memory.
+    int fused;               // 1: x_raw is used, Mpad == M, D == 4, NB == 16
+    int x_bf16;
+    const void* x_raw;       // [M, K] f32 or bf16
 };
 
 // One piece of work: k-blocks [kb0, kb1) of row tile t.  nseg > 1: the tile is
@@ -201,9 +206,24 @@ struct Sched {
 // Digits -> one exact 64-bit integer -> f32 (one rounding) -> row factor (a power
 // of two, exact) -> weight scale (one rounding).
 template <typename YT>
-__device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n) {
-    const float v = __ll2float_rn(acc) * __ldg(p.row_factor + m);
+__device__ __forceinline__ void finalize_store_f(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, float row_factor) {
+    const float v = __ll2float_rn(acc) * row_factor;
     store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, v * scale_n);
+}
+template <typename YT>
+__device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n) {
+    finalize_store_f<YT>(p, y, n, m, acc, scale_n, __ldg(p.row_factor + m));
+}
+
+// Four consecutive activations x[m, k..k+3] as f32 (zeros beyond K); K % 4 == 0.
+__device__ __forceinline__ float4 load_x4(const TcParams& p, int m, int k) {
+    if (k >= p.K) return make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p.x_bf16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.x_raw) + (size_t)m * p.K + k);
+        return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                           __uint_as_float(raw.y & 0xffff0000u));
+    }
+    return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_raw) + (size_t)m * p.K + k);
 }
 
 #define DBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
@@ -218,8 +238,9 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     uint8_t* sA = smem;
     uint8_t* sB = smem + (size_t)p.stages * A_STAGE_BYTES;
     // epilogue staging for the bulk reduce-add of a partial tile: [Mpad/2][128] x 16 bytes
-    int4* stage_red = reinterpret_cast<int4*>(sB + (size_t)p.stages * b_stage_bytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (size_t)p.Mpad * 8 * BM);
+    // fused mode: sB is not a ring but ALL digit tiles of x (one per k-block), written once by the epilogue warps
+    int4* stage_red = reinterpret_cast<int4*>(sB + (size_t)(p.fused ? p.kb_total : p.stages) * b_stage_bytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (p.fused ? (size_t)0 : (size_t)p.Mpad * 8 * BM));
     uint64_t* full = bars;                      // [stages]
     uint64_t* empty = bars + p.stages;          // [stages]
     uint64_t* acc_full = bars + 2 * p.stages;   // [2]
@@ -227,6 +248,10 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
+    float* s_red = reinterpret_cast<float*>(tmem_slot + 4);   // [16] row-maximum partials (fused mode)
+    float* s_scale = s_red + 16;                               // [4] s_m
+    float* s_factor = s_scale + 4;                             // [4] 1/s_m * 128^-3
+    uint64_t* dig_ready = reinterpret_cast<uint64_t*>(s_factor + 4);  // fused mode: the digit tiles of x are in place
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) DBG(0);
@@ -241,6 +266,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             mbar_init(&acc_full[a], 1);
             mbar_init(&acc_empty[a], 4);
         }
+        mbar_init(dig_ready, 4);
         *abort_flag = 0;
         *last_flag = 0;
         fence_barrier_init();
@@ -262,12 +288,25 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             bool ok = true;
             Sched sched(p);
             Segment sg;
+            if (p.fused) {
+                // weights only; they never depend on earlier kernels, so this role does not wait for them at all
+                while (ok && sched.next(sg)) {
+                    for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+                        if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                        mbar_expect_tx(&full[stage], (uint32_t)A_STAGE_BYTES);
+                        tma_load_2d(sA + (size_t)stage * A_STAGE_BYTES, &map_w, kb * BK, sg.t * BM, &full[stage], pol_w);
+                        ++issued;
+                        if (issued == 1) DBG(2);
+                        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
             // The weights do not depend on earlier kernels: start streaming them at once.  The digit planes do, so
             // the first ring-full of stages gets its weight tile now and its digit tile after pdl_wait().
             int early = 0;           // stages whose weight tile is already in flight
             int early_kb[8];
             bool waited = false;
-            while (ok && sched.next(sg)) {
+            while (!p.fused && ok && sched.next(sg)) {
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
                     if (!waited && early < p.stages) {
                         mbar_expect_tx(&full[early], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
@@ -293,7 +332,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (!waited) {  // fewer k-blocks than ring slots
+            if (!waited && !p.fused) {  // fewer k-blocks than ring slots
                 pdl_wait();
                 for (int e = 0; e < early; ++e)
                     tma_load_2d(sB + (size_t)e * b_stage_bytes, &map_x, early_kb[e] * BK, 0, &full[e], pol_x);
@@ -318,6 +357,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             bool ok = true;
             Sched sched(p);
             Segment sg;
+            if (p.fused && !mbar_wait(dig_ready, 0, abort_flag, p.status, 6)) ok = false;
             for (int i = 0; ok && sched.next(sg); ++i) {
                 const int ab = i & 1;
                 if (!mbar_wait(&acc_empty[ab], (((uint32_t)i >> 1) & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
@@ -328,7 +368,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     tc_fence_after();
                     if (kb == sg.kb0 && i == 0) DBG(4);
                     const uint64_t da = make_smem_desc(smem_u32(sA + (size_t)stage * A_STAGE_BYTES));
-                    const uint64_t db = make_smem_desc(smem_u32(sB + (size_t)stage * b_stage_bytes));
+                    const uint64_t db = make_smem_desc(smem_u32(sB + (size_t)(p.fused ? kb : stage) * b_stage_bytes));
 #pragma unroll
                     for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
                         // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
@@ -347,8 +387,89 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const int r = q * 32 + lane;            // row inside the tile
         YT* y = reinterpret_cast<YT*>(p.y);
         const int ncol = p.D * p.Mpad;          // accumulator columns in use
-        pdl_wait();                             // y, the parked partials and the counters belong to earlier kernels until now
+        pdl_wait();                             // x, y, the sums and the counters belong to earlier kernels until now
         bool ok = true;
+        const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
+        if (p.fused) {
+            // zero every digit tile once (rows that hold no digit plane stay zero for the whole kernel)
+            for (int i = et; i < p.kb_total * b_stage_bytes / 16; i += EPI_THREADS) reinterpret_cast<uint4*>(sB)[i] = make_uint4(0, 0, 0, 0);
+            // row maxima of x -> power-of-two scale per row (the same rule as the pre-pass kernel).  x is read in
+            // chunks of 4096 elements, 8 independent 16-byte loads per thread, so a chunk costs one L2 round trip.
+            float mx[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                if (m < p.M) {
+                    for (int c0 = 0; c0 < p.K; c0 += 4096) {
+                        float4 v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = load_x4(p, m, c0 + (j * EPI_THREADS + et) * 4);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float a4[4] = {fabsf(v[j].x), fabsf(v[j].y), fabsf(v[j].z), fabsf(v[j].w)};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) mx[m] = (a4[e] <= 3.0e38f) ? fmaxf(mx[m], a4[e]) : __int_as_float(0x7f800000);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xffffffffu, mx[m], off));
+                if (lane == 0) s_red[(warp - 2) * 4 + m] = mx[m];
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+            if (et < p.M) {
+                const float v = fmaxf(fmaxf(s_red[et], s_red[4 + et]), fmaxf(s_red[8 + et], s_red[12 + et]));
+                float sc = 1.0f;
+                if (v > 0.0f && v <= 3.0e38f) {
+                    int e;
+                    frexpf(v, &e);
+                    sc = ldexpf(1.0f, 7 - e);
+                    if (v * sc > 127.0f) sc *= 0.5f;
+                }
+                s_scale[et] = sc;
+                s_factor[et] = (v <= 3.0e38f) ? ldexpf(1.0f / sc, -21) : __int_as_float(0x7fc00000);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+            // all digit tiles: elements k..k+3 of row m -> 4 packed bytes at (k % 128) of row d*M + m in tile k / 128
+            // (128-byte swizzle: 16-byte chunk index XOR row % 8)
+            for (int m = 0; m < p.M; ++m) {
+                const float sm = s_scale[m];
+                for (int c0 = 0; c0 < p.K; c0 += 4096) {
+                    float4 v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = load_x4(p, m, c0 + (j * EPI_THREADS + et) * 4);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = c0 + (j * EPI_THREADS + et) * 4;
+                        if (k >= p.K) continue;
+                        const float xe[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                        uint32_t packed[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float rr = xe[e] * sm;
+#pragma unroll
+                            for (int d = 0; d < 4; ++d) {
+                                const float qd = rintf(rr);
+                                packed[d] |= ((uint32_t)(int)qd & 0xFFu) << (8 * e);
+                                rr = (rr - qd) * 128.0f;
+                            }
+                        }
+                        uint8_t* tile = sB + (size_t)(k / BK) * b_stage_bytes;
+                        const int kk = k % BK;
+#pragma unroll
+                        for (int d = 0; d < 4; ++d) {
+                            const int row = d * p.M + m;
+                            *reinterpret_cast<uint32_t*>(tile + row * BK + ((((kk >> 4) ^ (row & 7)) << 4) | (kk & 15))) = packed[d];
+                        }
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dig_ready);
+        }
         Sched sched(p);
         Segment sg;
         for (int i = 0; ok && sched.next(sg); ++i) {
@@ -359,7 +480,63 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             tc_fence_after();
             if (threadIdx.x == 64) DBG(6 + 4 * (i & 1));
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * p.NB);
-            if (sg.nseg == 1) {
+            if (p.fused) {
+                uint32_t c[16];
+                tmem_ld16(taddr, c);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                long long acc[4];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    acc[m] = 0;
+                    if (m < p.M) {
+#pragma unroll
+                        for (int d = 0; d < 4; ++d) {
+                            int32_t v = 0;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (j == d * p.M + m) v = (int32_t)c[j];
+                            acc[m] = acc[m] * 128 + v;
+                        }
+                    }
+                }
+                const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+                if (sg.nseg == 1) {
+                    if (row_ok)
+                        for (int m = 0; m < p.M; ++m) finalize_store_f<YT>(p, y, n, m, acc[m], sc, s_factor[m]);
+                } else {
+                    // a piece of a K-cut tile: 64-bit integer reductions straight from registers (exact, any order)
+                    const int lt = sg.t - p.dp_tiles;
+                    unsigned long long* tile_sum = reinterpret_cast<unsigned long long*>(p.part) + (size_t)lt * 4 * BM;
+                    if (row_ok)
+                        for (int m = 0; m < p.M; ++m) atomicAdd(tile_sum + (size_t)m * BM + r, (unsigned long long)acc[m]);
+                    __threadfence();
+                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                    if (threadIdx.x == 64) {
+                        unsigned prev = atomicAdd(p.counters + sg.t, 1u);
+                        *reinterpret_cast<volatile int*>(last_flag) = (prev == (unsigned)(sg.nseg - 1)) ? 1 : 0;
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                    if (*reinterpret_cast<volatile int*>(last_flag) != 0) {
+                        __threadfence();
+                        if (row_ok) {
+                            long long tot[4];
+#pragma unroll
+                            for (int m = 0; m < 4; ++m) tot[m] = m < p.M ? (long long)__ldcg(tile_sum + (size_t)m * BM + r) : 0;
+#pragma unroll
+                            for (int m = 0; m < 4; ++m)
+                                if (m < p.M) {
+                                    __stcg(tile_sum + (size_t)m * BM + r, 0ull);
+                                    finalize_store_f<YT>(p, y, n, m, tot[m], sc, s_factor[m]);
+                                }
+                        }
+                        if (threadIdx.x == 64) p.counters[sg.t] = 0u;
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                }
+            } else if (sg.nseg == 1) {
                 const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
                 for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
                     int32_t c[4][8];
@@ -553,9 +730,12 @@ bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a) {
 
 // One launch pair (digitise + GEMM) for up to 64 activation rows.
 static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void* x, void* y, uint32_t rows) {
-    const int M = (int)rows, Mpad = (M + 7) / 8 * 8;
-    const int D = pick_digits(a.x_dtype, rows);
-    const int NB = (D * Mpad + 15) / 16 * 16;
+    // Small batches whose activations a CTA can scan by itself (<= 64 KiB) skip the pre-pass kernel.
+    static const bool no_fuse = getenv("RUSTY_TC_NO_FUSED_X") != nullptr;
+    const bool fused = !no_fuse && rows <= 4 && (size_t)rows * a.K <= 16384;
+    const int M = (int)rows, Mpad = fused ? M : (M + 7) / 8 * 8;
+    const int D = fused ? 4 : pick_digits(a.x_dtype, rows);
+    const int NB = (fused && D * Mpad <= 8) ? 8 : (D * Mpad + 15) / 16 * 16;
     uint8_t* ws = (uint8_t*)ctx->tc_ws;
     int8_t* xq = (int8_t*)ws;
     float* inv_s = (float*)(ws + WS_XQ_BYTES);
@@ -564,11 +744,15 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     if ((size_t)D * Mpad * a.K > WS_XQ_BYTES)
         return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: %d digit rows x K=%u exceed the workspace", D * Mpad, a.K);
 
-    cudaError_t le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D)
-                                                  : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D);
-    if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
-    int rc = after_launch(ctx, "digitize_x");
-    if (rc) return rc;
+    cudaError_t le = cudaSuccess;
+    int rc = RUSTY_CUDA_OK;
+    if (!fused) {
+        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D)
+                                          : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D);
+        if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
+        rc = after_launch(ctx, "digitize_x");
+        if (rc) return rc;
+    }
 
     TcParams p{};
     p.scales = a.scales;
@@ -606,7 +790,7 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
             if (aligned >= 4 && (long long)p.sk_per_cta * 100 >= (long long)aligned * 85) p.sk_per_cta = aligned;
         }
         p.sk_ctas = (sk_work + p.sk_per_cta - 1) / p.sk_per_cta;
-        const size_t need = (size_t)p.sk_tiles * Mpad * BM * 8;
+        const size_t need = (size_t)p.sk_tiles * (fused ? 4 : Mpad) * BM * 8;
         if (need > WS_ACC_BYTES || (size_t)p.tiles * 4 > WS_CNT_BYTES) {
             p.dp_tiles = p.tiles;  // no room to park partial tiles: whole tiles only
             p.sk_tiles = 0;
@@ -620,6 +804,9 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.y_col0 = (int)a.y_col0;
     p.status = ctx->status_dev;
     p.dbg = (long long*)ctx->tc_dbg;
+    p.fused = fused ? 1 : 0;
+    p.x_bf16 = a.x_dtype == RUSTY_CUDA_BF16 ? 1 : 0;
+    p.x_raw = x;
     // int8 x int8 -> int32, both K-major: c_format=S32(2)@4, a_format=INT8(1)@7, b_format=INT8(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     uint32_t cols = 32;
@@ -630,17 +817,22 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     // prefetch its weights while this one drains (RUSTY_TC_FULL_SMEM=1: take it all, 8 stages).
     static const bool full_smem = getenv("RUSTY_TC_FULL_SMEM") != nullptr;
     size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
-    if (!full_smem && NB <= 32) budget = budget / 2 - 1024;  // narrow batches: 5 stages are enough to cover HBM latency
-    const size_t red_bytes = (size_t)Mpad * 8 * BM;  // epilogue staging of a partial tile
-    int stages = budget > red_bytes + 2048 ? (int)((budget - 1024 - 256 - red_bytes) / (size_t)(A_STAGE_BYTES + b_stage)) : 0;
+    // fused mode keeps every digit tile of x resident instead of a ring of them
+    const size_t dig_bytes = fused ? (size_t)p.kb_total * b_stage : 0;
+    if (!full_smem && NB <= 32 && dig_bytes + 4 * A_STAGE_BYTES + 4096 <= budget / 2)
+        budget = budget / 2 - 1024;  // narrow batches: leave room for the next kernel's CTA on the SM
+    const size_t red_bytes = fused ? dig_bytes : (size_t)Mpad * 8 * BM;  // epilogue staging of a partial tile
+    int stages = budget > red_bytes + 2048
+                     ? (int)((budget - 1024 - 512 - red_bytes) / (size_t)(A_STAGE_BYTES + (fused ? 0 : b_stage)))
+                     : 0;
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: tile does not fit shared memory");
     p.stages = stages;
-    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 64;
+    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + (fused ? 0 : b_stage)) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
 
     CUtensorMap map_w, map_x;
     if (!make_map_u8(&map_w, a.w, a.N, a.K, BM) ||
-        !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, a.K, (uint32_t)NB))
+        !make_map_u8(&map_x, xq, (uint64_t)D * (fused ? 8 : Mpad), a.K, (uint32_t)NB))
         return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "tensor-core path: cuTensorMapEncodeTiled failed");
 
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
@@ -806,7 +998,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(nullptr, RUSTY_CUDA_ERR_UNSUPPORTED, "qlinear_i8_forward_static: shared memory too small");
     p.stages = stages;
-    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 64;
+    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
     CUtensorMap map_w, map_x;
     if (!make_map_u8(&map_w, w_i8, N, K, BM) || !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, K, (uint32_t)NB))
         return fail(nullptr, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "qlinear_i8_forward_static: cuTensorMapEncodeTiled failed");

@@ -21,11 +21,11 @@
 // Layout KN ([in,out], rusty's own Linear orientation) kernel: a thread owns 16
 // consecutive output features and a slice of k; the block reduces the slices
 // through shared memory.
-#include "internal.h"
+#include "tc_common.cuh"
 
 namespace {
 
-constexpr int GEMV_THREADS = 512;
+constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 constexpr int CHUNK = 512;  // k-elements one warp covers per step (32 lanes x 16 bytes)
 
@@ -81,7 +81,7 @@ __device__ __forceinline__ int xs_index(int m, int nchunks, int k) {
 // MB * nchunks*32 floats holding the sum of each lane's 16 x values.
 // ---------------------------------------------------------------------------
 template <int MB, int R, int U, bool AFFINE, typename XT, typename YT>
-__global__ void __launch_bounds__(GEMV_THREADS)
+__global__ void __launch_bounds__(GEMV_THREADS, (MB <= 2 ? 2 : 1))
 gemv_nk_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, const float* __restrict__ biases,
                const XT* __restrict__ x, YT* __restrict__ y, int M, int N, int K, int ldy, int y_col0) {
     extern __shared__ __align__(16) float smem[];
@@ -89,6 +89,28 @@ gemv_nk_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
     float* xs = smem;
     float* xsum = smem + (size_t)MB * nchunks * CHUNK;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ngroups = (N + R - 1) / R;
+    const int gstride = gridDim.x * GEMV_WARPS;
+
+    // Let the next kernel in the stream start (programmatic dependent launch), and put this warp's first batch of
+    // weight bytes in flight BEFORE waiting for the previous kernel: weights never depend on it, x and y may.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    auto load_batch = [&](int g, int c0, uint4 (&dst)[U][R]) {
+        const int n0 = g * R;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (c0 + u) * CHUNK + lane * 16;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int n = n0 + r < N ? n0 + r : N - 1;  // clamp: a duplicate row is read, its result dropped
+                dst[u][r] = (k < K && g < ngroups) ? ld_stream_16B(W + (size_t)n * K + k) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    int g = blockIdx.x * GEMV_WARPS + warp, c0 = 0;
+    uint4 wnext[U][R];
+    load_batch(g, c0, wnext);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- stage x (zero-filled beyond M and beyond K) ----
     for (int i = tid; i < MB * nchunks * CHUNK; i += GEMV_THREADS) {
@@ -111,102 +133,104 @@ gemv_nk_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
         __syncthreads();
     }
 
-    const int ngroups = (N + R - 1) / R;
-    for (int g = blockIdx.x * GEMV_WARPS + warp; g < ngroups; g += gridDim.x * GEMV_WARPS) {
-        const int n0 = g * R;
-        float acc[R][MB];
+    float acc[R][MB];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int m = 0; m < MB; ++m) acc[r][m] = 0.0f;
-        const uint8_t* rowp[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            int n = n0 + r < N ? n0 + r : N - 1;  // clamp: a duplicate row is read, its result dropped
-            rowp[r] = W + (size_t)n * K + lane * 16;
-        }
+        for (int m = 0; m < MB; ++m) acc[r][m] = 0.0f;
 
-        for (int c0 = 0; c0 < nchunks; c0 += U) {
-            uint4 wv[U][R];
+    while (g < ngroups) {
+        // take the batch that is in flight, then put the following one in flight before computing
+        uint4 wv[U][R];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int k = (c0 + u) * CHUNK + lane * 16;
+        for (int u = 0; u < U; ++u)
 #pragma unroll
-                for (int r = 0; r < R; ++r)
-                    wv[u][r] = (k < K) ? ld_stream_16B(rowp[r] + (size_t)(c0 + u) * CHUNK) : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int c = c0 + u;
-                const int k = c * CHUNK + lane * 16;
-                if (c >= nchunks) break;
-                const bool live = k < K;
-                float sc[R], bi[R];
-                if (AFFINE) {
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        int n = n0 + r < N ? n0 + r : N - 1;
-                        size_t grp = ((size_t)n * K + k) / 64;
-                        sc[r] = live ? __ldg(scales + grp) : 0.0f;
-                        bi[r] = live ? __ldg(biases + grp) : 0.0f;
-                    }
-                }
-                float part[R][MB];
-#pragma unroll
-                for (int r = 0; r < R; ++r)
-#pragma unroll
-                    for (int m = 0; m < MB; ++m) part[r][m] = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float4 xv[MB];
-#pragma unroll
-                    for (int m = 0; m < MB; ++m)
-                        xv[m] = *reinterpret_cast<const float4*>(xs + ((size_t)((m * nchunks + c) * 4 + j) * 32 + lane) * 4);
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        const uint32_t word = j == 0 ? wv[u][r].x : j == 1 ? wv[u][r].y : j == 2 ? wv[u][r].z : wv[u][r].w;
-                        float f[4];
-                        bytes4_to_f32<!AFFINE>(word, f);
-#pragma unroll
-                        for (int m = 0; m < MB; ++m) {
-                            float* a = AFFINE ? &part[r][m] : &acc[r][m];
-                            *a = fmaf(xv[m].x, f[0], *a);
-                            *a = fmaf(xv[m].y, f[1], *a);
-                            *a = fmaf(xv[m].z, f[2], *a);
-                            *a = fmaf(xv[m].w, f[3], *a);
-                        }
-                    }
-                }
-                if (AFFINE) {
-#pragma unroll
-                    for (int m = 0; m < MB; ++m) {
-                        float sx = xsum[(m * nchunks + c) * 32 + lane];
-#pragma unroll
-                        for (int r = 0; r < R; ++r) acc[r][m] += sc[r] * part[r][m] + bi[r] * sx;
-                    }
-                }
-            }
+            for (int r = 0; r < R; ++r) wv[u][r] = wnext[u][r];
+        const int cur_g = g, cur_c0 = c0;
+        c0 += U;
+        if (c0 >= nchunks) {
+            c0 = 0;
+            g += gstride;
         }
-        // ---- warp reduction and store ----
+        load_batch(g, c0, wnext);
+        const int n0 = cur_g * R;
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+        for (int u = 0; u < U; ++u) {
+            const int c = cur_c0 + u;
+            const int k = c * CHUNK + lane * 16;
+            if (c >= nchunks) break;
+            const bool live = k < K;
+            float sc[R], bi[R];
+            if (AFFINE) {
 #pragma unroll
-            for (int m = 0; m < MB; ++m) {
-                float v = acc[r][m];
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-                acc[r][m] = v;
+                for (int r = 0; r < R; ++r) {
+                    int n = n0 + r < N ? n0 + r : N - 1;
+                    size_t grp = ((size_t)n * K + k) / 64;
+                    sc[r] = live ? __ldg(scales + grp) : 0.0f;
+                    bi[r] = live ? __ldg(biases + grp) : 0.0f;
+                }
             }
-        if (lane == 0) {
+            float part[R][MB];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                int n = n0 + r;
-                if (n >= N) continue;
-                float s = AFFINE ? 1.0f : __ldg(scales + n);
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int m = 0; m < MB; ++m) part[r][m] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float4 xv[MB];
 #pragma unroll
                 for (int m = 0; m < MB; ++m)
-                    if (m < M) store_out<YT>(y + (size_t)m * ldy + y_col0 + n, AFFINE ? acc[r][m] : acc[r][m] * s);
+                    xv[m] = *reinterpret_cast<const float4*>(xs + ((size_t)((m * nchunks + c) * 4 + j) * 32 + lane) * 4);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const uint32_t word = j == 0 ? wv[u][r].x : j == 1 ? wv[u][r].y : j == 2 ? wv[u][r].z : wv[u][r].w;
+                    float f[4];
+                    bytes4_to_f32<!AFFINE>(word, f);
+#pragma unroll
+                    for (int m = 0; m < MB; ++m) {
+                        float* a = AFFINE ? &part[r][m] : &acc[r][m];
+                        *a = fmaf(xv[m].x, f[0], *a);
+                        *a = fmaf(xv[m].y, f[1], *a);
+                        *a = fmaf(xv[m].z, f[2], *a);
+                        *a = fmaf(xv[m].w, f[3], *a);
+                    }
+                }
             }
+            if (AFFINE) {
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    float sx = xsum[(m * nchunks + c) * 32 + lane];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) acc[r][m] += sc[r] * part[r][m] + bi[r] * sx;
+                }
+            }
+        }
+        if (cur_c0 + U >= nchunks) {
+            // ---- the rows of this group are complete: warp reduction and store ----
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    float v = acc[r][m];
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                    acc[r][m] = v;
+                }
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    int n = n0 + r;
+                    if (n >= N) continue;
+                    float s = AFFINE ? 1.0f : __ldg(scales + n);
+#pragma unroll
+                    for (int m = 0; m < MB; ++m)
+                        if (m < M) store_out<YT>(y + (size_t)m * ldy + y_col0 + n, AFFINE ? acc[r][m] : acc[r][m] * s);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int m = 0; m < MB; ++m) acc[r][m] = 0.0f;
         }
     }
 }
@@ -323,10 +347,14 @@ int launch_nk(rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a, const void* x, v
     }
     int ngroups = (a.N + R - 1) / R;
     int blocks = (ngroups + GEMV_WARPS - 1) / GEMV_WARPS;
-    int max_blocks = ctx->sm_count * (smem <= 100 * 1024 ? 2 : 1);
+    // one CTA per SM for short problems (so that the next kernel's CTA fits beside it and prefetches its weights
+    // while this one drains), two when every warp has several row groups to stream
+    int per_sm = (smem <= 100 * 1024 && MB <= 2 && ngroups >= 4 * ctx->sm_count * GEMV_WARPS) ? 2 : 1;
+    int max_blocks = ctx->sm_count * per_sm;
     if (blocks > max_blocks) blocks = max_blocks;
-    kern<<<blocks, GEMV_THREADS, smem, ctx->stream>>>(a.w, a.scales, a.biases, (const XT*)x, (YT*)y, M, (int)a.N, (int)a.K,
-                                                      (int)a.ldy, (int)a.y_col0);
+    cudaError_t le = rusty_tc::launch_pdl(kern, dim3(blocks), dim3(GEMV_THREADS), smem, ctx->stream, a.w, a.scales, a.biases,
+                                          (const XT*)x, (YT*)y, M, (int)a.N, (int)a.K, (int)a.ldy, (int)a.y_col0);
+    if (le != cudaSuccess) return rusty::check_cuda(ctx, le, "gemv_nk");
     return rusty::after_launch(ctx, "gemv_nk");
 }
 
