@@ -219,6 +219,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (for profiling captures only)")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-Linear and CPU legs")
+    ap.add_argument("--single", default=None, metavar="MxKxN:f32|bf16",
+                    help="run ONE fused linear of this shape --steps times on rotating weight copies and print its "
+                         "timing (small case for profiler captures; not the benchmark line)")
     args = ap.parse_args()
     if args.warmup < 3 and args.layers is None:
         args.warmup = 3
@@ -229,6 +232,16 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.single:
+        import rusty_b200
+        from rusty_b200 import DType
+        shape, _, dt = args.single.partition(":")
+        M, K, N = (int(v) for v in shape.lower().split("x"))
+        d = DType.BF16 if dt == "bf16" else DType.FP32
+        ctx = rusty_b200.CudaContext(local_rank)
+        r = bench_single_linear(ctx, rusty_b200.ComputeEngine(ctx), M, K, N, d, d, max(1, args.steps), max(1, args.warmup))
+        print(json.dumps({"single": args.single, **r}), flush=True)
         return
 
     stack_name, M, desc = WORKLOADS[args.workload]
