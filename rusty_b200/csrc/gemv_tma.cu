@@ -46,6 +46,7 @@ struct TgParams {
     int ldy, y_col0;
     int x_bf16, y_bf16;
     rusty_cuda_dev_status* status;
+    long long* dbg;   // optional per-CTA timeline (development aid), null in normal use
 };
 
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar, uint64_t policy) {
@@ -65,6 +66,8 @@ __device__ __forceinline__ void s8x4_to_f32(uint32_t w, float (&f)[4]) {
 }
 
 // MB activation rows (1 or 2), NJ passes of 4096 k.
+#define TDBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+
 template <int MB, int NJ>
 __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -78,6 +81,7 @@ __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams 
     volatile int* abort_flag = reinterpret_cast<volatile int*>(freeb + p.stages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) TDBG(0);
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -133,9 +137,11 @@ __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams 
             if (lane == 0) mbar_arrive(&freeb[stage]);
             if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
+        if (lane == 0) TDBG(6);
     } else {
         // ------------------------------ compute -------------------------------
         pdl_wait();  // x may come from the previous kernel
+        if (threadIdx.x == 0) TDBG(1);
         // this lane's activations: 16 consecutive k per pass, for the whole kernel
         float xr[MB][NJ][16];
 #pragma unroll
@@ -162,10 +168,12 @@ __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams 
                     xr[m][j][e4 * 4 + 3] = v.w;
                 }
             }
+        if (threadIdx.x == 0) TDBG(3);
         int stage = 0;
         uint32_t phase = 0;
         for (int t = blockIdx.x; t < p.tiles; t += gridDim.x) {
             if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 23)) break;
+            if (threadIdx.x == 0 && t == blockIdx.x) TDBG(4);
             const uint8_t* tile = sW + (size_t)stage * stage_stride;
             const int rows = min(p.rows_per_stage, p.N - t * p.rows_per_stage);
             float acc[4][MB];
@@ -221,6 +229,7 @@ __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams 
             if (lane == 0) mbar_arrive(&done[stage]);
             if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
+        if (threadIdx.x == 0) TDBG(5);
     }
 }
 
@@ -268,17 +277,21 @@ int launch_gemv_tma(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.x_bf16 = a.x_dtype == RUSTY_CUDA_BF16;
     p.y_bf16 = a.y_dtype == RUSTY_CUDA_BF16;
     p.status = ctx->status_dev;
+    p.dbg = (long long*)ctx->tc_dbg;
     const int MB = a.M == 1 ? 1 : 2;
     const size_t stage_stride = ((size_t)p.rows_per_stage * p.K + 127) & ~(size_t)127;
-    // about half an SM's shared memory, so that two CTAs (this kernel's and the next one's) fit side by side
-    const size_t budget = (ctx->smem_optin > 8192 ? ctx->smem_optin - 8192 : 0) / 2;
+    // a quarter of an SM's shared memory: two CTAs of this kernel (16 compute warps per SM hide the conversion and
+    // shuffle latencies far better than 8) plus two of the next kernel, which prefetch while these drain
+    // (long problems: two CTAs with half each, deeper rings matter more than the hand-over to the next kernel)
+    const bool longrun = p.tiles >= 16 * ctx->sm_count;
+    const size_t budget = (ctx->smem_optin > 8192 ? ctx->smem_optin - 8192 : 0) / (longrun ? 2 : 4);
     int stages = (int)(budget / (stage_stride + 4 * MB * CW * 4 + 24));
     if (stages > 12) stages = 12;
     if (stages < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "gemv_tma: stage does not fit shared memory");
     p.stages = stages;
     const size_t smem = (size_t)stages * stage_stride + (size_t)stages * 4 * MB * CW * 4 + (size_t)stages * 24 + 64;
     // short problems: one CTA per SM (the next kernel's CTA moves in beside it); long ones: two per SM
-    const int per_sm = p.tiles >= 16 * ctx->sm_count ? 2 : 1;
+    const int per_sm = 2;
     int grid = ctx->sm_count * per_sm;
     if (grid > p.tiles) grid = p.tiles;
     const int NJ = (int)((a.K + CHUNKS_PER_PASS * 16 - 1) / (CHUNKS_PER_PASS * 16));
