@@ -1,0 +1,565 @@
+// Prefill GEMM over int8 weights on tcgen05 / TMEM with bf16 operands, CTA-PAIR version (tcgen05 cta_group::2).
+//
+// Same kernel as gemm_f16_tc.cu, but two CTAs of a cluster work on one 256-row weight tile: each converts its own 128
+// weight rows into its own tensor memory and loads only HALF of the activation tile; one tcgen05.mma issued by the leader
+// CTA multiplies all 256 weight rows by the whole activation tile, reading the other half of B from the peer's shared
+// memory.  Activation bytes fetched from L2 per flop halve, which is what limits the single-CTA kernel.  Each CTA issues
+// its own plain TMA copies; completion of the peer's copies is signalled on the leader's mbarrier (cta_group::2 form of
+// the copy); tcgen05.commit is issued once per CTA of the pair.
+//
+// (single-CTA description follows)
+//
+// Replaces, for many activation rows at once, the reference's "dequantise once
+// at load, f32 tiled matmul per forward" (rusty-loader/src/lib.rs:155-218,
+// rusty-backend/src/kernels.wgsl:16-54, :234-242):
+//     y[m,n] = scale[n] * sum_k x[m,k] * q[n,k]        x bf16, q int8, fp32 accumulation
+//
+// The weight rows are the M side of the MMA (128 rows per tile), the activation
+// rows the N side (up to 256 per tile), so the accumulator tile is y^T.
+//   * int8 weight tiles (128 rows x 128 k, 16 KB) arrive by TMA with the 128-byte
+//     swizzle; four converter warps (one thread per weight row) read their row
+//     conflict-free, turn bytes into bf16 pairs (byte-permute into the mantissa of
+//     2^23, subtract, packed convert: exact since |q| <= 128), and write them
+//     straight into TENSOR MEMORY with tcgen05.st — the A operand never goes back
+//     through shared memory;
+//   * bf16 activation tiles (up to 256 rows x 64 k) arrive by TMA as the B operand;
+//   * one elected thread issues tcgen05.mma kind::f16 (A bf16 from TMEM, B bf16
+//     from shared memory, fp32 accumulators in TMEM); bf16 x bf16 products are
+//     exact in the fp32 accumulate, so the only rounding is the summation;
+//   * four epilogue warps read the accumulators, apply the per-row weight scale and
+//     store y (bf16 or f32) while the converters already work on the next tile.
+// Persistent CTAs, one per SM; every mbarrier wait is bounded.
+#include <cstdlib>
+#include <cstring>
+
+#include "tc_common.cuh"
+
+using namespace rusty_tc;
+
+namespace {
+
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the pair leader's copy
+
+constexpr int BM = 128;          // weight rows per tile (UMMA M)
+constexpr int WK = 128;          // k per weight stage (bytes per row)
+constexpr int XK = 64;           // k per activation stage (128 bytes of bf16 per row)
+constexpr int W_STAGES = 5;        // 80 KB of weights in flight: the pair kernel consumes 16 KB every ~0.5 us and a refill takes ~2 us
+constexpr int A_BUFS = 3;        // converted-weight buffers in tensor memory, 64 columns each
+constexpr int A_COLS = WK / 2;   // two 16-bit values per 32-bit column
+constexpr int D_COLS = 256;      // accumulator columns reserved
+constexpr int CONV_WARPS = 8;     // two per TMEM lane quarter, each takes half of a stage's k range
+constexpr int F16_THREADS = 32 * (2 + CONV_WARPS + 4);  // producer, MMA, converter and 4 epilogue warps
+constexpr int W_STAGE_BYTES = BM * WK;
+
+struct F16Params2 {
+    const float* scales;  // [N]
+    void* y;
+    int Mx, N, K;
+    int BN;               // activation rows per pair tile (multiple of 32, <= 256); each CTA loads BN/2 of them
+    int tiles_w, tiles_n, nws;  // weight-row tiles, activation-row tiles, weight stages per tile
+    int x_stages;
+    // Schedule: units = tiles_w * tiles_n tiles of the output.  The last `sk_units` of them are cut along K
+    // (stream-K): their sk_units*nws weight stages form one linear space dealt out in contiguous runs of
+    // `sk_per_cta` to the first `sk_ctas` CTAs; the other units are taken whole, unit = cta, cta + grid, ...
+    int dp_units, sk_units, sk_per_cta, sk_ctas;
+    float* sums;              // [sk_units][BN/4][128] x float4: f32 sums of cut tiles (zero between uses)
+    unsigned int* counters;   // [sk_units] arrivals per cut tile (zero between uses)
+    int ldy, y_col0;
+    uint32_t idesc;
+    long long* dbg;       // optional per-CTA timeline (development aid)
+    int dbg_mode;         // tuning aid (RUSTY_F16_DBG): 1 = converters skip their work, 2 = MMA thread issues nothing
+    rusty_cuda_dev_status* status;
+};
+
+template <typename T>
+__device__ __forceinline__ void store_y(T* p, float v);
+template <>
+__device__ __forceinline__ void store_y<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// 16 int8 (one 128-bit word) -> 8 registers of packed bf16 pairs (low half = even k).
+// u = q ^ 0x80 is q + 128; dropping u into the low mantissa byte of 2^23 and subtracting 2^23 + 128 leaves q
+// exactly as an f32, and |q| <= 128 fits bf16's 8 significant bits, so the packed conversion is exact too.
+__device__ __forceinline__ void int8x16_to_bf16x2(const uint4& w, uint32_t* out) {
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t u = words[i] ^ 0x80808080u;
+        const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+        const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+        const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+        const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+        __nv_bfloat162 a = __floats2bfloat162_rn(f0, f1);
+        __nv_bfloat162 b = __floats2bfloat162_rn(f2, f3);
+        out[2 * i] = *reinterpret_cast<uint32_t*>(&a);
+        out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
+    }
+}
+
+// One piece of work: weight stages [s0, s1) of output tile `u`.  nseg > 1: the tile is shared with other CTAs.
+struct Piece {
+    int u, s0, s1, nseg, lu;
+};
+
+// Every role of the CTA walks the same list of pieces: the stream-K share first, whole tiles after it.
+struct PieceSched {
+    const F16Params2& p;
+    int g, g_end, dp_next;
+    __device__ PieceSched(const F16Params2& pp) : p(pp) {
+        const int c = blockIdx.x >> 1;   // pair index: both CTAs of a pair walk the same list
+        g = c < p.sk_ctas ? c * p.sk_per_cta : 0;
+        g_end = c < p.sk_ctas ? min(p.sk_units * p.nws, g + p.sk_per_cta) : 0;
+        dp_next = c;
+    }
+    __device__ bool next(Piece& q) {
+        if (g < g_end) {
+            q.lu = g / p.nws;
+            q.u = p.dp_units + q.lu;
+            q.s0 = g % p.nws;
+            q.s1 = min(p.nws, q.s0 + (g_end - g));
+            const int first = (q.lu * p.nws) / p.sk_per_cta;
+            const int last = ((q.lu + 1) * p.nws - 1) / p.sk_per_cta;
+            q.nseg = last - first + 1;
+            g += q.s1 - q.s0;
+            return true;
+        }
+        if (dp_next < p.dp_units) {
+            q.u = dp_next;
+            q.lu = 0;
+            q.s0 = 0;
+            q.s1 = p.nws;
+            q.nseg = 1;
+            dp_next += gridDim.x >> 1;
+            return true;
+        }
+        return false;
+    }
+};
+
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the pair LEADER's copy of a barrier (works from either CTA)
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & PEER_BIT_MASK) : "memory");
+}
+// TMA tile load whose completion bytes are counted on the pair leader's barrier
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint64_t* bar,
+                                                 uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & PEER_BIT_MASK), "r"(c0), "r"(c1),
+          "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot_in_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// the mbarrier at this offset in BOTH CTAs of the pair arrives once all MMAs issued so far have completed
+// (two plain commits, one per CTA: the peer's copy is addressed through mapa)
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint32_t own = smem_u32(bar);
+    uint32_t peer;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(own), "r"(1u));
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(own) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer) : "memory");
+}
+
+#define PDBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+
+template <typename YT>
+__global__ void __launch_bounds__(F16_THREADS, 1)
+qlinear_f16_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const F16Params2 p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int x_stage_bytes = (p.BN / 2) * XK * 2;   // this CTA's half of the activation tile
+    uint8_t* sW = smem;
+    uint8_t* sX = smem + (size_t)W_STAGES * W_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sX + (size_t)p.x_stages * x_stage_bytes);
+    uint64_t* w_full = bars;                   // [W_STAGES]
+    uint64_t* w_empty = w_full + W_STAGES;     // [W_STAGES]
+    uint64_t* a_full = w_empty + W_STAGES;     // [A_BUFS]
+    uint64_t* a_empty = a_full + A_BUFS;       // [A_BUFS]
+    uint64_t* d_full = a_empty + A_BUFS;       // [1]
+    uint64_t* d_empty = d_full + 1;            // [1]
+    uint64_t* x_full = d_empty + 1;            // [x_stages]
+    uint64_t* x_empty = x_full + p.x_stages;   // [x_stages]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_empty + p.x_stages);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_ctarank();   // 0: pair leader (issues the MMAs), 1: peer
+    if (threadIdx.x == 0) PDBG(0);
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < W_STAGES; ++s) {
+            mbar_init(&w_full[s], 1);
+            mbar_init(&w_empty[s], CONV_WARPS);
+        }
+        for (int s = 0; s < A_BUFS; ++s) {
+            mbar_init(&a_full[s], 2 * CONV_WARPS);   // leader's copy counts both CTAs' converter warps
+            mbar_init(&a_empty[s], 1);
+        }
+        mbar_init(d_full, 1);
+        mbar_init(d_empty, 8);                    // leader's copy counts both CTAs' epilogue warps
+        for (int s = 0; s < p.x_stages; ++s) {
+            mbar_init(&x_full[s], 1);
+            mbar_init(&x_empty[s], 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // both CTAs' barriers are initialised before anything arrives on them remotely
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a0 = tmem_base + D_COLS;
+    if (threadIdx.x == 0) PDBG(1);
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+            int ws = 0, xs = 0;
+            uint32_t wph = 0, xph = 0;
+            bool ok = true, waited = false;
+            int nx = 0;
+            PieceSched sched(p);
+            Piece pc;
+            while (ok && sched.next(pc)) {
+                const int t = pc.u % p.tiles_w, j = pc.u / p.tiles_w;
+                for (int s = pc.s0; s < pc.s1 && ok; ++s) {
+                    if (!mbar_wait(&w_empty[ws], wph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+                    mbar_expect_tx(&w_full[ws], (uint32_t)W_STAGE_BYTES);
+                    tma_load_2d(sW + (size_t)ws * W_STAGE_BYTES, &map_w, s * WK, (2 * t + rank) * BM, &w_full[ws], pol_w);
+                    if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
+                    if (!waited) {  // the weights never depend on earlier kernels; the activations may
+                        pdl_wait();
+                        waited = true;
+                    }
+                    for (int h = 0; h < WK / XK; ++h) {
+                        if (!mbar_wait(&x_empty[xs], xph ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
+                        if (rank == 0) mbar_expect_tx(&x_full[xs], (uint32_t)(2 * x_stage_bytes));   // both halves land on the leader's barrier
+                        tma_load_2d_pair(sX + (size_t)xs * x_stage_bytes, &map_x, s * WK + h * XK, j * p.BN + rank * (p.BN / 2), &x_full[xs],
+                                         pol_x);
+                        if (++xs == p.x_stages) { xs = 0; xph ^= 1u; }
+                        ++nx;
+                        if (nx == 1) PDBG(2);
+                        if (nx == 17) PDBG(3);
+                        if (nx == 33) PDBG(4);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (pair leader only) -------------
+        if (lane == 0 && rank == 0) {
+            int ab = 0, xs = 0;
+            uint32_t aph = 0, xph = 0;
+            bool ok = true;
+            int i = 0;
+            PieceSched sched(p);
+            Piece pc;
+            for (; ok && sched.next(pc); ++i) {
+                if (!mbar_wait(d_empty, ((uint32_t)i & 1u) ^ 1u, abort_flag, p.status, 13)) { ok = false; break; }
+                tc_fence_after();
+                for (int s = pc.s0; s < pc.s1 && ok; ++s) {
+                    if (!mbar_wait(&a_full[ab], aph, abort_flag, p.status, 14)) { ok = false; break; }
+                    tc_fence_after();
+                    if (i == 0 && s == pc.s0) PDBG(5);
+                    if (i == 0 && s == pc.s0 + 8) PDBG(6);
+                    if (i == 0 && s == pc.s0 + 16) PDBG(7);
+                    const uint32_t a_tmem = tmem_a0 + (uint32_t)(ab * A_COLS);
+                    for (int h = 0; h < WK / XK; ++h) {
+                        if (!mbar_wait(&x_full[xs], xph, abort_flag, p.status, 15)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint64_t db = make_smem_desc(smem_u32(sX + (size_t)xs * x_stage_bytes));
+#pragma unroll
+                        for (int k16 = 0; k16 < XK / 16; ++k16)
+                            if (p.dbg_mode != 2) umma_f16_ts_pair(tmem_base, a_tmem + (uint32_t)((h * (XK / 16) + k16) * 8), db + (uint64_t)(2 * k16), p.idesc,
+                                        (s > pc.s0 || h > 0 || k16 > 0) ? 1u : 0u);
+                        umma_commit_pair(&x_empty[xs]);
+                        if (++xs == p.x_stages) { xs = 0; xph ^= 1u; }
+                    }
+                    umma_commit_pair(&a_empty[ab]);
+                    if (++ab == A_BUFS) { ab = 0; aph ^= 1u; }
+                }
+                if (ok) umma_commit_pair(d_full);
+            }
+        }
+    } else if (warp < 2 + CONV_WARPS) {
+        // ------------------------------ converters --------------------------------
+        // Warp pair (w, w+4) shares TMEM lane quarter q = w & 3; `half` picks k 0..63 or 64..127 of the stage.
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int r = q * 32 + lane;  // weight row inside the tile = TMEM lane
+        int ws = 0, ab = 0;
+        int ncv = 0;
+        uint32_t wph = 0, aph = 0;
+        bool ok = true;
+        PieceSched sched(p);
+        Piece pc;
+        while (ok && sched.next(pc)) {
+            for (int s = pc.s0; s < pc.s1 && ok; ++s) {
+                if (!mbar_wait(&w_full[ws], wph, abort_flag, p.status, 16)) { ok = false; break; }
+                if (threadIdx.x == 64) { ++ncv; if (ncv == 1) PDBG(8); if (ncv == 9) PDBG(9); if (ncv == 17) PDBG(10); }
+                // row r of the swizzled tile: logical 16-byte chunk c sits at physical chunk c ^ (r & 7)
+                const uint4* row = reinterpret_cast<const uint4*>(sW + (size_t)ws * W_STAGE_BYTES + (size_t)r * WK);
+                uint4 raw[4];
+                if (p.dbg_mode != 1) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) raw[c] = row[(half * 4 + c) ^ (r & 7)];
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) raw[c] = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&w_empty[ws]);  // this warp's share is in registers
+                if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
+                uint32_t cv[32];
+                if (p.dbg_mode != 1) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[c], cv + 8 * c);
+                }
+                if (!mbar_wait(&a_empty[ab], aph ^ 1u, abort_flag, p.status, 17)) { ok = false; break; }
+                tc_fence_after();
+                if (p.dbg_mode != 1) {
+                    tmem_st32(tmem_a0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * A_COLS + half * 32), cv);
+                    tmem_st_wait();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(&a_full[ab]);
+                if (threadIdx.x == 64 && ncv == 9) PDBG(11);
+                if (++ab == A_BUFS) { ab = 0; aph ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        YT* y = reinterpret_cast<YT*>(p.y);
+        pdl_wait();
+        bool ok = true;
+        int i = 0;
+        PieceSched sched(p);
+        Piece pc;
+        for (; ok && sched.next(pc); ++i) {
+            const int t = pc.u % p.tiles_w, j = pc.u / p.tiles_w;
+            const int n = (2 * t + rank) * BM + r;
+            const bool row_ok = n < p.N;
+            const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+            if (!mbar_wait(d_full, (uint32_t)i & 1u, abort_flag, p.status, 18)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+            if (pc.nseg == 1) {
+                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const int m = j * p.BN + c0 + e;
+                            if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, __uint_as_float(v[e]) * sc);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(d_empty);
+            } else {
+                // a K-slice of a shared tile: add it into the tile's f32 sums ([col/4][row] x float4, so a warp's
+                // vector reductions cover 512 contiguous bytes); the last CTA to arrive writes y.
+                float* tile = p.sums + (size_t)(pc.lu * 2 + rank) * p.BN * BM;
+                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + (uint32_t)c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; e += 4)
+                        red_add_f32x4(tile + ((size_t)((c0 + e) / 4) * BM + r) * 4, __uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                      __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(d_empty);
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 32 * (2 + CONV_WARPS)) {
+                    const unsigned prev = atomicAdd(p.counters + pc.lu * 2 + rank, 1u);
+                    *last_flag = (prev == (unsigned)(pc.nseg - 1)) ? 1 : 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                        float4 f[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) f[e] = __ldcg(reinterpret_cast<const float4*>(tile) + (size_t)(c0 / 4 + e) * BM + r);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            __stcg(reinterpret_cast<float4*>(tile) + (size_t)(c0 / 4 + e) * BM + r, make_float4(0.f, 0.f, 0.f, 0.f));
+                        if (row_ok) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float vals[4] = {f[e].x, f[e].y, f[e].z, f[e].w};
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const int m = j * p.BN + c0 + e * 4 + k;
+                                    if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, vals[k] * sc);
+                                }
+                            }
+                        }
+                    }
+                    if (threadIdx.x == 32 * (2 + CONV_WARPS)) p.counters[pc.lu * 2 + rank] = 0u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // neither CTA lets go of its tensor memory or shared memory while the other may still use it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+}  // namespace
+
+namespace rusty {
+
+bool f16tc2_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a) {
+    // opt-in (RUSTY_CTA_PAIRS=1): correct, but so far slower than the single-CTA kernel
+    static const bool off = getenv("RUSTY_CTA_PAIRS") == nullptr;
+    if (off || ctx->sm_count < 2) return false;
+    if (!encode_tiled_fn()) return false;
+    if (a.layout != RUSTY_CUDA_LAYOUT_NK || a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
+    if (a.x_dtype != RUSTY_CUDA_BF16) return false;
+    if (a.K % 16 != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(a.w) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return false;
+    return true;
+}
+
+int launch_f16tc2(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
+    F16Params2 p{};
+    p.scales = a.scales;
+    p.y = a.y;
+    p.Mx = (int)a.M;
+    p.N = (int)a.N;
+    p.K = (int)a.K;
+    p.BN = a.M >= 256 ? 256 : (int)((a.M + 31) / 32 * 32);
+    p.tiles_w = (p.N + 2 * BM - 1) / (2 * BM);   // pair tiles of 256 weight rows
+    p.tiles_n = (p.Mx + p.BN - 1) / p.BN;
+    p.nws = (p.K + WK - 1) / WK;
+    p.ldy = (int)a.ldy;
+    p.y_col0 = (int)a.y_col0;
+    p.status = ctx->status_dev;
+    p.dbg = (long long*)ctx->tc_dbg;
+    {
+        static const int dbg = getenv("RUSTY_F16_DBG") ? atoi(getenv("RUSTY_F16_DBG")) : 0;
+        p.dbg_mode = dbg;
+    }
+    // bf16 A x bf16 B -> f32, M = 256 over the CTA pair: c_format=F32(1)@4, a_format=BF16(1)@7, b_format=BF16(1)@10, N>>3 @17, M>>4 @24
+    p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+    const size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
+    const size_t x_stage = (size_t)(p.BN / 2) * XK * 2;
+    int xs = (int)((budget - 1024 - 512 - (size_t)W_STAGES * W_STAGE_BYTES) / x_stage);
+    if (xs > 10) xs = 10;
+    if (xs < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "f16 pair kernel: tile does not fit shared memory");
+    p.x_stages = xs;
+    const size_t smem = 1024 + (size_t)W_STAGES * W_STAGE_BYTES + (size_t)xs * x_stage + (size_t)(2 * W_STAGES + 2 * A_BUFS + 2 + 2 * xs) * 8 + 64;
+
+    CUtensorMap map_w, map_x;
+    if (!make_map_u8(&map_w, a.w, a.N, a.K, BM) || !make_map_bf16(&map_x, a.x, a.M, a.K, (uint32_t)(p.BN / 2)))
+        return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "f16 pair kernel: cuTensorMapEncodeTiled failed");
+    const int units = p.tiles_w * p.tiles_n;
+    int pairs = ctx->sm_count / 2;
+    if (pairs > units) pairs = units;
+    // whole waves of pair tiles are taken tile-per-pair; the remainder is cut along K over all pairs (>= 4 stages each)
+    p.sk_units = units % pairs;
+    p.dp_units = units - p.sk_units;
+    p.sk_per_cta = p.sk_ctas = 0;
+    p.sums = nullptr;
+    p.counters = nullptr;
+    if (p.sk_units > 0) {
+        float* sums = nullptr;
+        unsigned int* counters = nullptr;
+        size_t sums_bytes = 0, cnt_bytes = 0;
+        tc_workspace_sums(ctx, &sums, &sums_bytes, &counters, &cnt_bytes);
+        const size_t need = (size_t)p.sk_units * 2 * p.BN * BM * 4;
+        if (sums && need <= sums_bytes && (size_t)p.sk_units * 8 <= cnt_bytes) {
+            const int work = p.sk_units * p.nws;
+            p.sk_per_cta = (work + pairs - 1) / pairs;
+            if (p.sk_per_cta < 4) p.sk_per_cta = 4;
+            p.sk_ctas = (work + p.sk_per_cta - 1) / p.sk_per_cta;
+            p.sums = sums;
+            p.counters = counters;
+        } else {
+            p.dp_units = units;
+            p.sk_units = 0;
+        }
+    }
+    const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
+    auto kern = yb ? qlinear_f16_tc2_kernel<__nv_bfloat16> : qlinear_f16_tc2_kernel<float>;
+    static size_t smem_set[2][16] = {{0}};
+    size_t& cur = smem_set[yb ? 1 : 0][ctx->device & 15];
+    if (smem > cur) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_f16_tc2: cudaFuncSetAttribute");
+        cur = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(F16_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, p);
+    if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_f16_tc2");
+    return after_launch(ctx, "qlinear_f16_tc2");
+}
+
+}  // namespace rusty

@@ -146,6 +146,9 @@ int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 bool f16tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 uint32_t f16tc_min_rows();
+// The same with CTA pairs (tcgen05 cta_group::2): each CTA loads half of the activation tile.
+bool f16tc2_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
+int launch_f16tc2(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 
 const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 // Forward into columns [y_col0, y_col0 + N) of a y whose rows are ldy elements apart.

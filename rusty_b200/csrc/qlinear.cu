@@ -41,6 +41,7 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
     a.x_dtype = x_dtype;
     a.y_dtype = y_dtype;
     a.M = M;
+    if (f16tc2_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16_pair";
     if (f16tc_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16";
     if (tc_supported(ql->ctx, a) && M >= tc_min_rows()) return "tcgen05";
     if (gemv_tma_supported(ql->ctx, a)) return "gemv_tma";
@@ -82,6 +83,7 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
     a.ldy = ldy;
     a.y_col0 = y_col0;
     DeviceGuard g(ctx->device);
+    if (f16tc2_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc2(ctx, a);
     if (f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
     if (tc_supported(ctx, a) && M >= tc_min_rows()) return launch_tc(ctx, a);
     if (gemv_tma_supported(ctx, a)) return launch_gemv_tma(ctx, a);

@@ -281,7 +281,7 @@ def test_prefill_f16_shapes(ctx, engine, oracle, M, K, N):
     x, q, s = sym_row_linear(5 * K + N + M, M, K, N)
     xb = bf16_bits_to_f32(f32_to_bf16_bits(x))
     ql = QLinear.from_host(ctx, q, s)
-    assert ql.plan(M, DType.BF16, DType.BF16) == "tcgen05_f16"
+    assert ql.plan(M, DType.BF16, DType.BF16) in ("tcgen05_f16", "tcgen05_f16_pair")
     got32 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.FP32)
     got16 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.BF16)
     ctx.sync()
