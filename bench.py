@@ -219,6 +219,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (for profiling captures only)")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-Linear and CPU legs")
+    ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
+                    help="N > 1: how a rank's output columns reach the other ranks: stores from the kernel's epilogue "
+                         "into every rank's memory (push) or an NCCL all-gather after each Linear (nccl)")
     ap.add_argument("--single", default=None, metavar="MxKxN:f32|bf16",
                     help="run ONE fused linear of this shape --steps times on rotating weight copies and print its "
                          "timing (small case for profiler captures; not the benchmark line)")
@@ -265,8 +268,8 @@ def main():
     shape = STACKS[stack_name]
     stack = LinearStack(ctx, shape, M, DType.FP32, DType.FP32, seed=0, rank=rank, world=world, layers=args.layers)
     if world > 1:
-        from rusty_b200.shard import ShardedStack
-        runner = ShardedStack(stack, dist)
+        from rusty_b200.shard import PushedStack, ShardedStack
+        runner = PushedStack(stack, dist) if args.exchange == "push" else ShardedStack(stack, dist)
     else:
         runner = stack
     runner.capture()
@@ -333,7 +336,9 @@ def main():
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "desc": desc, "batch_rows": M, "linears_per_step": stack.num_linears(),
                    "weights": "int8 [out,in], f32 scale per output row; q|k|v and gate|up stored back to back and run as one Linear each", "activations": "f32 in, f32 out, fp32 accumulate",
-                   "parallelism": "1 GPU" if world == 1 else f"output-feature shards x{world} + all-gather",
+                   "parallelism": ("1 GPU" if world == 1 else f"output-feature shards x{world}, " + (
+                       "outputs stored into every rank's memory by the kernel epilogue (NVLink peer stores)"
+                       if args.exchange == "push" else "NCCL all-gather after each Linear")),
                    "l2": "inputs larger than L2: each step streams %.2f GB of weights per GPU" % (stack.weight_bytes() / 1e9),
                    "kernels": runner.plans(), "layers": stack.layers},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -370,6 +375,8 @@ def main():
         print(json.dumps(line), flush=True)
     x_host.free()
     y_host.free()
+    if hasattr(runner, "close"):
+        runner.close()
     if dist is not None:
         dist.destroy_process_group()
 

@@ -244,6 +244,44 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_sharded_batch(rusty_cuda_ctx* ctx,
                                                             rusty_cuda_buf* gather_ws, rusty_cuda_buf* const* ys,
                                                             int y_dtype);
 
+/* ---- exchange by peer stores over NVLink (no counterpart in the reference) ----
+ * The second multi-GPU form of Linear::forward (rusty-graph/src/lib.rs:69-70):
+ * instead of an all-gather after the kernel, each rank's kernel stores its
+ * output columns straight into every rank's copy of y.  An arena is one device
+ * allocation with the same layout on every rank (one process per GPU, one node);
+ * ranks swap the 64-byte handles over any host channel and attach.
+ *
+ * Protocol: every rank enqueues the same sequence of pushed forwards on an
+ * arena.  y_full of a pushed forward is complete on this rank once the next
+ * pushed forward on the arena, or rusty_cuda_arena_wait, has run; it may be
+ * read until the following pushed forward is enqueued and may be the output of
+ * a pushed forward again from the second-next on.  Waits for other ranks are
+ * bounded (environment RUSTY_PEER_WAIT_MS, default 5000): when one runs out,
+ * the next rusty_cuda_sync returns RUSTY_CUDA_ERR_TIMEOUT and the context stays
+ * usable.  Keep an arena alive until every rank has stopped pushing to it. */
+#define RUSTY_CUDA_IPC_HANDLE_BYTES 64
+typedef struct rusty_cuda_arena rusty_cuda_arena;
+RUSTY_CUDA_API int rusty_cuda_arena_create(rusty_cuda_ctx* ctx, size_t bytes, int nranks, int rank, rusty_cuda_arena** out);
+/* Writes this arena's IPC handle (RUSTY_CUDA_IPC_HANDLE_BYTES bytes). */
+RUSTY_CUDA_API int rusty_cuda_arena_export(const rusty_cuda_arena* arena, void* handle64);
+/* `handles`: nranks handles back to back, in rank order (the own slot is ignored). */
+RUSTY_CUDA_API int rusty_cuda_arena_attach(rusty_cuda_arena* arena, const void* handles);
+/* A buffer object over [offset, offset+bytes) of the arena's data region (offset % 256 == 0);
+ * use the same offsets on every rank.  Released with rusty_cuda_buf_release. */
+RUSTY_CUDA_API int rusty_cuda_arena_buf(rusty_cuda_arena* arena, size_t offset, size_t bytes, rusty_cuda_buf** out);
+/* Enqueues a wait until the pushes of all ranks enqueued so far have landed in this rank's arena. */
+RUSTY_CUDA_API int rusty_cuda_arena_wait(rusty_cuda_ctx* ctx, rusty_cuda_arena* arena);
+RUSTY_CUDA_API int rusty_cuda_arena_destroy(rusty_cuda_arena* arena);
+/* y_full[M, G*Nl] (a buffer of the arena): columns [rank*Nl, (rank+1)*Nl) = x[M,K] . shard^T, written here
+ * and into every other rank's arena at the same offset. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_forward_pushed(rusty_cuda_ctx* ctx, rusty_cuda_arena* arena,
+                                                     const rusty_cuda_qlinear* ql_shard, const rusty_cuda_buf* x, int x_dtype,
+                                                     uint32_t M, rusty_cuda_buf* y_full, int y_dtype);
+RUSTY_CUDA_API int rusty_cuda_qlinear_forward_pushed_batch(rusty_cuda_ctx* ctx, rusty_cuda_arena* arena, size_t n,
+                                                           const rusty_cuda_qlinear* const* ql_shards,
+                                                           const rusty_cuda_buf* const* xs, int x_dtype, uint32_t M,
+                                                           rusty_cuda_buf* const* ys, int y_dtype);
+
 /* ---- stream capture and timing ---------------------------------------------
  * rusty submits one command buffer per op (lib.rs:4452); a decode step here is
  * hundreds of short kernels, so the sequence can be recorded once into a CUDA

@@ -82,6 +82,14 @@ SIGNATURES = {
     "rusty_cuda_comm_check": ([_vp], _int),
     "rusty_cuda_qlinear_forward_sharded": ([_vp, _vp, _vp, _vp, _int, _u32, _vp, _vp, _int], _int),
     "rusty_cuda_qlinear_forward_sharded_batch": ([_vp, _vp, _sz, _vpp, _vpp, _int, _u32, _vp, _vpp, _int], _int),
+    "rusty_cuda_arena_create": ([_vp, _sz, _int, _int, _vpp], _int),
+    "rusty_cuda_arena_export": ([_vp, _vp], _int),
+    "rusty_cuda_arena_attach": ([_vp, _vp], _int),
+    "rusty_cuda_arena_buf": ([_vp, _sz, _sz, _vpp], _int),
+    "rusty_cuda_arena_wait": ([_vp, _vp], _int),
+    "rusty_cuda_arena_destroy": ([_vp], _int),
+    "rusty_cuda_qlinear_forward_pushed": ([_vp, _vp, _vp, _vp, _int, _u32, _vp, _int], _int),
+    "rusty_cuda_qlinear_forward_pushed_batch": ([_vp, _vp, _sz, _vpp, _vpp, _int, _u32, _vpp, _int], _int),
     "rusty_cuda_graph_begin": ([_vp], _int),
     "rusty_cuda_graph_end": ([_vp, _vpp], _int),
     "rusty_cuda_graph_launch": ([_vp, _vp], _int),

@@ -66,13 +66,22 @@ __device__ __forceinline__ float x_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { retu
 
 template <typename XT, int D>
 __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ x, int8_t* __restrict__ xq,
-                                                         float* __restrict__ inv_s, int M, int Mpad, int K) {
+                                                         float* __restrict__ inv_s, int M, int Mpad, int K,
+                                                         const PeerPush push, long long* dbg) {
     const int m = blockIdx.x;
     __shared__ float red[8];
     __shared__ float s_scale;
     const int tid = threadIdx.x;
+    if (dbg && tid == 0 && m == 0) dbg[0] = (long long)globaltimer_ns();
     pdl_launch_dependents();
-    pdl_wait();  // x may come from the previous kernel, and that kernel may still be reading the digit planes
+    pdl_wait();
+    if (dbg && tid == 0 && m == 0) dbg[1] = (long long)globaltimer_ns();  // x may come from the previous kernel, and that kernel may still be reading the digit planes
+    if (push.nranks > 1) {
+        // x may hold columns pushed by the other ranks, and the GEMM that follows overwrites their copies of y:
+        // wait until every rank has finished (and delivered) all earlier pushes
+        if (tid == 0) peer_wait_all(push, 30);
+        __syncthreads();
+    }
     if (m >= M) {
         for (int k = tid * 4; k < K; k += 256 * 4)
 #pragma unroll
@@ -122,6 +131,7 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
 #pragma unroll
         for (int d = 0; d < D; ++d) *reinterpret_cast<uint32_t*>(xq + (size_t)(d * Mpad + m) * K + k) = packed[d];
     }
+    if (dbg && tid == 0 && m == 0) dbg[2] = (long long)globaltimer_ns();
 }
 
 // ----------------------------------------------------------------------------
@@ -147,6 +157,7 @@ struct TcParams {
     uint32_t tmem_cols;
     rusty_cuda_dev_status* status;
     long long* dbg;          // optional per-CTA timeline (16 slots each), null in normal use
+    PeerPush push;           // nranks > 1: every output is also stored into the other ranks' arenas
     // Fused small-batch mode (M <= 4): no pre-pass and no digit planes in global memory.  The CTA finds the row
     // maxima of x itself and its epilogue warps write the digit tile of every stage straight into shared memory.
     int fused;               // 1: x_raw is used, Mpad == M, D == 4, NB == 16
@@ -205,14 +216,25 @@ struct Sched {
 
 // Digits -> one exact 64-bit integer -> f32 (one rounding) -> row factor (a power
 // of two, exact) -> weight scale (one rounding).
+// The other ranks' arenas as byte offsets from this rank's (exchange by peer stores), kept in shared memory: indexing
+// an array inside the kernel parameter with a run-time index makes the compiler copy it to local memory at every use.
+struct PeerOut {
+    int n;                   // number of other ranks (0: no exchange)
+    const long long* delta;  // [n] in shared memory
+};
 template <typename YT>
-__device__ __forceinline__ void finalize_store_f(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, float row_factor) {
-    const float v = __ll2float_rn(acc) * row_factor;
-    store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, v * scale_n);
+__device__ __forceinline__ void finalize_store_f(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, float row_factor,
+                                                 const PeerOut& po) {
+    const float v = __ll2float_rn(acc) * row_factor * scale_n;
+    YT* dst = y + (size_t)m * p.ldy + p.y_col0 + n;
+    store_y<YT>(dst, v);
+    // exchange fused into the epilogue: the same element of every other rank's y, over NVLink
+    for (int g = 0; g < po.n; ++g) store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<char*>(dst) + po.delta[g]), v);
 }
 template <typename YT>
-__device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n) {
-    finalize_store_f<YT>(p, y, n, m, acc, scale_n, __ldg(p.row_factor + m));
+__device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, const float* s_rowf,
+                                               const PeerOut& po) {
+    finalize_store_f<YT>(p, y, n, m, acc, scale_n, s_rowf[m], po);
 }
 
 // Four consecutive activations x[m, k..k+3] as f32 (zeros beyond K); K % 4 == 0.
@@ -226,11 +248,12 @@ __device__ __forceinline__ float4 load_x4(const TcParams& p, int m, int k) {
     return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_raw) + (size_t)m * p.K + k);
 }
 
-#define DBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+#define DBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = (long long)globaltimer_ns(); } while (0)
 
 template <typename YT>
 __global__ void __launch_bounds__(TC_THREADS, 2)
-qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                     const __grid_constant__ TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // carve: [A stages][B stages][barriers]
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -253,6 +276,15 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     float* s_factor = s_scale + 4;                             // [4] 1/s_m * 128^-3
     uint64_t* dig_ready = reinterpret_cast<uint64_t*>(s_factor + 4);  // fused mode: the digit tiles of x are in place
 
+    __shared__ float s_rowf[64];  // 1/s_m * 128^-(D-1) per activation row of this pass (at most 64 rows)
+    __shared__ long long s_peer_delta[PEER_MAX_RANKS];
+    if (threadIdx.x == 0) {
+        int k = 0;  // the other ranks, compacted (own rank left out); static indices into the parameter
+#pragma unroll
+        for (int g = 0; g < PEER_MAX_RANKS; ++g)
+            if (g < p.push.nranks && g != p.push.rank) s_peer_delta[k++] = p.push.delta[g];
+    }
+    const PeerOut po = {p.push.nranks > 1 ? p.push.nranks - 1 : 0, s_peer_delta};  // visible after the set-up barrier below
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) DBG(0);
     pdl_launch_dependents();
@@ -390,6 +422,12 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         pdl_wait();                             // x, y, the sums and the counters belong to earlier kernels until now
         bool ok = true;
         const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
+        if (!p.fused) {
+            // per-row factors of the pre-pass: once into shared memory (a load from global memory per output costs
+            // an L2 round trip each time)
+            if (et < p.Mpad) s_rowf[et] = __ldcg(p.row_factor + et);
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+        }
         if (p.fused) {
             // zero every digit tile once (rows that hold no digit plane stay zero for the whole kernel)
             for (int i = et; i < p.kb_total * b_stage_bytes / 16; i += EPI_THREADS) reinterpret_cast<uint4*>(sB)[i] = make_uint4(0, 0, 0, 0);
@@ -505,7 +543,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
                 if (sg.nseg == 1) {
                     if (row_ok)
-                        for (int m = 0; m < p.M; ++m) finalize_store_f<YT>(p, y, n, m, acc[m], sc, s_factor[m]);
+                        for (int m = 0; m < p.M; ++m) finalize_store_f<YT>(p, y, n, m, acc[m], sc, s_factor[m], po);
                 } else {
                     // a piece of a K-cut tile: 64-bit integer reductions straight from registers (exact, any order)
                     const int lt = sg.t - p.dp_tiles;
@@ -529,7 +567,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                             for (int m = 0; m < 4; ++m)
                                 if (m < p.M) {
                                     __stcg(tile_sum + (size_t)m * BM + r, 0ull);
-                                    finalize_store_f<YT>(p, y, n, m, tot[m], sc, s_factor[m]);
+                                    finalize_store_f<YT>(p, y, n, m, tot[m], sc, s_factor[m], po);
                                 }
                         }
                         if (threadIdx.x == 64) p.counters[sg.t] = 0u;
@@ -552,7 +590,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 #pragma unroll
                                 for (int d = 1; d < 4; ++d)
                                     if (d < p.D) acc = acc * 128 + c[d][mm];
-                                finalize_store<YT>(p, y, n, m0 + mm, acc, sc);
+                                finalize_store<YT>(p, y, n, m0 + mm, acc, sc, s_rowf, po);
                             }
                         }
                     }
@@ -614,6 +652,11 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     // every piece has been added: turn the sums into y and leave zeros behind for the next use
                     __threadfence();
                     const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+                    if (threadIdx.x == 64) DBG(10);
+                    // The sums come back in batches of independent loads (one L2 round trip per batch) and are parked in
+                    // this thread's column of the staging tile, which the bulk reduce has finished reading; the
+                    // conversion then runs as a rolled loop over shared memory.  Straight-line code that runs once
+                    // per kernel is paid for in instruction fetches, not in issue slots, so it is kept short.
                     for (int mp0 = 0; mp0 * 2 < p.Mpad; mp0 += 8) {
                         int4 ld[8];
 #pragma unroll
@@ -621,16 +664,20 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                             ld[h] = (mp0 + h) * 2 < p.Mpad ? __ldcg(tile_sum + (size_t)(mp0 + h) * BM + r) : make_int4(0, 0, 0, 0);
 #pragma unroll
                         for (int h = 0; h < 8; ++h)
-                            if ((mp0 + h) * 2 < p.Mpad) __stcg(tile_sum + (size_t)(mp0 + h) * BM + r, make_int4(0, 0, 0, 0));
-                        if (row_ok) {
-#pragma unroll
-                            for (int h = 0; h < 8; ++h) {
-                                const int m = (mp0 + h) * 2;
-                                if (m < p.M) finalize_store<YT>(p, y, n, m, ((long long)ld[h].y << 32) | (unsigned int)ld[h].x, sc);
-                                if (m + 1 < p.M) finalize_store<YT>(p, y, n, m + 1, ((long long)ld[h].w << 32) | (unsigned int)ld[h].z, sc);
+                            if ((mp0 + h) * 2 < p.Mpad) {
+                                __stcg(tile_sum + (size_t)(mp0 + h) * BM + r, make_int4(0, 0, 0, 0));
+                                stage_red[(size_t)(mp0 + h) * BM + r] = ld[h];
                             }
+                    }
+                    if (threadIdx.x == 64) DBG(12);
+                    if (row_ok) {
+#pragma unroll 2
+                        for (int m = 0; m < p.M; ++m) {
+                            const longlong2 two = *reinterpret_cast<const longlong2*>(&stage_red[(size_t)(m >> 1) * BM + r]);
+                            finalize_store<YT>(p, y, n, m, (m & 1) ? two.y : two.x, sc, s_rowf, po);
                         }
                     }
+                    if (threadIdx.x == 64) DBG(13);
                     if (threadIdx.x == 64) p.counters[sg.t] = 0u;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // last_flag is reused by the next segment
@@ -646,6 +693,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         tc_fence_after();
         tmem_dealloc(tmem_base, p.tmem_cols);
     }
+    if (threadIdx.x == 0) peer_signal_cta_done(p.push, gridDim.x);  // after the barrier: every store of this CTA is issued
     if (threadIdx.x == 32) DBG(15);
 }
 
@@ -665,10 +713,11 @@ int pick_digits(int x_dtype, uint32_t rows) {
 }
 
 template <typename XT>
-cudaError_t launch_digitize(rusty_cuda_ctx* ctx, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D) {
+cudaError_t launch_digitize(rusty_cuda_ctx* ctx, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D,
+                            const PeerPush& push, long long* dbg) {
     if (D == 4)
-        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K);
-    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K);
+        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg);
+    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg);
 }
 
 }  // namespace
@@ -728,6 +777,9 @@ bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     return true;
 }
 
+// The kernel pair below stores into the peers' arenas itself, except in the small-batch mode that has no pre-pass.
+bool tc_pushes_fused(uint32_t M) { return M > 4; }
+
 // One launch pair (digitise + GEMM) for up to 64 activation rows.
 static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void* x, void* y, uint32_t rows) {
     // Small batches whose activations a CTA can scan by itself (<= 64 KiB) skip the pre-pass kernel.
@@ -746,9 +798,20 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
 
     cudaError_t le = cudaSuccess;
     int rc = RUSTY_CUDA_OK;
+    // development aid: each launch pair writes its timeline into the next 152 x 16 slots of the attached buffer
+    long long* dbg = nullptr;
+    if (ctx->tc_dbg) {
+        dbg = (long long*)ctx->tc_dbg + (size_t)ctx->tc_dbg_seq * 152 * 16;
+        ctx->tc_dbg_seq = (ctx->tc_dbg_seq + 1) % (ctx->tc_dbg_slots > 0 ? ctx->tc_dbg_slots : 1);
+    }
+    PeerPush push{};
+    if (a.push && a.push->nranks > 1) {
+        if (fused) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "tensor-core path: the small-batch mode does not push to peers");
+        push = *a.push;
+    }
     if (!fused) {
-        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D)
-                                          : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D);
+        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr)
+                                          : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr);
         if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
         rc = after_launch(ctx, "digitize_x");
         if (rc) return rc;
@@ -803,7 +866,8 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
     p.status = ctx->status_dev;
-    p.dbg = (long long*)ctx->tc_dbg;
+    p.dbg = dbg;
+    p.push = push;
     p.fused = fused ? 1 : 0;
     p.x_bf16 = a.x_dtype == RUSTY_CUDA_BF16 ? 1 : 0;
     p.x_raw = x;
@@ -867,6 +931,8 @@ int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
 extern "C" RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf) {
     if (!ctx) return RUSTY_CUDA_ERR_INVALID_OPERATION;
     ctx->tc_dbg = buf ? buf->ptr : nullptr;
+    ctx->tc_dbg_seq = 0;
+    ctx->tc_dbg_slots = buf ? (int)(buf->bytes / (152 * 16 * 8)) : 0;
     return RUSTY_CUDA_OK;
 }
 
@@ -957,7 +1023,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: clearing the scratch");
 
     const int Mi = (int)M, Mpad = 8, D = 4, NB = 32;
-    e = launch_pdl(digitize_x_kernel<float, 4>, dim3(Mpad), dim3(256), 0, st, x_f32, xq, factor, Mi, Mpad, (int)K);
+    e = launch_pdl(digitize_x_kernel<float, 4>, dim3(Mpad), dim3(256), 0, st, x_f32, xq, factor, Mi, Mpad, (int)K, PeerPush{}, (long long*)nullptr);
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: digitize_x");
 
     TcParams p{};

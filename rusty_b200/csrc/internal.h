@@ -44,6 +44,7 @@ struct rusty_cuda_ctx {
     void* tc_ws = nullptr;
     size_t tc_ws_bytes = 0;
     void* tc_dbg = nullptr;  // optional kernel timeline buffer (development aid)
+    int tc_dbg_seq = 0, tc_dbg_slots = 0;
     // stream capture in progress (rusty_cuda_graph_begin .. _end)
     bool capturing = false;
     uint64_t launches_at_capture = 0;
@@ -112,6 +113,23 @@ int launch_dequantize_u8(rusty_cuda_ctx* ctx, const uint32_t* in, size_t in_word
 int launch_affine_dequantize_g64(rusty_cuda_ctx* ctx, const uint8_t* w, const float* scales, const float* biases,
                                  float* out, size_t n);
 
+// Exchange by peer stores (peer.cu): what a kernel needs to write its outputs into the other ranks' copies of y and
+// to tell them so.  Every rank owns an arena with the same layout; rank g's arena is mapped here at peer_base[g].
+//   ctl[0..7]  flags: ctl[g] = number of pushes of rank g that have landed in THIS arena (written by rank g)
+//   ctl[16]    epoch: pushes this rank has completed (local)
+//   ctl[17]    CTAs of the running push that have finished (local, zero between kernels)
+constexpr int PEER_MAX_RANKS = 8;
+constexpr int PEER_CTL_EPOCH = 16;
+constexpr int PEER_CTL_DONE = 17;
+struct PeerPush {
+    int nranks, rank;                            // nranks <= 1: nothing to push, nothing to wait for
+    unsigned int* ctl;                           // this rank's control block
+    unsigned int* peer_ctl[PEER_MAX_RANKS];      // every rank's control block as mapped in this process (own included)
+    long long delta[PEER_MAX_RANKS];             // bytes from an address in this arena to the same place in rank g's
+    unsigned long long wait_ns;                  // limit of a wait for the other ranks
+    rusty_cuda_dev_status* status;
+};
+
 struct QLinearArgs {
     const uint8_t* w;
     const float* scales;
@@ -125,6 +143,9 @@ struct QLinearArgs {
     int y_dtype;
     uint32_t ldy;    // row stride of y in elements (>= N)
     uint32_t y_col0; // first output column written (for shards writing into a wider y)
+    // Non-null: y lies in a peer arena; the kernel also stores every output into the other ranks' arenas and
+    // signals them (honoured by the kernels for which qlinear_pushes_fused() is true).
+    const PeerPush* push = nullptr;
 };
 
 bool gemv_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
@@ -141,6 +162,7 @@ int tc_workspace_reserve(rusty_cuda_ctx* ctx);
 void tc_workspace_release(rusty_cuda_ctx* ctx);
 void tc_workspace_sums(rusty_cuda_ctx* ctx, float** sums, size_t* sums_bytes, unsigned int** counters, size_t* cnt_bytes);
 int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
+bool tc_pushes_fused(uint32_t M);
 
 // Prefill path: int8 -> fp16 into tensor memory, bf16 activations (tcgen05 kind::f16).
 bool f16tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
@@ -150,10 +172,13 @@ uint32_t f16tc_min_rows();
 bool f16tc2_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 int launch_f16tc2(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 
+// True when the kernel chosen for this shape stores into the peers' arenas itself.
+bool qlinear_pushes_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 // Forward into columns [y_col0, y_col0 + N) of a y whose rows are ldy elements apart.
 int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
-                         uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0);
+                         uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0,
+                         const PeerPush* push = nullptr);
 
 }  // namespace rusty
 

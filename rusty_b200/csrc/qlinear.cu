@@ -49,8 +49,12 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
     return "unsupported";
 }
 
+bool qlinear_pushes_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype) {
+    return strcmp(qlinear_plan(ql, x_dtype, M, y_dtype), "tcgen05") == 0 && tc_pushes_fused(M);
+}
+
 int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
-                         uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0) {
+                         uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0, const PeerPush* push) {
     if (!ql || !x || !y) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: null argument");
     if (ql->ctx != ctx) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: object belongs to another context");
     size_t xs = dtype_size(x_dtype), ys = dtype_size(y_dtype);
@@ -82,6 +86,11 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
     a.y_dtype = y_dtype;
     a.ldy = ldy;
     a.y_col0 = y_col0;
+    if (push && push->nranks > 1) {
+        if (!qlinear_pushes_fused(ql, x_dtype, M, y_dtype))
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: the kernel for this shape does not push to peers");
+        a.push = push;
+    }
     DeviceGuard g(ctx->device);
     if (f16tc2_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc2(ctx, a);
     if (f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);

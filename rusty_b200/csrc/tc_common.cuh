@@ -3,10 +3,15 @@
 #pragma once
 
 #include <cuda.h>
+#include <cstdlib>
 
 #include "internal.h"
 
 namespace rusty_tc {
+using rusty::PeerPush;
+using rusty::PEER_CTL_EPOCH;
+using rusty::PEER_CTL_DONE;
+using rusty::PEER_MAX_RANKS;
 
 constexpr long long WAIT_LIMIT_CYCLES = 8000000000ll;  // ~4 s of SM clock
 
@@ -50,6 +55,55 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         }
     }
 }
+// ---- exchange by peer stores ------------------------------------------------
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Called by ONE thread after everything earlier in the stream has finished (so the local epoch is stable): waits
+// until every rank has signalled that epoch, i.e. the outputs all ranks pushed in earlier operations have landed
+// in this rank's arena and every rank is done reading what the next push may overwrite.  Gives up after
+// pp.wait_ns, records site `site` in the status word and returns false; the caller carries on.
+__device__ __forceinline__ bool peer_wait_all(const PeerPush& pp, unsigned site) {
+    if (pp.nranks <= 1) return true;
+    const unsigned int e = *reinterpret_cast<volatile unsigned int*>(pp.ctl + PEER_CTL_EPOCH);
+    const unsigned long long t0 = globaltimer_ns();
+    for (int g = 0; g < pp.nranks; ++g) {
+        while ((int)(ld_acquire_sys_u32(pp.ctl + g) - e) < 0) {
+            if (globaltimer_ns() - t0 > pp.wait_ns) {
+                if (atomicExch(&pp.status->timeout_flag, 1u) == 0u) pp.status->timeout_where = site;
+                return false;
+            }
+            __nanosleep(100);
+        }
+    }
+    return true;
+}
+// Called by ONE thread of every CTA of a pushing kernel, after a CTA-wide barrier that follows the CTA's last
+// store.  The last CTA to arrive advances the local epoch and writes it into slot `rank` of every arena.
+__device__ __forceinline__ void peer_signal_cta_done(const PeerPush& pp, unsigned int n_ctas) {
+    if (pp.nranks <= 1) return;
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(pp.ctl + PEER_CTL_DONE, 1u);
+    if (prev + 1u == n_ctas) {
+        __threadfence_system();
+        volatile unsigned int* ctl = pp.ctl;
+        ctl[PEER_CTL_DONE] = 0u;
+        const unsigned int e = ctl[PEER_CTL_EPOCH] + 1u;
+        ctl[PEER_CTL_EPOCH] = e;
+        for (int g = 0; g < pp.nranks; ++g) st_release_sys_u32(pp.peer_ctl[g] + pp.rank, e);
+    }
+}
+
 // Programmatic dependent launch: let the next kernel in the stream start its
 // prologue now / wait until everything earlier in the stream has finished and
 // its writes are visible.  Both are no-ops for a kernel launched the plain way.
@@ -177,7 +231,8 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    static const bool no_pdl = getenv("RUSTY_NO_PDL") != nullptr;  // tuning aid: plain stream order
+    cfg.numAttrs = no_pdl ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

@@ -5,16 +5,20 @@ activations are replicated; each Linear's output is all-gathered so every rank
 continues with the whole y[M,N].  The reference has no multi-device code; the
 partitioning rule and the reassembly order live here so that CPU ranks (gloo)
 and GPU ranks (NCCL through the C ABI) share them.
+
+Two exchanges are offered: the NCCL all-gather (`Comm`, `ShardedStack`) and
+stores into the other ranks' memory from the kernel's epilogue (`Arena`,
+`PushedStack`), which needs one process per GPU on one node.
 """
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Sequence
+from typing import Dict, List, Sequence, Tuple
 
 import numpy as np
 
 from . import capi
-from .backend import CudaContext, DType, Graph, UnifiedTensor
+from .backend import CudaContext, DType, Graph, UnifiedTensor, _Storage
 from .capi import check, lib
 
 
@@ -111,3 +115,140 @@ class ShardedStack:
 
     def plans(self):
         return self.stack.plans()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Exchange by peer stores
+# ---------------------------------------------------------------------------------------------------------------
+IPC_HANDLE_BYTES = 64
+ARENA_ALIGN = 256
+
+
+def arena_layout(sizes: Sequence[Tuple[object, int]]) -> Tuple[Dict[object, int], int]:
+    """Offsets of named buffers inside an arena's data region, identical on every rank: first come, first placed,
+    each start rounded up to 256 bytes.  Returns ({key: offset}, total bytes).  A key given twice keeps its first slot
+    and must ask for the same size."""
+    offsets: Dict[object, int] = {}
+    seen: Dict[object, int] = {}
+    total = 0
+    for key, nbytes in sizes:
+        if nbytes < 0:
+            raise ValueError(f"{key!r}: negative size")
+        if key in offsets:
+            if seen[key] != nbytes:
+                raise ValueError(f"{key!r}: sizes {seen[key]} and {nbytes} disagree")
+            continue
+        offsets[key] = total
+        seen[key] = nbytes
+        total += (nbytes + ARENA_ALIGN - 1) // ARENA_ALIGN * ARENA_ALIGN
+    return offsets, total
+
+
+class _ArenaStorage(_Storage):
+    """A window of an arena wearing the interface of a device buffer."""
+
+    def __init__(self, arena: "Arena", offset: int, nbytes: int):
+        h = C.c_void_p()
+        check(lib().rusty_cuda_arena_buf(arena._h, offset, nbytes, C.byref(h)), arena.ctx.handle)
+        self.h, self.ctx, self.nbytes, self._arena = h, arena.ctx, nbytes, arena
+
+
+class Arena:
+    """One device allocation with the same layout on every rank; rank r's kernels store into all of them."""
+
+    def __init__(self, ctx: CudaContext, nbytes: int, world: int, rank: int):
+        h = C.c_void_p()
+        check(lib().rusty_cuda_arena_create(ctx.handle, nbytes, world, rank, C.byref(h)), ctx.handle)
+        self._h, self.ctx, self.world, self.rank, self.nbytes = h, ctx, world, rank, nbytes
+
+    def export(self) -> bytes:
+        buf = C.create_string_buffer(IPC_HANDLE_BYTES)
+        check(lib().rusty_cuda_arena_export(self._h, buf), self.ctx.handle)
+        return buf.raw
+
+    def attach(self, handles: Sequence[bytes]) -> None:
+        assert len(handles) == self.world and all(len(h) == IPC_HANDLE_BYTES for h in handles)
+        blob = C.create_string_buffer(b"".join(handles), IPC_HANDLE_BYTES * self.world)
+        check(lib().rusty_cuda_arena_attach(self._h, blob), self.ctx.handle)
+
+    def connect(self, dist) -> None:
+        """Swap handles over a torch.distributed process group (any backend) and map the peers."""
+        if self.world == 1:
+            return
+        handles: List = [None] * self.world
+        dist.all_gather_object(handles, self.export())
+        self.attach(handles)
+        dist.barrier()  # nobody pushes before everybody has attached
+
+    def tensor(self, offset: int, shape: Sequence[int], dtype: DType) -> UnifiedTensor:
+        n = int(np.prod(shape, dtype=np.int64)) * dtype.size_bytes()
+        return UnifiedTensor(_ArenaStorage(self, offset, n), shape, dtype)
+
+    def wait(self) -> None:
+        check(lib().rusty_cuda_arena_wait(self.ctx.handle, self._h), self.ctx.handle)
+
+    def destroy(self) -> None:
+        if self._h is not None:
+            lib().rusty_cuda_arena_destroy(self._h)
+            self._h = None
+
+
+def forward_pushed(ctx: CudaContext, arena: Arena, ql_shard, x: UnifiedTensor, M: int, y_full: UnifiedTensor) -> None:
+    check(lib().rusty_cuda_qlinear_forward_pushed(ctx.handle, arena._h, ql_shard._h, x.buffer(), int(x.dtype), M,
+                                                  y_full.buffer(), int(y_full.dtype)), ctx.handle)
+
+
+class PushedStack:
+    """Runs a LinearStack built with (rank, world): every Linear computes this rank's output columns and stores them
+    into every rank's copy of the full output (no collective call).  Outputs of equal width share one arena buffer;
+    the stack never writes the same buffer in two consecutive Linears."""
+
+    def __init__(self, stack, dist):
+        self.stack = stack
+        self.ctx = stack.ctx
+        ctx = self.ctx
+        M, ydt = stack.M, stack.y_dtype
+        keys = [(-1 if nm == "lm_head" else n) for n, nm in zip(stack.full_n, stack.names)]
+        for a, b in zip(keys, keys[1:]):
+            assert a != b, "two consecutive Linears would share an output buffer"
+        sizes = [(k, M * (n if k != -1 else n) * ydt.size_bytes()) for k, n in zip(keys, stack.full_n)]
+        offsets, total = arena_layout(sizes)
+        self.arena = Arena(ctx, total, stack.world, stack.rank)
+        self.arena.connect(dist)
+        self.full_outputs = {k: self.arena.tensor(offsets[k], [M, n], ydt) for k, n in zip(keys, stack.full_n)}
+        self._ys = [self.full_outputs[k] for k in keys]
+        self.graph = None
+        self._dist = dist
+
+    def full_logits(self) -> UnifiedTensor:
+        return self.full_outputs[-1]
+
+    def step(self) -> None:
+        s = self.stack
+        n = len(s.qls)
+        arr = C.c_void_p * n
+        check(lib().rusty_cuda_qlinear_forward_pushed_batch(
+            self.ctx.handle, self.arena._h, n, arr(*[q._h for q in s.qls]), arr(*[x.buffer() for x in s._xs]),
+            int(s.x_dtype), s.M, arr(*[y.buffer() for y in self._ys]), int(s.y_dtype)), self.ctx.handle)
+        self.arena.wait()   # the logits (and everything before them) are complete on this rank after the step
+
+    def capture(self) -> Graph:
+        g = Graph(self.ctx)
+        with g:
+            self.step()
+        self.graph = g
+        return g
+
+    def replay(self) -> None:
+        self.graph.launch()
+
+    def plans(self):
+        return self.stack.plans()
+
+    def close(self) -> None:
+        self.ctx.sync()
+        if self.stack.world > 1:
+            self._dist.barrier()  # every rank has stopped pushing before any arena goes away
+        self.full_outputs.clear()
+        self._ys = []
+        self.arena.destroy()

@@ -45,22 +45,130 @@ for (M, K, N) in [(1, 1024, 512), (32, 4096, 2048), (256, 512, 1024)]:
     comm.check()
     same_kernel = shard.plan(M) == full.plan(M)
     ok = ok and (np.array_equal(a.view(np.uint32), b.view(np.uint32)) if same_kernel else rel_err(a, b) <= 1e-5)
-print("rank", rank, "ok" if ok else "MISMATCH", flush=True)
+sys.stdout.write("rank %d %s\n" % (rank, "ok" if ok else "MISMATCH")); sys.stdout.flush()
 comm.destroy(); ctx.destroy(); dist.destroy_process_group()
 sys.exit(0 if ok else 1)
 '''
 
 
-def _run(world: int, tmp_path):
+# The same check for the exchange by peer stores: every rank's kernel writes its columns into every rank's y.
+# The cases cover the kernel with the fused exchange (5 <= M, several 64-row passes included), the kernels followed
+# by the copy kernel (M = 1, bf16 prefill) and outputs narrower than a 16-byte vector; each arena buffer is reused
+# on alternate operations, as a layer stack does.
+_PUSH_SCRIPT = r'''
+import os, sys
+import numpy as np
+sys.path.insert(0, {root!r})
+sys.path.insert(0, os.path.join({root!r}, "tests"))
+import torch, torch.distributed as dist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")                       # host channel for the IPC handles only
+import rusty_b200
+from rusty_b200 import DType, QLinear, UnifiedTensor
+from rusty_b200.shard import Arena, arena_layout, forward_pushed, shard_rows
+from rusty_b200.workloads import sym_row_linear
+from rusty_b200.backend import bf16_bits_to_f32
+from parity import rel_err
+ctx = rusty_b200.CudaContext(rank)
+eng = rusty_b200.ComputeEngine(ctx)
+cases = [(32, 4096, 2048, DType.FP32), (1, 1024, 512, DType.FP32), (256, 512, 1024, DType.FP32),
+         (128, 1024, 768, DType.BF16), (3, 256, 6 * world, DType.FP32), (32, 4096, 2048, DType.FP32)]
+sizes = [(i % 2, max(M * N * 4 for j, (M, K, N, dt) in enumerate(cases) if j % 2 == i % 2)) for i in range(len(cases))]
+offsets, total = arena_layout(sizes)
+arena = Arena(ctx, total, world, rank)
+arena.connect(dist)
+ok = True
+pending = []
+for i, (M, K, N, dt) in enumerate(cases):
+    x, q, s = sym_row_linear(M + N + i, M, K, N)
+    rows = shard_rows(N, world, rank)
+    shard = QLinear.from_host(ctx, q[rows], s[rows])
+    full = QLinear.from_host(ctx, q, s)
+    xt = UnifiedTensor.from_bf16(ctx, x, [M, K]) if dt == DType.BF16 else UnifiedTensor.new(ctx, x, [M, K])
+    y = arena.tensor(offsets[i % 2], [M, N], dt)
+    forward_pushed(ctx, arena, shard, xt, M, y)
+    y1 = UnifiedTensor.empty_with_dtype(ctx, [M, N], dt)
+    eng.qlinear(ctx, xt, full, y1)
+    pending.append((y, y1, shard.plan(M, dt, dt) == full.plan(M, dt, dt), dt, (shard, full, xt)))
+    if i % 2 == 1 or i == len(cases) - 1:
+        # results of the last two operations live in the two buffers: wait for the peers' columns, then compare
+        arena.wait()
+        for (ya, yb, same_kernel, d, _keep) in pending:
+            a, b = ya.to_bytes(ctx), yb.to_bytes(ctx)
+            if d == DType.BF16:
+                fa, fb = bf16_bits_to_f32(a.view(np.uint16)), bf16_bits_to_f32(b.view(np.uint16))
+                ok = ok and rel_err(fa, fb) <= 1e-2
+            elif same_kernel:
+                ok = ok and np.array_equal(a, b)
+            else:
+                ok = ok and rel_err(a.view(np.float32), b.view(np.float32)) <= 1e-5
+        pending = []
+        ctx.sync()
+        dist.barrier()   # the comparison read both buffers: nobody overwrites them before everybody is done
+sys.stdout.write("rank %d %s\n" % (rank, "ok" if ok else "MISMATCH")); sys.stdout.flush()
+ctx.sync(); dist.barrier()
+arena.destroy(); ctx.destroy(); dist.destroy_process_group()
+sys.exit(0 if ok else 1)
+'''
+
+# A rank that never pushes: the others' bounded wait runs out, the next sync reports Timeout and the context
+# keeps working.  The absent rank is idle (no kernel in flight); nothing faults.
+_TIMEOUT_SCRIPT = r'''
+import os, sys
+import numpy as np
+sys.path.insert(0, {root!r})
+import torch, torch.distributed as dist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+import rusty_b200
+from rusty_b200 import DType, QLinear, UnifiedTensor
+from rusty_b200.capi import BackendError
+from rusty_b200.shard import Arena, forward_pushed, shard_rows
+from rusty_b200.workloads import sym_row_linear
+ctx = rusty_b200.CudaContext(rank)
+eng = rusty_b200.ComputeEngine(ctx)
+M, K, N = 32, 1024, 512
+arena = Arena(ctx, M * N * 4, world, rank)
+arena.connect(dist)
+x, q, s = sym_row_linear(3, M, K, N)
+rows = shard_rows(N, world, rank)
+shard = QLinear.from_host(ctx, q[rows], s[rows])
+xt = UnifiedTensor.new(ctx, x, [M, K])
+y = arena.tensor(0, [M, N], DType.FP32)
+ok = True
+if rank == 0:
+    forward_pushed(ctx, arena, shard, xt, M, y)   # rank 1 never answers
+    arena.wait()
+    try:
+        ctx.sync()
+        ok = False
+    except BackendError as e:
+        ok = e.kind == "Timeout"
+    # the context still works
+    full = QLinear.from_host(ctx, q, s)
+    y1 = UnifiedTensor.empty(ctx, [M, N])
+    eng.qlinear(ctx, xt, full, y1)
+    ctx.sync()
+    ok = ok and bool(np.isfinite(y1.to_vec(ctx)).all())
+dist.barrier()
+sys.stdout.write("rank %d %s\n" % (rank, "ok" if ok else "FAILED")); sys.stdout.flush()
+ctx.sync(); dist.barrier()
+arena.destroy(); ctx.destroy(); dist.destroy_process_group()
+sys.exit(0 if ok else 1)
+'''
+
+
+def _run(world: int, tmp_path, script_text: str = None, extra_env=None):
     script = tmp_path / "rank.py"
-    script.write_text(_RANK_SCRIPT.format(root=ROOT))
+    script.write_text((script_text or _RANK_SCRIPT).format(root=ROOT))
     port = 29600 + os.getpid() % 300
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), str(script)]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env.update(extra_env or {})
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert r.stdout.count(" ok") == world, r.stdout
+    assert r.stdout.count("ok") == world, r.stdout   # lines of two ranks may interleave
 
 
 def test_single_rank_communicator(tmp_path):
@@ -72,3 +180,28 @@ def test_two_ranks_match_single_gpu_bit_for_bit(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _run(2, tmp_path)
+
+
+def test_pushed_single_rank(tmp_path):
+    _run(1, tmp_path, _PUSH_SCRIPT)
+
+
+def test_pushed_two_ranks_match_single_gpu_bit_for_bit(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(2, tmp_path, _PUSH_SCRIPT)
+
+
+def test_pushed_unfused_copy_kernel_two_ranks(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(2, tmp_path, _PUSH_SCRIPT, {"RUSTY_PUSH_UNFUSED": "1"})
+
+
+def test_absent_rank_is_reported_as_timeout(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(2, tmp_path, _TIMEOUT_SCRIPT, {"RUSTY_PEER_WAIT_MS": "300"})
