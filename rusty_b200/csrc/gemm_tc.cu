@@ -64,10 +64,23 @@ __device__ __forceinline__ float x_to_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float x_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+// Four consecutive activations as f32 (p is 16-byte aligned for f32, 8-byte aligned for bf16: K % 16 == 0).
+template <typename XT>
+__device__ __forceinline__ float4 load_row4(const XT* p);
+template <>
+__device__ __forceinline__ float4 load_row4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 load_row4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                       __uint_as_float(raw.y & 0xffff0000u));
+}
+
 template <typename XT, int D>
 __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ x, int8_t* __restrict__ xq,
                                                          float* __restrict__ inv_s, int M, int Mpad, int K,
-                                                         const PeerPush push, long long* dbg) {
+                                                         const PeerPush push, long long* dbg,
+                                                         unsigned int* __restrict__ counters, int n_counters) {
     const int m = blockIdx.x;
     __shared__ float red[8];
     __shared__ float s_scale;
@@ -75,7 +88,10 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
     if (dbg && tid == 0 && m == 0) dbg[0] = (long long)globaltimer_ns();
     pdl_launch_dependents();
     pdl_wait();
-    if (dbg && tid == 0 && m == 0) dbg[1] = (long long)globaltimer_ns();  // x may come from the previous kernel, and that kernel may still be reading the digit planes
+    if (dbg && tid == 0 && m == 0) dbg[1] = (long long)globaltimer_ns();
+    // arrival counters of the GEMM's shared tiles: the kernel before has finished with them, the GEMM after this
+    // kernel counts from zero
+    for (int i = m * 256 + tid; i < n_counters; i += gridDim.x * 256) counters[i] = 0u;  // x may come from the previous kernel, and that kernel may still be reading the digit planes
     if (push.nranks > 1) {
         // x may hold columns pushed by the other ranks, and the GEMM that follows overwrites their copies of y:
         // wait until every rank has finished (and delivered) all earlier pushes
@@ -89,38 +105,57 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
         return;
     }
     const XT* xr = x + (size_t)m * K;
+    // Rows of up to 16384 elements stay in registers between the maximum and the digits (one trip to memory).
+    constexpr int MAXV = 16;
+    const bool in_regs = K <= 256 * 4 * MAXV;
+    float4 v[MAXV];
     float mx = 0.0f;
-    for (int k = tid; k < K; k += 256) {
-        float a = fabsf(x_to_f32<XT>(xr[k]));
-        mx = (a <= 3.0e38f) ? fmaxf(mx, a) : __int_as_float(0x7f800000);  // NaN or inf anywhere poisons the row
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int k = (j * 256 + tid) * 4;
+            v[j] = k < K ? load_row4<XT>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const float a4[4] = {fabsf(v[j].x), fabsf(v[j].y), fabsf(v[j].z), fabsf(v[j].w)};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mx = (a4[e] <= 3.0e38f) ? fmaxf(mx, a4[e]) : __int_as_float(0x7f800000);
+        }
+    } else {
+        for (int k = tid; k < K; k += 256) {
+            float a = fabsf(x_to_f32<XT>(xr[k]));
+            mx = (a <= 3.0e38f) ? fmaxf(mx, a) : __int_as_float(0x7f800000);  // NaN or inf anywhere poisons the row
+        }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     if ((tid & 31) == 0) red[tid >> 5] = mx;
     __syncthreads();
     if (tid == 0) {
-        float v = red[0];
-        for (int i = 1; i < 8; ++i) v = fmaxf(v, red[i]);
+        float vmax = red[0];
+        for (int i = 1; i < 8; ++i) vmax = fmaxf(vmax, red[i]);
         float s = 1.0f;
-        if (v > 0.0f && v <= 3.0e38f) {
+        if (vmax > 0.0f && vmax <= 3.0e38f) {
             int e;
-            frexpf(v, &e);            // v = f * 2^e, f in [0.5, 1)
-            s = ldexpf(1.0f, 7 - e);  // v*s in [64, 128)
-            if (v * s > 127.0f) s *= 0.5f;
+            frexpf(vmax, &e);            // vmax = f * 2^e, f in [0.5, 1)
+            s = ldexpf(1.0f, 7 - e);     // vmax*s in [64, 128)
+            if (vmax * s > 127.0f) s *= 0.5f;
         }
         s_scale = s;
         // 1/s_m * 128^-(D-1): both powers of two, so the product is exact
-        inv_s[m] = (v <= 3.0e38f) ? ldexpf(1.0f / s, -7 * (D - 1)) : __int_as_float(0x7fc00000);  // inf/nan poisons the row
+        inv_s[m] = (vmax <= 3.0e38f) ? ldexpf(1.0f / s, -7 * (D - 1)) : __int_as_float(0x7fc00000);  // inf/nan poisons the row
     }
     __syncthreads();
     const float s = s_scale;
-    for (int k = tid * 4; k < K; k += 256 * 4) {  // K % 4 == 0 (K % 16 == 0 is required by the caller)
+    auto emit = [&](int k, const float4& f) {
+        const float in4[4] = {f.x, f.y, f.z, f.w};
         uint32_t packed[D];
 #pragma unroll
         for (int d = 0; d < D; ++d) packed[d] = 0u;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            float r = x_to_f32<XT>(xr[k + e]) * s;  // exact: s is a power of two
+            float r = in4[e] * s;  // exact: s is a power of two
 #pragma unroll
             for (int d = 0; d < D; ++d) {
                 float q = rintf(r);
@@ -130,6 +165,15 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
         }
 #pragma unroll
         for (int d = 0; d < D; ++d) *reinterpret_cast<uint32_t*>(xq + (size_t)(d * Mpad + m) * K + k) = packed[d];
+    };
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int k = (j * 256 + tid) * 4;
+            if (k < K) emit(k, v[j]);
+        }
+    } else {
+        for (int k = tid * 4; k < K; k += 256 * 4) emit(k, load_row4<XT>(xr + k));  // K % 4 == 0 (K % 16 == 0 is required by the caller)
     }
     if (dbg && tid == 0 && m == 0) dbg[2] = (long long)globaltimer_ns();
 }
@@ -153,6 +197,7 @@ struct TcParams {
     int dp_tiles, sk_tiles, sk_per_cta, sk_ctas;
     int ldy, y_col0;
     int stages;
+    int red_bytes;           // epilogue staging area: a partial tile (Mpad x 128 x 8 bytes), at least 12 KiB
     uint32_t idesc;
     uint32_t tmem_cols;
     rusty_cuda_dev_status* status;
@@ -263,7 +308,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     // epilogue staging for the bulk reduce-add of a partial tile: [Mpad/2][128] x 16 bytes
     // fused mode: sB is not a ring but ALL digit tiles of x (one per k-block), written once by the epilogue warps
     int4* stage_red = reinterpret_cast<int4*>(sB + (size_t)(p.fused ? p.kb_total : p.stages) * b_stage_bytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (p.fused ? (size_t)0 : (size_t)p.Mpad * 8 * BM));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (p.fused ? (size_t)0 : (size_t)p.red_bytes));
     uint64_t* full = bars;                      // [stages]
     uint64_t* empty = bars + p.stages;          // [stages]
     uint64_t* acc_full = bars + 2 * p.stages;   // [2]
@@ -508,9 +553,87 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(dig_ready);
         }
+        int cut_t[2], cut_j[2], cut_n[2], n_cut = 0;  // shared tiles this CTA added a piece to
         Sched sched(p);
         Segment sg;
-        for (int i = 0; ok && sched.next(sg); ++i) {
+        for (int i = 0;; ++i) {
+            const bool have = ok && sched.next(sg);
+            // Shared tiles: once all pieces of a tile have been added, each CTA that holds one of them turns an equal share
+            // of the tile's rows into y and leaves zeros behind (the arrival counters are cleared by the next pre-pass).  All pieces are added before anybody waits here, and the
+            // CTAs of the grid are resident together (one wave), so the wait cannot depend on a CTA that has not started.
+            if (ok && n_cut > 0 && (!have || sg.nseg == 1) && threadIdx.x == 64) {
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // this CTA's adds have been performed
+                __threadfence();
+                for (int e = 0; e < n_cut; ++e)
+                    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.counters + cut_t[e]) : "memory");
+            }
+            for (int e = 0; ok && e < n_cut && (!have || sg.nseg == 1); ++e) {
+                const int t = cut_t[e], nseg = cut_n[e], j = cut_j[e];
+                if (threadIdx.x == 64) {
+                    const long long t0 = clock64();
+                    while (ld_acquire_gpu_u32(p.counters + t) < (unsigned)nseg) {
+                        if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                            *abort_flag = 1;
+                            if (atomicExch(&p.status->timeout_flag, 1u) == 0u) p.status->timeout_where = 8;
+                            break;
+                        }
+                    }
+                    DBG(10);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                if (*abort_flag) { ok = false; break; }
+                int4* tile_sum = reinterpret_cast<int4*>(p.part) + (size_t)(t - p.dp_tiles) * (p.Mpad / 2) * BM;
+                const int lo = j * BM / nseg, rows = (j + 1) * BM / nseg - lo;  // this CTA's share of the tile's rows
+                const int items = rows * (p.Mpad / 2);                         // one item: a row, two activation rows
+                if (rows <= 0) continue;
+                // item -> (row, mp) without a division per item: start at (et % rows, et / rows), step by EPI_THREADS items
+                int row = et % rows, mp = et / rows;
+                const int step_row = EPI_THREADS % rows, step_mp = EPI_THREADS / rows;
+                for (int it0 = et; it0 < items; it0 += 4 * EPI_THREADS) {
+                    int4 v[4];
+                    float sc[4];
+                    int rw[4], mq[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {  // independent loads: one L2 round trip per batch
+                        rw[u] = lo + row;
+                        mq[u] = mp;
+                        const bool in = it0 + u * EPI_THREADS < items && t * BM + rw[u] < p.N;
+                        v[u] = in ? __ldcg(tile_sum + (size_t)mp * BM + rw[u]) : make_int4(0, 0, 0, 0);
+                        sc[u] = in ? __ldg(p.scales + t * BM + rw[u]) : 0.0f;
+                        row += step_row;
+                        mp += step_mp;
+                        if (row >= rows) {
+                            row -= rows;
+                            ++mp;
+                        }
+                    }
+                    // Park the batch in this thread's slots of the staging tile (free by now) and convert in a rolled
+                    // loop: code that runs once per CTA costs an instruction fetch per line, so it is kept short.
+                    float* stage_sc = reinterpret_cast<float*>(stage_red + 4 * EPI_THREADS);
+                    int* stage_at = reinterpret_cast<int*>(stage_sc + 4 * EPI_THREADS);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const bool live = it0 + u * EPI_THREADS < items;
+                        if (live) __stcg(tile_sum + (size_t)mq[u] * BM + rw[u], make_int4(0, 0, 0, 0));
+                        stage_red[u * EPI_THREADS + et] = v[u];
+                        stage_sc[u * EPI_THREADS + et] = sc[u];
+                        stage_at[u * EPI_THREADS + et] = (live && t * BM + rw[u] < p.N) ? (rw[u] | (mq[u] << 8)) : -1;
+                    }
+#pragma unroll 1
+                    for (int u = 0; u < 4; ++u) {
+                        const int at = stage_at[u * EPI_THREADS + et];
+                        if (at < 0) continue;
+                        const longlong2 two = *reinterpret_cast<const longlong2*>(&stage_red[u * EPI_THREADS + et]);
+                        const float scu = stage_sc[u * EPI_THREADS + et];
+                        const int nn = t * BM + (at & 0xff), m = 2 * (at >> 8);
+                        if (m < p.M) finalize_store<YT>(p, y, nn, m, two.x, scu, s_rowf, po);
+                        if (m + 1 < p.M) finalize_store<YT>(p, y, nn, m + 1, two.y, scu, s_rowf, po);
+                    }
+                }
+                if (threadIdx.x == 64) DBG(11);
+            }
+            if (!have || !ok) break;
+            if (sg.nseg == 1) n_cut = 0;  // the shared tiles recorded so far have just been converted
             const int ab = i & 1;
             const int n = sg.t * BM + r;
             const bool row_ok = n < p.N;
@@ -640,47 +763,23 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                                  "r"(smem_u32(stage_red)), "r"(bytes)
                                  : "memory");
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the adds have been performed
-                    __threadfence();
-                    unsigned prev = atomicAdd(p.counters + sg.t, 1u);
-                    *reinterpret_cast<volatile int*>(last_flag) = (prev == (unsigned)(sg.nseg - 1)) ? 1 : 0;
+                    // only until the staging tile has been read: the adds themselves complete while the next segment
+                    // is folded, and are waited for (and announced) before the shared conversion below
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-                const bool last = *reinterpret_cast<volatile int*>(last_flag) != 0;
                 if (threadIdx.x == 64) DBG(8 + 4 * (i & 1));
-                if (last) {
-                    // every piece has been added: turn the sums into y and leave zeros behind for the next use
-                    __threadfence();
-                    const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
-                    if (threadIdx.x == 64) DBG(10);
-                    // The sums come back in batches of independent loads (one L2 round trip per batch) and are parked in
-                    // this thread's column of the staging tile, which the bulk reduce has finished reading; the
-                    // conversion then runs as a rolled loop over shared memory.  Straight-line code that runs once
-                    // per kernel is paid for in instruction fetches, not in issue slots, so it is kept short.
-                    for (int mp0 = 0; mp0 * 2 < p.Mpad; mp0 += 8) {
-                        int4 ld[8];
-#pragma unroll
-                        for (int h = 0; h < 8; ++h)
-                            ld[h] = (mp0 + h) * 2 < p.Mpad ? __ldcg(tile_sum + (size_t)(mp0 + h) * BM + r) : make_int4(0, 0, 0, 0);
-#pragma unroll
-                        for (int h = 0; h < 8; ++h)
-                            if ((mp0 + h) * 2 < p.Mpad) {
-                                __stcg(tile_sum + (size_t)(mp0 + h) * BM + r, make_int4(0, 0, 0, 0));
-                                stage_red[(size_t)(mp0 + h) * BM + r] = ld[h];
-                            }
-                    }
-                    if (threadIdx.x == 64) DBG(12);
-                    if (row_ok) {
-#pragma unroll 2
-                        for (int m = 0; m < p.M; ++m) {
-                            const longlong2 two = *reinterpret_cast<const longlong2*>(&stage_red[(size_t)(m >> 1) * BM + r]);
-                            finalize_store<YT>(p, y, n, m, (m & 1) ? two.y : two.x, sc, s_rowf, po);
-                        }
-                    }
-                    if (threadIdx.x == 64) DBG(13);
-                    if (threadIdx.x == 64) p.counters[sg.t] = 0u;
+                // The conversion of the finished sums is shared between the CTAs that hold the tile's pieces and is
+                // done after the CTA's last segment (below): remember the tile and which piece this was.
+                if (n_cut < 2) {
+                    cut_t[n_cut] = sg.t;
+                    cut_j[n_cut] = (int)blockIdx.x - sg.first_cta;
+                    cut_n[n_cut] = sg.nseg;
+                    ++n_cut;
+                } else {
+                    ok = false;  // cannot happen: a run of k-blocks starts and ends inside at most two shared tiles
+                    if (threadIdx.x == 64 && atomicExch(&p.status->timeout_flag, 1u) == 0u) p.status->timeout_where = 7;
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // last_flag is reused by the next segment
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // the staging tile is free again (the bulk reduce has read it)
                 if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
             }
         }
@@ -703,8 +802,9 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 constexpr size_t WS_XQ_BYTES = 24u << 20;      // digit planes: up to 256 rows x K <= 96K
 constexpr size_t WS_INVS_BYTES = 4096;
 constexpr size_t WS_ACC_BYTES = 48u << 20;     // split-K partial sums
-constexpr size_t WS_CNT_BYTES = 64u << 10;
-constexpr size_t WS_TOTAL = WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES + WS_CNT_BYTES;
+constexpr size_t WS_CNT_BYTES = 64u << 10;     // arrival counters, kept at zero between kernels (small-batch mode, prefill kernels)
+constexpr size_t WS_CNT2_BYTES = 64u << 10;    // arrival counters of the GEMM with a pre-pass, which clears them
+constexpr size_t WS_TOTAL = WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES + WS_CNT_BYTES + WS_CNT2_BYTES;
 
 int pick_digits(int x_dtype, uint32_t rows) {
     // 4 digits (28 bits under the row maximum) while the B operand stays narrow, else 3 (21 bits).
@@ -714,10 +814,12 @@ int pick_digits(int x_dtype, uint32_t rows) {
 
 template <typename XT>
 cudaError_t launch_digitize(rusty_cuda_ctx* ctx, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D,
-                            const PeerPush& push, long long* dbg) {
+                            const PeerPush& push, long long* dbg, unsigned int* counters, int n_counters) {
     if (D == 4)
-        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg);
-    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg);
+        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg,
+                          counters, n_counters);
+    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg,
+                      counters, n_counters);
 }
 
 }  // namespace
@@ -792,12 +894,16 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     int8_t* xq = (int8_t*)ws;
     float* inv_s = (float*)(ws + WS_XQ_BYTES);
     int32_t* acc = (int32_t*)(ws + WS_XQ_BYTES + WS_INVS_BYTES);
-    unsigned int* counters = (unsigned int*)(ws + WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES);
+    // two sets of arrival counters: one kept at zero by its users, one cleared by the pre-pass of this path
+    unsigned int* counters = (unsigned int*)(ws + WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES + (fused ? 0 : WS_CNT_BYTES));
     if ((size_t)D * Mpad * a.K > WS_XQ_BYTES)
         return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: %d digit rows x K=%u exceed the workspace", D * Mpad, a.K);
 
     cudaError_t le = cudaSuccess;
     int rc = RUSTY_CUDA_OK;
+    const int n_tiles = (int)((a.N + BM - 1) / BM);
+    if ((size_t)n_tiles * 4 > WS_CNT_BYTES)
+        return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: N=%u has more row tiles than arrival counters", a.N);
     // development aid: each launch pair writes its timeline into the next 152 x 16 slots of the attached buffer
     long long* dbg = nullptr;
     if (ctx->tc_dbg) {
@@ -810,8 +916,8 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
         push = *a.push;
     }
     if (!fused) {
-        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr)
-                                          : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr);
+        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr, counters, n_tiles)
+                                          : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr, counters, n_tiles);
         if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
         rc = after_launch(ctx, "digitize_x");
         if (rc) return rc;
@@ -885,13 +991,15 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     const size_t dig_bytes = fused ? (size_t)p.kb_total * b_stage : 0;
     if (!full_smem && NB <= 32 && dig_bytes + 4 * A_STAGE_BYTES + 4096 <= budget / 2)
         budget = budget / 2 - 1024;  // narrow batches: leave room for the next kernel's CTA on the SM
-    const size_t red_bytes = fused ? dig_bytes : (size_t)Mpad * 8 * BM;  // epilogue staging of a partial tile
+    // epilogue staging of a partial tile; the shared finalize parks 4 x 128 sums, scales and positions there (12 KiB)
+    const size_t red_bytes = fused ? dig_bytes : ((size_t)Mpad * 8 * BM > 12288 ? (size_t)Mpad * 8 * BM : (size_t)12288);
     int stages = budget > red_bytes + 2048
                      ? (int)((budget - 1024 - 512 - red_bytes) / (size_t)(A_STAGE_BYTES + (fused ? 0 : b_stage)))
                      : 0;
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: tile does not fit shared memory");
     p.stages = stages;
+    p.red_bytes = (int)red_bytes;
     const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + (fused ? 0 : b_stage)) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
 
     CUtensorMap map_w, map_x;
@@ -1023,7 +1131,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: clearing the scratch");
 
     const int Mi = (int)M, Mpad = 8, D = 4, NB = 32;
-    e = launch_pdl(digitize_x_kernel<float, 4>, dim3(Mpad), dim3(256), 0, st, x_f32, xq, factor, Mi, Mpad, (int)K, PeerPush{}, (long long*)nullptr);
+    e = launch_pdl(digitize_x_kernel<float, 4>, dim3(Mpad), dim3(256), 0, st, x_f32, xq, factor, Mi, Mpad, (int)K, PeerPush{}, (long long*)nullptr, counters, (int)((N + BM - 1) / BM));
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: digitize_x");
 
     TcParams p{};
@@ -1058,12 +1166,13 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     p.tmem_cols = 64;
     const int b_stage = NB * BK;
-    const size_t red_bytes = (size_t)Mpad * 8 * BM;
+    const size_t red_bytes = (size_t)Mpad * 8 * BM > 12288 ? (size_t)Mpad * 8 * BM : (size_t)12288;
     const size_t budget = (sd.smem_optin > 4096 ? sd.smem_optin - 4096 : 0) / 2;
     int stages = budget > red_bytes + 4096 ? (int)((budget - 2048 - red_bytes) / (size_t)(A_STAGE_BYTES + b_stage)) : 0;
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(nullptr, RUSTY_CUDA_ERR_UNSUPPORTED, "qlinear_i8_forward_static: shared memory too small");
     p.stages = stages;
+    p.red_bytes = (int)red_bytes;
     const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
     CUtensorMap map_w, map_x;
     if (!make_map_u8(&map_w, w_i8, N, K, BM) || !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, K, (uint32_t)NB))
@@ -1071,7 +1180,10 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     auto kern = qlinear_i8_tc_kernel<float>;
     // Raise the kernel's dynamic shared-memory limit to the device maximum: enough for this launch and never
     // below what another entry point has asked for.
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sd.smem_optin);
+    cudaFuncAttributes fa;
+    e = cudaFuncGetAttributes(&fa, kern);
+    if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: cudaFuncGetAttributes");
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sd.smem_optin - fa.sharedSizeBytes));
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: cudaFuncSetAttribute");
     e = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, st, map_w, map_x, p);
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: launch");
