@@ -76,22 +76,24 @@ __device__ __forceinline__ float4 load_row4<__nv_bfloat16>(const __nv_bfloat16* 
                        __uint_as_float(raw.y & 0xffff0000u));
 }
 
+constexpr int DIG_THREADS = 1024;  // one block per activation row; a 4096-wide row is one 16-byte load per thread
+
 template <typename XT, int D>
-__global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ x, int8_t* __restrict__ xq,
-                                                         float* __restrict__ inv_s, int M, int Mpad, int K,
-                                                         const PeerPush push, long long* dbg,
-                                                         unsigned int* __restrict__ counters, int n_counters) {
+__global__ void __launch_bounds__(DIG_THREADS) digitize_x_kernel(const XT* __restrict__ x, int8_t* __restrict__ xq,
+                                                                 float* __restrict__ inv_s, int M, int Mpad, int K,
+                                                                 const PeerPush push, long long* dbg,
+                                                                 unsigned int* __restrict__ counters, int n_counters) {
     const int m = blockIdx.x;
-    __shared__ float red[8];
+    __shared__ float red[DIG_THREADS / 32];
     __shared__ float s_scale;
     const int tid = threadIdx.x;
     if (dbg && tid == 0 && m == 0) dbg[0] = (long long)globaltimer_ns();
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait();  // x may come from the previous kernel, and that kernel may still be reading the digit planes
     if (dbg && tid == 0 && m == 0) dbg[1] = (long long)globaltimer_ns();
     // arrival counters of the GEMM's shared tiles: the kernel before has finished with them, the GEMM after this
     // kernel counts from zero
-    for (int i = m * 256 + tid; i < n_counters; i += gridDim.x * 256) counters[i] = 0u;  // x may come from the previous kernel, and that kernel may still be reading the digit planes
+    for (int i = m * DIG_THREADS + tid; i < n_counters; i += gridDim.x * DIG_THREADS) counters[i] = 0u;
     if (push.nranks > 1) {
         // x may hold columns pushed by the other ranks, and the GEMM that follows overwrites their copies of y:
         // wait until every rank has finished (and delivered) all earlier pushes
@@ -99,21 +101,21 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
         __syncthreads();
     }
     if (m >= M) {
-        for (int k = tid * 4; k < K; k += 256 * 4)
+        for (int k = tid * 4; k < K; k += DIG_THREADS * 4)
 #pragma unroll
             for (int d = 0; d < D; ++d) *reinterpret_cast<uint32_t*>(xq + (size_t)(d * Mpad + m) * K + k) = 0u;
         return;
     }
     const XT* xr = x + (size_t)m * K;
     // Rows of up to 16384 elements stay in registers between the maximum and the digits (one trip to memory).
-    constexpr int MAXV = 16;
-    const bool in_regs = K <= 256 * 4 * MAXV;
+    constexpr int MAXV = 4;
+    const bool in_regs = K <= DIG_THREADS * 4 * MAXV;
     float4 v[MAXV];
     float mx = 0.0f;
     if (in_regs) {
 #pragma unroll
         for (int j = 0; j < MAXV; ++j) {
-            const int k = (j * 256 + tid) * 4;
+            const int k = (j * DIG_THREADS + tid) * 4;
             v[j] = k < K ? load_row4<XT>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
@@ -123,7 +125,7 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
             for (int e = 0; e < 4; ++e) mx = (a4[e] <= 3.0e38f) ? fmaxf(mx, a4[e]) : __int_as_float(0x7f800000);
         }
     } else {
-        for (int k = tid; k < K; k += 256) {
+        for (int k = tid; k < K; k += DIG_THREADS) {
             float a = fabsf(x_to_f32<XT>(xr[k]));
             mx = (a <= 3.0e38f) ? fmaxf(mx, a) : __int_as_float(0x7f800000);  // NaN or inf anywhere poisons the row
         }
@@ -132,19 +134,26 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     if ((tid & 31) == 0) red[tid >> 5] = mx;
     __syncthreads();
-    if (tid == 0) {
-        float vmax = red[0];
-        for (int i = 1; i < 8; ++i) vmax = fmaxf(vmax, red[i]);
-        float s = 1.0f;
-        if (vmax > 0.0f && vmax <= 3.0e38f) {
-            int e;
-            frexpf(vmax, &e);            // vmax = f * 2^e, f in [0.5, 1)
-            s = ldexpf(1.0f, 7 - e);     // vmax*s in [64, 128)
-            if (vmax * s > 127.0f) s *= 0.5f;
+    if (tid < 32) {
+        float vmax = red[tid];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+        if (tid == 0) {
+            // s = the power of two that puts vmax*s into [64, 128) but not above 127
+            float s = 1.0f;
+            if (vmax >= 1.0e-30f && vmax <= 3.0e38f) {
+                const int e = (int)((__float_as_uint(vmax) >> 23) & 0xffu) - 126;  // vmax = f * 2^e, f in [0.5, 1)
+                s = __uint_as_float((uint32_t)(127 + 7 - e) << 23);                 // 2^(7-e): 7-e in [-121, 106]
+                if (vmax * s > 127.0f) s *= 0.5f;
+            } else if (vmax > 0.0f && vmax <= 3.0e38f) {
+                int e;
+                frexpf(vmax, &e);
+                s = ldexpf(1.0f, 7 - e > 120 ? 120 : 7 - e);  // tiny rows: any power of two that keeps |x*s| <= 127 will do
+            }
+            s_scale = s;
+            // 1/s_m * 128^-(D-1): both powers of two, so the product is exact
+            inv_s[m] = (vmax <= 3.0e38f) ? ldexpf(1.0f / s, -7 * (D - 1)) : __int_as_float(0x7fc00000);  // inf/nan poisons the row
         }
-        s_scale = s;
-        // 1/s_m * 128^-(D-1): both powers of two, so the product is exact
-        inv_s[m] = (vmax <= 3.0e38f) ? ldexpf(1.0f / s, -7 * (D - 1)) : __int_as_float(0x7fc00000);  // inf/nan poisons the row
     }
     __syncthreads();
     const float s = s_scale;
@@ -169,11 +178,11 @@ __global__ void __launch_bounds__(256) digitize_x_kernel(const XT* __restrict__ 
     if (in_regs) {
 #pragma unroll
         for (int j = 0; j < MAXV; ++j) {
-            const int k = (j * 256 + tid) * 4;
+            const int k = (j * DIG_THREADS + tid) * 4;
             if (k < K) emit(k, v[j]);
         }
     } else {
-        for (int k = tid * 4; k < K; k += 256 * 4) emit(k, load_row4<XT>(xr + k));  // K % 4 == 0 (K % 16 == 0 is required by the caller)
+        for (int k = tid * 4; k < K; k += DIG_THREADS * 4) emit(k, load_row4<XT>(xr + k));  // K % 4 == 0 (K % 16 == 0 is required by the caller)
     }
     if (dbg && tid == 0 && m == 0) dbg[2] = (long long)globaltimer_ns();
 }
@@ -195,6 +204,7 @@ struct TcParams {
     // runs of `sk_per_cta` to the first `sk_ctas` CTAs.  The other tiles are
     // taken whole, tile = cta, cta + grid, ...
     int dp_tiles, sk_tiles, sk_per_cta, sk_ctas;
+    int sk_ways;             // > 0: every shared tile is cut into this many near-equal pieces, one per CTA (CTA = tile * ways + piece)
     int ldy, y_col0;
     int stages;
     int red_bytes;           // epilogue staging area: a partial tile (Mpad x 128 x 8 bytes), at least 12 KiB
@@ -224,8 +234,15 @@ struct Sched {
     int seg_index;
     __device__ Sched(const TcParams& pp) : p(pp) {
         const int c = blockIdx.x;
-        g = c < p.sk_ctas ? c * p.sk_per_cta : 0;
-        g_end = c < p.sk_ctas ? min(p.sk_tiles * p.kb_total, g + p.sk_per_cta) : 0;
+        if (p.sk_ways > 0) {
+            // one piece per CTA, cut at the same places in every tile: g walks the piece's k-blocks
+            const int lt = c / p.sk_ways, j = c % p.sk_ways;
+            g = c < p.sk_ctas ? lt * p.kb_total + j * p.kb_total / p.sk_ways : 0;
+            g_end = c < p.sk_ctas ? lt * p.kb_total + (j + 1) * p.kb_total / p.sk_ways : 0;
+        } else {
+            g = c < p.sk_ctas ? c * p.sk_per_cta : 0;
+            g_end = c < p.sk_ctas ? min(p.sk_tiles * p.kb_total, g + p.sk_per_cta) : 0;
+        }
         dp_next = c;
         seg_index = 0;
     }
@@ -235,9 +252,14 @@ struct Sched {
             s.t = p.dp_tiles + lt;
             s.kb0 = g % p.kb_total;
             s.kb1 = min(p.kb_total, s.kb0 + (g_end - g));
-            s.first_cta = (lt * p.kb_total) / p.sk_per_cta;
-            const int last_cta = ((lt + 1) * p.kb_total - 1) / p.sk_per_cta;
-            s.nseg = last_cta - s.first_cta + 1;
+            if (p.sk_ways > 0) {
+                s.first_cta = lt * p.sk_ways;
+                s.nseg = p.sk_ways;
+            } else {
+                s.first_cta = (lt * p.kb_total) / p.sk_per_cta;
+                const int last_cta = ((lt + 1) * p.kb_total - 1) / p.sk_per_cta;
+                s.nseg = last_cta - s.first_cta + 1;
+            }
             // head piece (the CTA's run starts inside this tile) -> even slot, tail piece -> odd slot
             s.slot = 2 * (int)blockIdx.x + ((int)blockIdx.x * p.sk_per_cta >= lt * p.kb_total ? 0 : 1);
             g += s.kb1 - s.kb0;
@@ -816,9 +838,9 @@ template <typename XT>
 cudaError_t launch_digitize(rusty_cuda_ctx* ctx, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D,
                             const PeerPush& push, long long* dbg, unsigned int* counters, int n_counters) {
     if (D == 4)
-        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg,
+        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(Mpad), dim3(DIG_THREADS), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg,
                           counters, n_counters);
-    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(Mpad), dim3(256), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg,
+    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(Mpad), dim3(DIG_THREADS), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg,
                       counters, n_counters);
 }
 
@@ -959,12 +981,20 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
             if (aligned >= 4 && (long long)p.sk_per_cta * 100 >= (long long)aligned * 85) p.sk_per_cta = aligned;
         }
         p.sk_ctas = (sk_work + p.sk_per_cta - 1) / p.sk_per_cta;
+        // No whole tiles at all and room for `ways` CTAs per tile: cut every tile at the same places, so that each CTA
+        // holds exactly one piece (runs of a fixed length drift across tile borders and leave most CTAs with two).
+        if (p.dp_tiles == 0 && ways >= 2 && p.kb_total / ways >= 4) {
+            p.sk_ways = ways;
+            p.sk_ctas = p.sk_tiles * ways;
+            p.sk_per_cta = (p.kb_total + ways - 1) / ways;
+        }
         const size_t need = (size_t)p.sk_tiles * (fused ? 4 : Mpad) * BM * 8;
         if (need > WS_ACC_BYTES || (size_t)p.tiles * 4 > WS_CNT_BYTES) {
             p.dp_tiles = p.tiles;  // no room to park partial tiles: whole tiles only
             p.sk_tiles = 0;
             p.sk_per_cta = 0;
             p.sk_ctas = 0;
+            p.sk_ways = 0;
             if (grid > p.tiles) grid = p.tiles;
         }
     }
@@ -1131,7 +1161,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: clearing the scratch");
 
     const int Mi = (int)M, Mpad = 8, D = 4, NB = 32;
-    e = launch_pdl(digitize_x_kernel<float, 4>, dim3(Mpad), dim3(256), 0, st, x_f32, xq, factor, Mi, Mpad, (int)K, PeerPush{}, (long long*)nullptr, counters, (int)((N + BM - 1) / BM));
+    e = launch_pdl(digitize_x_kernel<float, 4>, dim3(Mpad), dim3(DIG_THREADS), 0, st, x_f32, xq, factor, Mi, Mpad, (int)K, PeerPush{}, (long long*)nullptr, counters, (int)((N + BM - 1) / BM));
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: digitize_x");
 
     TcParams p{};
