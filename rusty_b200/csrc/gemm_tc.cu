@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(DIG_THREADS) digitize_x_kernel(const XT* __res
         // wait until every rank has finished (and delivered) all earlier pushes
         if (tid == 0) peer_wait_all(push, 30);
         __syncthreads();
+        if (dbg && tid == 0 && m == 0) dbg[3] = (long long)globaltimer_ns();
     }
     if (m >= M) {
         for (int k = tid * 4; k < K; k += DIG_THREADS * 4)
@@ -814,8 +815,10 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         tc_fence_after();
         tmem_dealloc(tmem_base, p.tmem_cols);
     }
-    if (threadIdx.x == 0) peer_signal_cta_done(p.push, gridDim.x);  // after the barrier: every store of this CTA is issued
-    if (threadIdx.x == 32) DBG(15);
+    if (threadIdx.x == 0) {
+        peer_signal_cta_done(p.push);  // after the barrier: every store of this CTA is issued
+        DBG(15);
+    }
 }
 
 // ----------------------------------------------------------------------------

@@ -115,12 +115,10 @@ int launch_affine_dequantize_g64(rusty_cuda_ctx* ctx, const uint8_t* w, const fl
 
 // Exchange by peer stores (peer.cu): what a kernel needs to write its outputs into the other ranks' copies of y and
 // to tell them so.  Every rank owns an arena with the same layout; rank g's arena is mapped here at peer_base[g].
-//   ctl[0..7]  flags: ctl[g] = number of pushes of rank g that have landed in THIS arena (written by rank g)
-//   ctl[16]    epoch: pushes this rank has completed (local)
-//   ctl[17]    CTAs of the running push that have finished (local, zero between kernels)
+//   ctl[0..7]  ctl[g] = CTAs of rank g's pushing kernels whose outputs have landed in THIS arena (added to by rank g)
+//   ctl[16]    epoch: CTAs of this rank's pushing kernels that have finished (local)
 constexpr int PEER_MAX_RANKS = 8;
 constexpr int PEER_CTL_EPOCH = 16;
-constexpr int PEER_CTL_DONE = 17;
 struct PeerPush {
     int nranks, rank;                            // nranks <= 1: nothing to push, nothing to wait for
     unsigned int* ctl;                           // this rank's control block

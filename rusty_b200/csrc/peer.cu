@@ -9,10 +9,12 @@
 // that happens in its epilogue (gemm_tc.cu); the other kernels are followed by
 // a copy kernel.  Completion travels as one counter per rank per arena:
 //
-//   * the last CTA of a pushing kernel advances the local epoch and writes it
-//     into slot `rank` of every arena (after a system-scope fence);
+//   * every CTA of a pushing kernel, once its stores have been performed
+//     (system-scope fence), adds one to slot `rank` of every other arena and
+//     to the local epoch;
 //   * the next pushing operation, or rusty_cuda_arena_wait, first waits until
-//     all slots of the local arena have reached the local epoch.
+//     the other ranks' slots in the local arena have reached the local epoch
+//     (all ranks run the same grids, so equal counts mean "same kernels done").
 //
 // All ranks must enqueue the same sequence of pushing operations on an arena.
 // Waits are bounded (RUSTY_PEER_WAIT_MS, default 5000): a rank that never
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(256) peer_push_kernel(const uint8_t* __restric
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) peer_signal_cta_done(pp, gridDim.x);
+    if (threadIdx.x == 0) peer_signal_cta_done(pp);
 }
 
 }  // namespace

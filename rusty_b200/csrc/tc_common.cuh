@@ -10,7 +10,6 @@
 namespace rusty_tc {
 using rusty::PeerPush;
 using rusty::PEER_CTL_EPOCH;
-using rusty::PEER_CTL_DONE;
 using rusty::PEER_MAX_RANKS;
 
 constexpr long long WAIT_LIMIT_CYCLES = 8000000000ll;  // ~4 s of SM clock
@@ -83,6 +82,7 @@ __device__ __forceinline__ bool peer_wait_all(const PeerPush& pp, unsigned site)
     const unsigned int e = *reinterpret_cast<volatile unsigned int*>(pp.ctl + PEER_CTL_EPOCH);
     const unsigned long long t0 = globaltimer_ns();
     for (int g = 0; g < pp.nranks; ++g) {
+        if (g == pp.rank) continue;
         while ((int)(ld_acquire_sys_u32(pp.ctl + g) - e) < 0) {
             if (globaltimer_ns() - t0 > pp.wait_ns) {
                 if (atomicExch(&pp.status->timeout_flag, 1u) == 0u) pp.status->timeout_where = site;
@@ -94,19 +94,18 @@ __device__ __forceinline__ bool peer_wait_all(const PeerPush& pp, unsigned site)
     return true;
 }
 // Called by ONE thread of every CTA of a pushing kernel, after a CTA-wide barrier that follows the CTA's last
-// store.  The last CTA to arrive advances the local epoch and writes it into slot `rank` of every arena.
-__device__ __forceinline__ void peer_signal_cta_done(const PeerPush& pp, unsigned int n_ctas) {
+// store.  Progress is counted in CTAs: the CTA adds one to slot `rank` of every other arena once its stores have
+// been performed there (system-scope fence), and one to the local epoch.  All ranks run the same grids, so a
+// rank's slot in a peer's arena and that peer's own epoch meet when the rank's kernel has finished.
+__device__ __forceinline__ void peer_signal_cta_done(const PeerPush& pp) {
     if (pp.nranks <= 1) return;
-    __threadfence_system();
-    const unsigned int prev = atomicAdd(pp.ctl + PEER_CTL_DONE, 1u);
-    if (prev + 1u == n_ctas) {
-        __threadfence_system();
-        volatile unsigned int* ctl = pp.ctl;
-        ctl[PEER_CTL_DONE] = 0u;
-        const unsigned int e = ctl[PEER_CTL_EPOCH] + 1u;
-        ctl[PEER_CTL_EPOCH] = e;
-        for (int g = 0; g < pp.nranks; ++g) st_release_sys_u32(pp.peer_ctl[g] + pp.rank, e);
-    }
+    // The release on each add orders it after this CTA's stores (the CTA-wide barrier before the call makes the other
+    // threads' stores part of what is released); a separate sequentially consistent system fence here cost ~7 us.
+#pragma unroll
+    for (int g = 0; g < PEER_MAX_RANKS; ++g)  // static indices: a run-time index would copy the table to local memory
+        if (g < pp.nranks && g != pp.rank)
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(pp.peer_ctl[g] + pp.rank) : "memory");
+    asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" ::"l"(pp.ctl + PEER_CTL_EPOCH) : "memory");
 }
 
 // Programmatic dependent launch: let the next kernel in the stream start its
