@@ -222,6 +222,8 @@ def main():
     ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
                     help="N > 1: how a rank's output columns reach the other ranks: stores from the kernel's epilogue "
                          "into every rank's memory (push) or an NCCL all-gather after each Linear (nccl)")
+    ap.add_argument("--no-swiglu", action="store_true",
+                    help="write gate|up as [M, 2*ffn] instead of applying silu(gate)*up in the kernel's epilogue")
     ap.add_argument("--single", default=None, metavar="MxKxN:f32|bf16",
                     help="run ONE fused linear of this shape --steps times on rotating weight copies and print its "
                          "timing (small case for profiler captures; not the benchmark line)")
@@ -266,7 +268,8 @@ def main():
     ctx = rusty_b200.CudaContext(local_rank)
     eng = rusty_b200.ComputeEngine(ctx)
     shape = STACKS[stack_name]
-    stack = LinearStack(ctx, shape, M, DType.FP32, DType.FP32, seed=0, rank=rank, world=world, layers=args.layers)
+    stack = LinearStack(ctx, shape, M, DType.FP32, DType.FP32, seed=0, rank=rank, world=world, layers=args.layers,
+                        swiglu=not args.no_swiglu)
     if world > 1:
         from rusty_b200.shard import PushedStack, ShardedStack
         runner = PushedStack(stack, dist) if args.exchange == "push" else ShardedStack(stack, dist)
@@ -335,7 +338,8 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "desc": desc, "batch_rows": M, "linears_per_step": stack.num_linears(),
-                   "weights": "int8 [out,in], f32 scale per output row; q|k|v and gate|up stored back to back and run as one Linear each", "activations": "f32 in, f32 out, fp32 accumulate",
+                   "weights": "int8 [out,in], f32 scale per output row; q|k|v and gate|up run as one Linear each" + (
+                       "; gate|up rows pair-interleaved, silu(gate)*up applied in the kernel epilogue ([M, ffn] out)" if stack.swiglu else ""), "activations": "f32 in, f32 out, fp32 accumulate",
                    "parallelism": ("1 GPU" if world == 1 else f"output-feature shards x{world}, " + (
                        "outputs stored into every rank's memory by the kernel epilogue (NVLink peer stores)"
                        if args.exchange == "push" else "NCCL all-gather after each Linear")),

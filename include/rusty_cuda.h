@@ -244,6 +244,23 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_sharded_batch(rusty_cuda_ctx* ctx,
                                                             rusty_cuda_buf* gather_ws, rusty_cuda_buf* const* ys,
                                                             int y_dtype);
 
+/* ---- SwiGLU glue of the MLP (rusty-graph/src/lib.rs:317-323) ------------------
+ * MLP::forward is gate = Linear, silu(gate), up = Linear, mul, down = Linear.  The two unfused shaders: */
+/* WGSL `silu` (kernels.wgsl:104-113): out[i] = x[i] * (1 / (1 + exp(-x[i]))), f32. */
+RUSTY_CUDA_API int rusty_cuda_silu_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* x, rusty_cuda_buf* out, size_t n);
+/* WGSL `mul` (kernels.wgsl:146-151): out[i] = a[i] * b[i], f32. */
+RUSTY_CUDA_API int rusty_cuda_mul_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* a, const rusty_cuda_buf* b,
+                                      rusty_cuda_buf* out, size_t n);
+/* And the fused form (no counterpart in the reference): a gate|up weight stored pair-interleaved, row 2j = gate_j,
+ * row 2j+1 = up_j (RUSTY_CUDA_LAYOUT_NK, RUSTY_CUDA_QMODE_SYM_ROW, N even).  After
+ * rusty_cuda_qlinear_set_activation(ql, RUSTY_CUDA_ACT_SWIGLU_PAIRS) every forward of `ql` (plain, batch, sharded,
+ * pushed) writes y[M, N/2] with y[m,j] = silu(x.gate_j) * (x.up_j): the activation runs in the kernel's epilogue and
+ * the [M, N] intermediate never exists.  Row shards must hold whole pairs.  Kernels without the fused epilogue
+ * answer RUSTY_CUDA_ERR_UNSUPPORTED. */
+#define RUSTY_CUDA_ACT_NONE 0
+#define RUSTY_CUDA_ACT_SWIGLU_PAIRS 1
+RUSTY_CUDA_API int rusty_cuda_qlinear_set_activation(rusty_cuda_qlinear* ql, int act);
+
 /* ---- exchange by peer stores over NVLink (no counterpart in the reference) ----
  * The second multi-GPU form of Linear::forward (rusty-graph/src/lib.rs:69-70):
  * instead of an all-gather after the kernel, each rank's kernel stores its

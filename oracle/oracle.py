@@ -211,3 +211,30 @@ def np_matmul_seq(a, b_kn) -> np.ndarray:
     for k in range(a.shape[1]):
         acc = acc + (a[:, k:k + 1] * b_kn[k:k + 1, :]).astype(np.float32)
     return acc
+
+
+def silu(x) -> np.ndarray:
+    """`silu` shader: x * (1 / (1 + exp(-x)))."""
+    a, pa = _f32(np.ravel(x))
+    out = np.empty(a.size, np.float32)
+    lib().oracle_silu(pa, out.ctypes.data_as(_f32p), C.c_size_t(a.size))
+    return out.reshape(np.shape(x))
+
+
+def mul(a, b) -> np.ndarray:
+    """`mul` shader: elementwise product."""
+    x, px = _f32(np.ravel(a))
+    y, py = _f32(np.ravel(b))
+    assert x.size == y.size
+    out = np.empty(x.size, np.float32)
+    lib().oracle_mul(px, py, out.ctypes.data_as(_f32p), C.c_size_t(x.size))
+    return out.reshape(np.shape(a))
+
+
+def swiglu_pairs(s) -> np.ndarray:
+    """[M, 2F] with (gate_j, up_j) in columns (2j, 2j+1) -> [M, F] = silu(gate) * up (MLP::forward order)."""
+    s2 = np.ascontiguousarray(s, np.float32)
+    M, F2 = s2.shape
+    out = np.empty((M, F2 // 2), np.float32)
+    lib().oracle_swiglu_pairs(s2.ctypes.data_as(_f32p), out.ctypes.data_as(_f32p), C.c_uint32(M), C.c_uint32(F2 // 2))
+    return out

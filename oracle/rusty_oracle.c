@@ -292,3 +292,28 @@ ORACLE_API void oracle_qlinear_rowscale_fused_mt_simd(const float* x, const int8
         }
     }
 }
+
+/* ---- SwiGLU glue of the MLP (the step between gate|up and down) ------------
+ * WGSL `silu` (rusty-backend/src/kernels.wgsl:104-113): out = x * (1.0 / (1.0 + exp(-x))).
+ * WGSL `mul`  (kernels.wgsl:146-151): out = a * b.
+ * MLP::forward (rusty-graph/src/lib.rs:317-323) applies SiLU to the GATE projection and multiplies by UP
+ * (the unused `silu_gate_fused` shader, kernels.wgsl:527-542, applies it to `up`; MLP::forward is followed).
+ * exp is libm's expf here; WGSL leaves its accuracy to the driver, so results are compared with a tolerance. */
+ORACLE_API void oracle_silu(const float* x, float* out, size_t n) {
+    for (size_t i = 0; i < n; ++i) out[i] = x[i] * (1.0f / (1.0f + expf(-x[i])));
+}
+
+ORACLE_API void oracle_mul(const float* a, const float* b, float* out, size_t n) {
+    for (size_t i = 0; i < n; ++i) out[i] = a[i] * b[i];
+}
+
+/* s is [M, 2F] with gate_j in column 2j and up_j in column 2j+1 (the row order of a pair-interleaved gate|up
+ * weight); out[M, F] = silu(gate) * up, composed from the two shaders above. */
+ORACLE_API void oracle_swiglu_pairs(const float* s, float* out, uint32_t M, uint32_t F) {
+    for (uint32_t m = 0; m < M; ++m)
+        for (uint32_t j = 0; j < F; ++j) {
+            float g = s[(size_t)m * 2 * F + 2 * j], u = s[(size_t)m * 2 * F + 2 * j + 1], act;
+            oracle_silu(&g, &act, 1);
+            oracle_mul(&act, &u, &out[(size_t)m * F + j], 1);
+        }
+}

@@ -201,6 +201,15 @@ class UnifiedTensor:
         return raw[: raw.size // 4 * 4].view(np.float32)
 
 
+def interleave_pairs(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """Rows (or entries) a_0, b_0, a_1, b_1, ... of two equally shaped arrays."""
+    a, b = np.asarray(a), np.asarray(b)
+    assert a.shape == b.shape and a.dtype == b.dtype
+    out = np.empty((2 * a.shape[0],) + a.shape[1:], a.dtype)
+    out[0::2], out[1::2] = a, b
+    return out
+
+
 class QLinear:
     """A weight kept in its 1-byte quantised form on the device."""
 
@@ -229,6 +238,24 @@ class QLinear:
         st = UnifiedTensor.new(ctx, np.asarray(scales, np.float32).ravel(), [int(np.size(scales))])
         bt = UnifiedTensor.new(ctx, np.asarray(biases, np.float32).ravel(), [int(np.size(biases))]) if affine else None
         return QLinear(ctx, wt, st, bt, N, K, layout, capi.QMODE_AFFINE_G64 if affine else capi.QMODE_SYM_ROW)
+
+    def set_activation(self, act: int) -> "QLinear":
+        """capi.ACT_SWIGLU_PAIRS: rows (2j, 2j+1) are (gate_j, up_j); every forward then writes silu(gate) * up,
+        N/2 columns (MLP::forward, rusty-graph/src/lib.rs:317-323, with the activation in the kernel's epilogue)."""
+        check(lib().rusty_cuda_qlinear_set_activation(self._h, act), self.ctx.handle)
+        self.act = act
+        return self
+
+    @property
+    def out_features(self) -> int:
+        return self.N // 2 if getattr(self, "act", 0) == capi.ACT_SWIGLU_PAIRS else self.N
+
+    @staticmethod
+    def from_gate_up(ctx: CudaContext, gate_q: np.ndarray, gate_s: np.ndarray, up_q: np.ndarray,
+                     up_s: np.ndarray) -> "QLinear":
+        """Interleave two [F, K] int8 projections row by row (gate_0, up_0, gate_1, ...) and enable the pair epilogue."""
+        q, s = interleave_pairs(gate_q, up_q), interleave_pairs(gate_s, up_s)
+        return QLinear.from_host(ctx, q, s).set_activation(capi.ACT_SWIGLU_PAIRS)
 
     def plan(self, M: int, x_dtype: DType = DType.FP32, y_dtype: DType = DType.FP32) -> str:
         buf = C.create_string_buffer(64)
@@ -276,6 +303,14 @@ class ComputeEngine:
 
     def copy_tensor(self, ctx: CudaContext, src: UnifiedTensor, dst: UnifiedTensor, dst_offset: int) -> None:
         check(lib().rusty_cuda_buf_copy(ctx.handle, src.buffer(), dst.buffer(), dst_offset), ctx.handle)
+
+    def silu(self, ctx: CudaContext, x: UnifiedTensor, out: UnifiedTensor) -> None:
+        total = int(np.prod(out.shape, dtype=np.int64))
+        check(lib().rusty_cuda_silu_f32(ctx.handle, x.buffer(), out.buffer(), total), ctx.handle)
+
+    def mul(self, ctx: CudaContext, a: UnifiedTensor, b: UnifiedTensor, out: UnifiedTensor) -> None:
+        total = int(np.prod(out.shape, dtype=np.int64))
+        check(lib().rusty_cuda_mul_f32(ctx.handle, a.buffer(), b.buffer(), out.buffer(), total), ctx.handle)
 
     def qlinear(self, ctx: CudaContext, x: UnifiedTensor, w: QLinear, out: UnifiedTensor) -> None:
         """out[M,N] = x[M,K] (.) w, fused dequantise + multiply."""

@@ -35,6 +35,7 @@ STATUS_NAMES = {
 F32, F16, BF16, I8, U8 = 0, 1, 2, 3, 4
 QMODE_AFFINE_G64, QMODE_SYM_ROW = 0, 1
 LAYOUT_NK, LAYOUT_KN = 0, 1
+ACT_NONE, ACT_SWIGLU_PAIRS = 0, 1
 
 _vp = C.c_void_p
 _vpp = C.POINTER(C.c_void_p)
@@ -82,6 +83,9 @@ SIGNATURES = {
     "rusty_cuda_comm_check": ([_vp], _int),
     "rusty_cuda_qlinear_forward_sharded": ([_vp, _vp, _vp, _vp, _int, _u32, _vp, _vp, _int], _int),
     "rusty_cuda_qlinear_forward_sharded_batch": ([_vp, _vp, _sz, _vpp, _vpp, _int, _u32, _vp, _vpp, _int], _int),
+    "rusty_cuda_silu_f32": ([_vp, _vp, _vp, _sz], _int),
+    "rusty_cuda_mul_f32": ([_vp, _vp, _vp, _vp, _sz], _int),
+    "rusty_cuda_qlinear_set_activation": ([_vp, _int], _int),
     "rusty_cuda_arena_create": ([_vp, _sz, _int, _int, _vpp], _int),
     "rusty_cuda_arena_export": ([_vp, _vp], _int),
     "rusty_cuda_arena_attach": ([_vp, _vp], _int),

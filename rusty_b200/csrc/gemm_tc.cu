@@ -207,6 +207,7 @@ struct TcParams {
     int dp_tiles, sk_tiles, sk_per_cta, sk_ctas;
     int sk_ways;             // > 0: every shared tile is cut into this many near-equal pieces, one per CTA (CTA = tile * ways + piece)
     int ldy, y_col0;
+    int act;                 // RUSTY_CUDA_ACT_SWIGLU_PAIRS: rows 2j, 2j+1 -> y[:, (y_col0 + 2j) / 2] = silu(gate) * up
     int stages;
     int red_bytes;           // epilogue staging area: a partial tile (Mpad x 128 x 8 bytes), at least 12 KiB
     uint32_t idesc;
@@ -290,19 +291,31 @@ struct PeerOut {
     int n;                   // number of other ranks (0: no exchange)
     const long long* delta;  // [n] in shared memory
 };
+// Every lane of the warp must call this together (the pair epilogue exchanges values between neighbouring lanes);
+// `live` says whether this lane's output exists.  Lane parity equals the parity of n at every call site.
 template <typename YT>
 __device__ __forceinline__ void finalize_store_f(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, float row_factor,
-                                                 const PeerOut& po) {
-    const float v = __ll2float_rn(acc) * row_factor * scale_n;
-    YT* dst = y + (size_t)m * p.ldy + p.y_col0 + n;
+                                                 const PeerOut& po, bool live) {
+    float v = __ll2float_rn(acc) * row_factor * scale_n;
+    int col = p.y_col0 + n;
+    if (p.act) {
+        // rows 2j / 2j+1 are gate_j / up_j: the even lane takes its neighbour's value and writes silu(gate) * up
+        // (rusty-graph/src/lib.rs:317-323; silu as kernels.wgsl:104-113)
+        const float up = __shfl_down_sync(0xffffffffu, v, 1);
+        live = live && !(n & 1);
+        v = (v * (1.0f / (1.0f + expf(-v)))) * up;
+        col >>= 1;
+    }
+    if (!live) return;
+    YT* dst = y + (size_t)m * p.ldy + col;
     store_y<YT>(dst, v);
     // exchange fused into the epilogue: the same element of every other rank's y, over NVLink
     for (int g = 0; g < po.n; ++g) store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<char*>(dst) + po.delta[g]), v);
 }
 template <typename YT>
 __device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, const float* s_rowf,
-                                               const PeerOut& po) {
-    finalize_store_f<YT>(p, y, n, m, acc, scale_n, s_rowf[m], po);
+                                               const PeerOut& po, bool live) {
+    finalize_store_f<YT>(p, y, n, m, acc, scale_n, s_rowf[m], po, live);
 }
 
 // Four consecutive activations x[m, k..k+3] as f32 (zeros beyond K); K % 4 == 0.
@@ -606,13 +619,16 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (*abort_flag) { ok = false; break; }
                 int4* tile_sum = reinterpret_cast<int4*>(p.part) + (size_t)(t - p.dp_tiles) * (p.Mpad / 2) * BM;
-                const int lo = j * BM / nseg, rows = (j + 1) * BM / nseg - lo;  // this CTA's share of the tile's rows
+                // this CTA's share of the tile's rows, cut in units of two rows so that a (gate, up) pair stays together
+                const int lo = 2 * (j * (BM / 2) / nseg), rows = 2 * ((j + 1) * (BM / 2) / nseg) - lo;
                 const int items = rows * (p.Mpad / 2);                         // one item: a row, two activation rows
                 if (rows <= 0) continue;
                 // item -> (row, mp) without a division per item: start at (et % rows, et / rows), step by EPI_THREADS items
                 int row = et % rows, mp = et / rows;
                 const int step_row = EPI_THREADS % rows, step_mp = EPI_THREADS / rows;
-                for (int it0 = et; it0 < items; it0 += 4 * EPI_THREADS) {
+                // the loop bounds are the same for every thread: the pair epilogue needs whole warps
+                for (int base = 0; base < items; base += 4 * EPI_THREADS) {
+                    const int it0 = base + et;
                     int4 v[4];
                     float sc[4];
                     int rw[4], mq[4];
@@ -645,12 +661,12 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 #pragma unroll 1
                     for (int u = 0; u < 4; ++u) {
                         const int at = stage_at[u * EPI_THREADS + et];
-                        if (at < 0) continue;
+                        const bool live = at >= 0;
                         const longlong2 two = *reinterpret_cast<const longlong2*>(&stage_red[u * EPI_THREADS + et]);
                         const float scu = stage_sc[u * EPI_THREADS + et];
-                        const int nn = t * BM + (at & 0xff), m = 2 * (at >> 8);
-                        if (m < p.M) finalize_store<YT>(p, y, nn, m, two.x, scu, s_rowf, po);
-                        if (m + 1 < p.M) finalize_store<YT>(p, y, nn, m + 1, two.y, scu, s_rowf, po);
+                        const int nn = t * BM + (at & 0xff), m = live ? 2 * (at >> 8) : 0;
+                        finalize_store<YT>(p, y, nn, m, two.x, scu, s_rowf, po, live && m < p.M);
+                        finalize_store<YT>(p, y, nn, m + 1, two.y, scu, s_rowf, po, live && m + 1 < p.M);
                     }
                 }
                 if (threadIdx.x == 64) DBG(11);
@@ -689,7 +705,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
                 if (sg.nseg == 1) {
                     if (row_ok)
-                        for (int m = 0; m < p.M; ++m) finalize_store_f<YT>(p, y, n, m, acc[m], sc, s_factor[m], po);
+                        for (int m = 0; m < p.M; ++m) finalize_store_f<YT>(p, y, n, m, acc[m], sc, s_factor[m], po, true);
                 } else {
                     // a piece of a K-cut tile: 64-bit integer reductions straight from registers (exact, any order)
                     const int lt = sg.t - p.dp_tiles;
@@ -713,7 +729,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                             for (int m = 0; m < 4; ++m)
                                 if (m < p.M) {
                                     __stcg(tile_sum + (size_t)m * BM + r, 0ull);
-                                    finalize_store_f<YT>(p, y, n, m, tot[m], sc, s_factor[m], po);
+                                    finalize_store_f<YT>(p, y, n, m, tot[m], sc, s_factor[m], po, true);
                                 }
                         }
                         if (threadIdx.x == 64) p.counters[sg.t] = 0u;
@@ -728,16 +744,14 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     for (int d = 0; d < 4; ++d)
                         if (d < p.D) tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c[d]);
                     tmem_ld_wait();
-                    if (row_ok) {
 #pragma unroll
-                        for (int mm = 0; mm < 8; ++mm) {
-                            if (m0 + mm < p.M) {
-                                long long acc = c[0][mm];
+                    for (int mm = 0; mm < 8; ++mm) {
+                        if (m0 + mm < p.M) {  // the same for the whole warp
+                            long long acc = c[0][mm];
 #pragma unroll
-                                for (int d = 1; d < 4; ++d)
-                                    if (d < p.D) acc = acc * 128 + c[d][mm];
-                                finalize_store<YT>(p, y, n, m0 + mm, acc, sc, s_rowf, po);
-                            }
+                            for (int d = 1; d < 4; ++d)
+                                if (d < p.D) acc = acc * 128 + c[d][mm];
+                            finalize_store<YT>(p, y, n, m0 + mm, acc, sc, s_rowf, po, row_ok);
                         }
                     }
                 }
@@ -1004,6 +1018,7 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     if (p.dp_tiles == 0 && p.sk_ctas > 0) grid = p.sk_ctas;
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
+    p.act = a.act;
     p.status = ctx->status_dev;
     p.dbg = dbg;
     p.push = push;

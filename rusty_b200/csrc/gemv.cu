@@ -83,7 +83,7 @@ __device__ __forceinline__ int xs_index(int m, int nchunks, int k) {
 template <int MB, int R, int U, bool AFFINE, typename XT, typename YT>
 __global__ void __launch_bounds__(GEMV_THREADS, (MB <= 2 ? 2 : 1))
 gemv_nk_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, const float* __restrict__ biases,
-               const XT* __restrict__ x, YT* __restrict__ y, int M, int N, int K, int ldy, int y_col0) {
+               const XT* __restrict__ x, YT* __restrict__ y, int M, int N, int K, int ldy, int y_col0, int act) {
     extern __shared__ __align__(16) float smem[];
     const int nchunks = (K + CHUNK - 1) / CHUNK;
     float* xs = smem;
@@ -216,7 +216,19 @@ gemv_nk_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
                     for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
                     acc[r][m] = v;
                 }
-            if (lane == 0) {
+            if (lane == 0 && act) {
+                // the warp's two rows are one (gate, up) pair: y[m, pair] = silu(x.gate) * (x.up), as MLP::forward composes it
+                static_assert(R == 2, "pairs need two rows per warp");
+                if (n0 + 1 < N) {
+                    const float s0 = AFFINE ? 1.0f : __ldg(scales + n0), s1 = AFFINE ? 1.0f : __ldg(scales + n0 + 1);
+#pragma unroll
+                    for (int m = 0; m < MB; ++m)
+                        if (m < M) {
+                            const float g = AFFINE ? acc[0][m] : acc[0][m] * s0, u = AFFINE ? acc[1][m] : acc[1][m] * s1;
+                            store_out<YT>(y + (size_t)m * ldy + ((y_col0 + n0) >> 1), (g * (1.0f / (1.0f + expf(-g)))) * u);
+                        }
+                }
+            } else if (lane == 0) {
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     int n = n0 + r;
@@ -353,7 +365,7 @@ int launch_nk(rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a, const void* x, v
     int max_blocks = ctx->sm_count * per_sm;
     if (blocks > max_blocks) blocks = max_blocks;
     cudaError_t le = rusty_tc::launch_pdl(kern, dim3(blocks), dim3(GEMV_THREADS), smem, ctx->stream, a.w, a.scales, a.biases,
-                                          (const XT*)x, (YT*)y, M, (int)a.N, (int)a.K, (int)a.ldy, (int)a.y_col0);
+                                          (const XT*)x, (YT*)y, M, (int)a.N, (int)a.K, (int)a.ldy, (int)a.y_col0, a.act);
     if (le != cudaSuccess) return rusty::check_cuda(ctx, le, "gemv_nk");
     return rusty::after_launch(ctx, "gemv_nk");
 }
@@ -421,6 +433,7 @@ namespace rusty {
 
 bool gemv_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
     if (a.layout == RUSTY_CUDA_LAYOUT_NK) return a.K % 16 == 0;
+    if (a.act) return false;  // pairs are rows of an [out,in] matrix
     return a.N % 16 == 0;
 }
 

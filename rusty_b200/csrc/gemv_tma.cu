@@ -253,6 +253,7 @@ namespace rusty {
 
 bool gemv_tma_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
     if (a.layout != RUSTY_CUDA_LAYOUT_NK || a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
+    if (a.act) return false;  // the pair epilogue lives in the CUDA-core GEMV and the int8 tensor-core kernel
     if (a.M < 1 || a.M > 2) return false;
     if (a.K % 16 != 0 || a.K > (uint32_t)((a.M == 1 ? MAXJ : 2) * CHUNKS_PER_PASS * 16)) return false;
     static const bool off = getenv("RUSTY_NO_GEMV_TMA") != nullptr;

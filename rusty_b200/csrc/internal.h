@@ -78,6 +78,7 @@ struct rusty_cuda_qlinear {
     rusty_cuda_buf* biases = nullptr;
     uint32_t N = 0, K = 0;
     int layout = 0, qmode = 0;
+    int act = 0;  // RUSTY_CUDA_ACT_*: applied to pairs of output features in the kernel's epilogue
 };
 
 namespace rusty {
@@ -141,6 +142,9 @@ struct QLinearArgs {
     int y_dtype;
     uint32_t ldy;    // row stride of y in elements (>= N)
     uint32_t y_col0; // first output column written (for shards writing into a wider y)
+    // RUSTY_CUDA_ACT_SWIGLU_PAIRS: rows 2j / 2j+1 of w are gate_j / up_j; the kernel writes silu(gate)*up into column
+    // (y_col0 + 2j) / 2, so y has N/2 columns per call, ldy counts those, and y_col0 (even) still counts rows of w
+    int act;
     // Non-null: y lies in a peer arena; the kernel also stores every output into the other ranks' arenas and
     // signals them (honoured by the kernels for which qlinear_pushes_fused() is true).
     const PeerPush* push = nullptr;

@@ -213,7 +213,9 @@ int rusty_cuda_qlinear_forward_pushed(rusty_cuda_ctx* ctx, rusty_cuda_arena* are
     const size_t ys = y_dtype == RUSTY_CUDA_BF16 ? 2 : y_dtype == RUSTY_CUDA_F32 ? 4 : 0;
     if (!ys) return fail(ctx, RUSTY_CUDA_ERR_INVALID_DATA_TYPE, "qlinear_forward_pushed: y must be f32 or bf16");
     const int G = arena->nranks;
-    const uint32_t Nl = ql_shard->N, N = Nl * (uint32_t)G, col0 = Nl * (uint32_t)arena->rank;
+    // with the pair activation a shard of Nl rows yields Nl/2 columns; col0 keeps counting rows of the whole weight
+    const uint32_t Nl = ql_shard->N, col0 = Nl * (uint32_t)arena->rank;
+    const uint32_t Nl_out = ql_shard->act ? Nl / 2 : Nl, N = Nl_out * (uint32_t)G, col0_out = ql_shard->act ? col0 / 2 : col0;
     const uint8_t* lo = arena->base + ARENA_CTL_BYTES;
     const uint8_t* yp = (const uint8_t*)y_full->ptr;
     if (yp < lo || yp > lo + arena->data_bytes || y_full->bytes > (size_t)(lo + arena->data_bytes - yp))
@@ -235,8 +237,8 @@ int rusty_cuda_qlinear_forward_pushed(rusty_cuda_ctx* ctx, rusty_cuda_arena* are
     }
     int rc = qlinear_forward_cols(ctx, ql_shard, x, x_dtype, M, y_full, y_dtype, N, col0, nullptr);
     if (rc || G == 1) return rc;
-    const uint8_t* slice = yp + (size_t)col0 * ys;
-    const size_t row_bytes = (size_t)Nl * ys, ld_bytes = (size_t)N * ys;
+    const uint8_t* slice = yp + (size_t)col0_out * ys;
+    const size_t row_bytes = (size_t)Nl_out * ys, ld_bytes = (size_t)N * ys;
     const int vec = (row_bytes % 16 == 0 && ld_bytes % 16 == 0 && ((uintptr_t)slice & 15) == 0) ? 16 : (int)(ys == 4 ? 4 : 2);
     const size_t work = (size_t)M * (row_bytes / vec);
     size_t blocks = (work + 255) / 256, cap = (size_t)ctx->sm_count * 4;

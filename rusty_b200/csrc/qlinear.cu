@@ -41,9 +41,11 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
     a.x_dtype = x_dtype;
     a.y_dtype = y_dtype;
     a.M = M;
-    if (f16tc2_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16_pair";
-    if (f16tc_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16";
-    if (tc_supported(ql->ctx, a) && M >= tc_min_rows()) return "tcgen05";
+    a.act = ql->act;
+    // the bf16 prefill kernels have no activation epilogue: batches of pairs go through the int8 kernel in 64-row passes
+    if (!a.act && f16tc2_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16_pair";
+    if (!a.act && f16tc_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16";
+    if (tc_supported(ql->ctx, a) && M >= tc_min_rows() && (!a.act || tc_pushes_fused(M))) return "tcgen05";
     if (gemv_tma_supported(ql->ctx, a)) return "gemv_tma";
     if (gemv_supported(ql->ctx, a)) return "gemv";
     return "unsupported";
@@ -61,9 +63,12 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
     if (!xs || !ys)
         return fail(ctx, RUSTY_CUDA_ERR_INVALID_DATA_TYPE, "qlinear_forward: x/y must be f32 or bf16 (got %d, %d)", x_dtype,
                     y_dtype);
-    if (ldy < y_col0 + ql->N)
-        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward: row stride %u < first column %u + N %u", ldy,
-                    y_col0, ql->N);
+    const uint32_t out_cols = ql->act ? (y_col0 + ql->N) / 2 : y_col0 + ql->N;  // columns of y this call reaches
+    if (ldy < out_cols)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward: row stride %u < first column %u + N %u%s", ldy,
+                    y_col0, ql->N, ql->act ? " (pairs: halved)" : "");
+    if (ql->act && (y_col0 & 1u))
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward: a shard of pairs starts at an even row, got %u", y_col0);
     if (x->bytes < (size_t)M * ql->K * xs)
         return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward: x holds %zu bytes, [%u,%u] needs %zu", x->bytes, M,
                     ql->K, (size_t)M * ql->K * xs);
@@ -86,15 +91,16 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
     a.y_dtype = y_dtype;
     a.ldy = ldy;
     a.y_col0 = y_col0;
+    a.act = ql->act;
     if (push && push->nranks > 1) {
         if (!qlinear_pushes_fused(ql, x_dtype, M, y_dtype))
             return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: the kernel for this shape does not push to peers");
         a.push = push;
     }
     DeviceGuard g(ctx->device);
-    if (f16tc2_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc2(ctx, a);
-    if (f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
-    if (tc_supported(ctx, a) && M >= tc_min_rows()) return launch_tc(ctx, a);
+    if (!a.act && f16tc2_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc2(ctx, a);
+    if (!a.act && f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
+    if (tc_supported(ctx, a) && M >= tc_min_rows() && (!a.act || tc_pushes_fused(M))) return launch_tc(ctx, a);
     if (gemv_tma_supported(ctx, a)) return launch_gemv_tma(ctx, a);
     if (gemv_supported(ctx, a)) return launch_gemv(ctx, a);
     return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED,
@@ -157,6 +163,20 @@ int rusty_cuda_qlinear_create(rusty_cuda_ctx* ctx, rusty_cuda_buf* weight, rusty
     return RUSTY_CUDA_OK;
 }
 
+int rusty_cuda_qlinear_set_activation(rusty_cuda_qlinear* ql, int act) {
+    if (!ql) return fail(nullptr, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_set_activation: null qlinear");
+    if (act != RUSTY_CUDA_ACT_NONE && act != RUSTY_CUDA_ACT_SWIGLU_PAIRS)
+        return fail(ql->ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_set_activation: unknown activation %d", act);
+    if (act == RUSTY_CUDA_ACT_SWIGLU_PAIRS) {
+        if (ql->layout != RUSTY_CUDA_LAYOUT_NK || ql->qmode != RUSTY_CUDA_QMODE_SYM_ROW)
+            return fail(ql->ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "qlinear_set_activation: pairs need [out,in] storage with one scale per row");
+        if (ql->N % 2 != 0)
+            return fail(ql->ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_set_activation: %u rows are not whole (gate, up) pairs", ql->N);
+    }
+    ql->act = act;
+    return RUSTY_CUDA_OK;
+}
+
 int rusty_cuda_qlinear_destroy(rusty_cuda_qlinear* ql) {
     if (!ql) return RUSTY_CUDA_OK;
     rusty_cuda_buf_release(ql->weight);
@@ -170,7 +190,7 @@ int rusty_cuda_qlinear_forward(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql
                                uint32_t M, rusty_cuda_buf* y, int y_dtype) {
     RUSTY_REQUIRE_CTX(ctx);
     if (!ql) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: null qlinear");
-    return qlinear_forward_cols(ctx, ql, x, x_dtype, M, y, y_dtype, ql->N, 0);
+    return qlinear_forward_cols(ctx, ql, x, x_dtype, M, y, y_dtype, ql->act ? ql->N / 2 : ql->N, 0);
 }
 
 int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t n, const rusty_cuda_qlinear* const* qls,
@@ -180,7 +200,7 @@ int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t n, const rusty_
     if (n && (!qls || !xs || !ys)) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_batch: null array");
     for (size_t i = 0; i < n; ++i) {
         if (!qls[i]) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_batch: entry %zu is null", i);
-        int rc = qlinear_forward_cols(ctx, qls[i], xs[i], x_dtype, M, ys[i], y_dtype, qls[i]->N, 0);
+        int rc = qlinear_forward_cols(ctx, qls[i], xs[i], x_dtype, M, ys[i], y_dtype, qls[i]->act ? qls[i]->N / 2 : qls[i]->N, 0);
         if (rc) return rc;
     }
     return RUSTY_CUDA_OK;

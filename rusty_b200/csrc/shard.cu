@@ -153,7 +153,7 @@ int rusty_cuda_qlinear_forward_sharded(rusty_cuda_ctx* ctx, rusty_cuda_comm* com
     const size_t ys = y_dtype == RUSTY_CUDA_BF16 ? 2 : y_dtype == RUSTY_CUDA_F32 ? 4 : 0;
     if (!ys) return fail(ctx, RUSTY_CUDA_ERR_INVALID_DATA_TYPE, "qlinear_forward_sharded: y must be f32 or bf16");
     const int G = comm->nranks;
-    const uint32_t Nl = ql_shard->N;
+    const uint32_t Nl = ql_shard->act ? ql_shard->N / 2 : ql_shard->N;  // output columns of this rank
     const size_t shard_bytes = (size_t)M * Nl * ys;
     if (gather_ws->bytes < shard_bytes * G || y_full->bytes < shard_bytes * G)
         return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward_sharded: gather workspace and y need %zu bytes each",

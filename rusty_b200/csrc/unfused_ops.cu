@@ -157,6 +157,22 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ 
     for (; i < n; i += stride) out[i] = __fadd_rn(a[i], b[i]);
 }
 
+// WGSL `silu` (kernels.wgsl:104-113) and `mul` (kernels.wgsl:146-151), one element per thread as there.
+__global__ void __launch_bounds__(256) silu_f32_kernel(const float* __restrict__ x, float* __restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        const float v = x[i];
+        out[i] = __fmul_rn(v, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v))));
+    }
+}
+__global__ void __launch_bounds__(256) mul_f32_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                      float* __restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) out[i] = __fmul_rn(a[i], b[i]);
+}
+
 }  // namespace
 
 namespace rusty {
@@ -252,6 +268,34 @@ int rusty_cuda_add_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* a, const rusty
     if (blocks > cap) blocks = cap;
     add_f32_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float*)a->ptr, (const float*)b->ptr, (float*)out->ptr, n);
     return after_launch(ctx, "add_f32");
+}
+
+int rusty_cuda_silu_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* x, rusty_cuda_buf* out, size_t n) {
+    RUSTY_REQUIRE_CTX(ctx);
+    int rc;
+    if ((rc = need(ctx, "silu", "x", x, n * 4))) return rc;
+    if ((rc = need(ctx, "silu", "out", out, n * 4))) return rc;
+    if (n == 0) return RUSTY_CUDA_OK;
+    DeviceGuard g(ctx->device);
+    size_t blocks = (n + 255) / 256, cap = (size_t)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    silu_f32_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float*)x->ptr, (float*)out->ptr, n);
+    return after_launch(ctx, "silu_f32");
+}
+
+int rusty_cuda_mul_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* a, const rusty_cuda_buf* b, rusty_cuda_buf* out,
+                       size_t n) {
+    RUSTY_REQUIRE_CTX(ctx);
+    int rc;
+    if ((rc = need(ctx, "mul", "a", a, n * 4))) return rc;
+    if ((rc = need(ctx, "mul", "b", b, n * 4))) return rc;
+    if ((rc = need(ctx, "mul", "out", out, n * 4))) return rc;
+    if (n == 0) return RUSTY_CUDA_OK;
+    DeviceGuard g(ctx->device);
+    size_t blocks = (n + 255) / 256, cap = (size_t)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    mul_f32_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float*)a->ptr, (const float*)b->ptr, (float*)out->ptr, n);
+    return after_launch(ctx, "mul_f32");
 }
 
 int rusty_cuda_dequantize_u8(rusty_cuda_ctx* ctx, const rusty_cuda_buf* in, rusty_cuda_buf* out, size_t n_in) {

@@ -148,8 +148,15 @@ public:
     QWeight(const QWeight&) = delete;
     QWeight& operator=(const QWeight&) = delete;
     rusty_cuda_qlinear* raw() const { return raw_; }
+    // RUSTY_CUDA_ACT_SWIGLU_PAIRS: rows (2j, 2j+1) are (gate_j, up_j); forwards then write silu(gate) * up, N/2 columns
+    void set_activation(const CudaContext& ctx, int act) {
+        check(rusty_cuda_qlinear_set_activation(raw_, act), ctx.raw());
+        act_ = act;
+    }
+    uint32_t out_features() const { return act_ == RUSTY_CUDA_ACT_SWIGLU_PAIRS ? N / 2 : N; }
     const uint32_t N, K;
 private:
+    int act_ = RUSTY_CUDA_ACT_NONE;
     rusty_cuda_qlinear* raw_ = nullptr;
     UnifiedTensor keep_w_, keep_s_, keep_b_;
 };
@@ -177,6 +184,13 @@ public:
     }
     void add(const CudaContext& ctx, const UnifiedTensor& a, const UnifiedTensor& b, const UnifiedTensor& out) const {
         check(rusty_cuda_add_f32(ctx.raw(), a.buffer(), b.buffer(), out.buffer(), numel(out.shape)), ctx.raw());
+    }
+    // WGSL silu / mul (kernels.wgsl:104-113, :146-151): the glue of MLP::forward
+    void silu(const CudaContext& ctx, const UnifiedTensor& x, const UnifiedTensor& out) const {
+        check(rusty_cuda_silu_f32(ctx.raw(), x.buffer(), out.buffer(), numel(out.shape)), ctx.raw());
+    }
+    void mul(const CudaContext& ctx, const UnifiedTensor& a, const UnifiedTensor& b, const UnifiedTensor& out) const {
+        check(rusty_cuda_mul_f32(ctx.raw(), a.buffer(), b.buffer(), out.buffer(), numel(out.shape)), ctx.raw());
     }
     void copy_tensor(const CudaContext& ctx, const UnifiedTensor& src, const UnifiedTensor& dst, size_t dst_offset) const {
         check(rusty_cuda_buf_copy(ctx.raw(), src.buffer(), dst.buffer(), dst_offset), ctx.raw());
@@ -212,7 +226,7 @@ public:
 
     UnifiedTensor forward(const ComputeEngine& engine, const UnifiedTensor& x, DType out_dtype = DType::FP32) const {
         const size_t k = q_ ? q_->K : weight_.shape[0];
-        const size_t n = q_ ? q_->N : weight_.shape[1];
+        const size_t n = q_ ? q_->out_features() : weight_.shape[1];
         if (x.shape.empty() || x.shape.back() != k) throw std::invalid_argument("Linear: last dimension of x does not match in_features");
         const size_t rows = numel(x.shape) / k;
         UnifiedTensor x2 = x.reshaped({rows, k});
@@ -244,6 +258,35 @@ private:
     UnifiedTensor weight_;
     std::shared_ptr<QWeight> q_;
     std::shared_ptr<LoRAAdapter> lora_;
+};
+
+// MLP keeps the reference contract (rusty-graph/src/lib.rs:310-323): down(silu(gate(x)) * up(x)).  `fused` builds it
+// from ONE pair-interleaved gate|up weight whose kernel applies silu(gate) * up in its epilogue.
+class MLP {
+public:
+    MLP(const CudaContext& ctx, Linear gate, Linear up, Linear down)
+        : ctx_(ctx), gate_(std::make_unique<Linear>(std::move(gate))), up_(std::make_unique<Linear>(std::move(up))),
+          down_(std::make_unique<Linear>(std::move(down))) {}
+    static MLP fused(const CudaContext& ctx, std::shared_ptr<QWeight> gate_up_pairs, Linear down) {
+        gate_up_pairs->set_activation(ctx, RUSTY_CUDA_ACT_SWIGLU_PAIRS);
+        MLP m(ctx, std::move(down));
+        m.gate_up_ = std::make_unique<Linear>(Linear::from_quantized(ctx, std::move(gate_up_pairs)));
+        return m;
+    }
+    UnifiedTensor forward(const ComputeEngine& engine, const UnifiedTensor& input) const {
+        if (gate_up_) return down_->forward(engine, gate_up_->forward(engine, input));
+        UnifiedTensor gate_linear = gate_->forward(engine, input);
+        UnifiedTensor gate_act = UnifiedTensor::empty(ctx_, gate_linear.shape);
+        engine.silu(ctx_, gate_linear, gate_act);
+        UnifiedTensor up = up_->forward(engine, input);
+        UnifiedTensor fused = UnifiedTensor::empty(ctx_, up.shape);
+        engine.mul(ctx_, gate_act, up, fused);
+        return down_->forward(engine, fused);
+    }
+private:
+    MLP(const CudaContext& ctx, Linear down) : ctx_(ctx), down_(std::make_unique<Linear>(std::move(down))) {}
+    const CudaContext& ctx_;
+    std::unique_ptr<Linear> gate_, up_, down_, gate_up_;
 };
 
 }  // namespace rusty

@@ -29,7 +29,7 @@ from .workloads import StackShape
 class LinearStack:
     def __init__(self, ctx: CudaContext, shape: StackShape, M: int, x_dtype: DType = DType.FP32,
                  y_dtype: DType = DType.FP32, seed: int = 0, rank: int = 0, world: int = 1,
-                 layers: Optional[int] = None, fuse: bool = True):
+                 layers: Optional[int] = None, fuse: bool = True, swiglu: bool = False):
         self.ctx, self.shape, self.M = ctx, shape, M
         self.x_dtype, self.y_dtype = x_dtype, y_dtype
         self.rank, self.world = rank, world
@@ -38,8 +38,12 @@ class LinearStack:
         host_w: Dict[Tuple[int, int], Tuple[np.ndarray, np.ndarray]] = {}
         self.qls: List[QLinear] = []
         self.names: List[str] = []
-        self.dims: List[Tuple[int, int]] = []   # (N_local, K)
-        self.full_n: List[int] = []
+        self.dims: List[Tuple[int, int]] = []   # (N_local, K): rows of this rank's weight
+        self.out_n: List[int] = []               # output columns of this rank (N_local, or half of it for gate|up pairs)
+        self.full_n: List[int] = []              # output columns over all ranks
+        # gate|up stored pair-interleaved with silu(gate)*up applied in the kernel's epilogue (MLP::forward,
+        # rusty-graph/src/lib.rs:317-323): its output is [M, ffn] and the [M, 2*ffn] intermediate never exists
+        self.swiglu = swiglu and fuse
 
         def draw(n: int, k: int):
             if (n, k) not in host_w:
@@ -69,12 +73,20 @@ class LinearStack:
                 q, s = draw(n, k)
                 qs.append(q[rank * nl:(rank + 1) * nl])
                 ss.append(s[rank * nl:(rank + 1) * nl])
-            qcat = qs[0] if len(qs) == 1 else np.concatenate(qs, axis=0)
-            scat = ss[0] if len(ss) == 1 else np.concatenate(ss)
-            self.qls.append(QLinear.from_host(ctx, qcat, scat))
+            pairs = self.swiglu and name.endswith(".gate_up")
+            if pairs:
+                ql = QLinear.from_gate_up(ctx, qs[0], ss[0], qs[1], ss[1])
+                n_rows = 2 * qs[0].shape[0]
+            else:
+                qcat = qs[0] if len(qs) == 1 else np.concatenate(qs, axis=0)
+                scat = ss[0] if len(ss) == 1 else np.concatenate(ss)
+                ql = QLinear.from_host(ctx, qcat, scat)
+                n_rows = qcat.shape[0]
+            self.qls.append(ql)
             self.names.append(name)
-            self.dims.append((qcat.shape[0], k))
-            self.full_n.append(sum(n for n, _ in members))
+            self.dims.append((n_rows, k))
+            self.out_n.append(ql.out_features)
+            self.full_n.append(sum(n for n, _ in members) // (2 if pairs else 1))
         # activations: one fixed input per distinct K, N(0,1) like the benchmark's x
         self.inputs: Dict[int, UnifiedTensor] = {}
         self.host_inputs: Dict[int, np.ndarray] = {}
@@ -85,13 +97,13 @@ class LinearStack:
                               else UnifiedTensor.new(ctx, xh, [M, k]))
         # outputs: one buffer per distinct local N (reused across layers), logits separate
         self.outputs: Dict[int, UnifiedTensor] = {}
-        for (nl, _k), name in zip(self.dims, self.names):
+        for nl, name in zip(self.out_n, self.names):
             key = -1 if name == "lm_head" else nl
             if key not in self.outputs:
                 self.outputs[key] = UnifiedTensor.empty_with_dtype(ctx, [M, nl], y_dtype)
         self.logits = self.outputs[-1]
         self._xs = [self.inputs[k] for _, k in self.dims]
-        self._ys = [self.outputs[-1 if nm == "lm_head" else nl] for (nl, _), nm in zip(self.dims, self.names)]
+        self._ys = [self.outputs[-1 if nm == "lm_head" else nl] for nl, nm in zip(self.out_n, self.names)]
         self.graph: Optional[Graph] = None
 
     # ---- accounting (algorithmic bytes / flops of ONE step on this rank) ----
@@ -100,7 +112,7 @@ class LinearStack:
 
     def algorithmic_bytes(self) -> int:
         xs, ys = self.x_dtype.size_bytes(), self.y_dtype.size_bytes()
-        return sum(n * k + n * 4 + self.M * k * xs + self.M * n * ys for n, k in self.dims)
+        return sum(n * k + n * 4 + self.M * k * xs + self.M * no * ys for (n, k), no in zip(self.dims, self.out_n))
 
     def flops(self) -> int:
         return sum(2 * self.M * n * k for n, k in self.dims)

@@ -1,6 +1,7 @@
 // Exercises the C++ host mirror (rusty_b200/host/rusty_host.hpp) the way a test in rusty-backend / rusty-graph
 // would: the ops_test.rs identity product, a quantised Linear against a scalar restatement of
 // dequantise-then-matmul_bt, LoRA, views, and the error path.  Prints "ok" and exits 0 on success.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <random>
@@ -72,6 +73,43 @@ int main() {
     auto lora = std::make_shared<LoRAAdapter>(ctx, K, N, 4, 16.0f);
     auto with = Linear::with_lora(ctx, tw, lora).forward(engine, tx).to_vec(ctx);
     REQUIRE(plain == with);
+
+    // MLP::forward (rusty-graph/src/lib.rs:317-323): gate, silu, up, mul, down as separate operators, against the
+    // same MLP built from ONE pair-interleaved gate|up weight whose kernel applies silu(gate) * up itself
+    {
+        const size_t F = 160;
+        std::vector<int8_t> gq(F * K), uq(F * K), dq(K * F), pq(2 * F * K);
+        std::vector<float> gs(F), us(F), ds(K), ps(2 * F);
+        for (auto& e : gq) e = (int8_t)qd(rng);
+        for (auto& e : uq) e = (int8_t)qd(rng);
+        for (auto& e : dq) e = (int8_t)qd(rng);
+        for (auto& e : gs) e = sd(rng) * 0.1f;
+        for (auto& e : us) e = sd(rng);
+        for (auto& e : ds) e = sd(rng);
+        for (size_t j = 0; j < F; ++j) {
+            std::copy(gq.begin() + j * K, gq.begin() + (j + 1) * K, pq.begin() + (2 * j) * K);
+            std::copy(uq.begin() + j * K, uq.begin() + (j + 1) * K, pq.begin() + (2 * j + 1) * K);
+            ps[2 * j] = gs[j];
+            ps[2 * j + 1] = us[j];
+        }
+        auto mk = [&](const std::vector<int8_t>& qq, const std::vector<float>& ss, size_t n, size_t k) {
+            auto t1 = UnifiedTensor::from_bytes(ctx, qq.data(), qq.size(), {n, k}, DType::I8);
+            auto t2 = UnifiedTensor::make(ctx, ss.data(), {n});
+            return std::make_shared<QWeight>(ctx, t1, t2, nullptr, (uint32_t)n, (uint32_t)k, RUSTY_CUDA_LAYOUT_NK, RUSTY_CUDA_QMODE_SYM_ROW);
+        };
+        MLP unfused(ctx, Linear::from_quantized(ctx, mk(gq, gs, F, K)), Linear::from_quantized(ctx, mk(uq, us, F, K)),
+                    Linear::from_quantized(ctx, mk(dq, ds, K, F)));
+        MLP fused = MLP::fused(ctx, mk(pq, ps, 2 * F, K), Linear::from_quantized(ctx, mk(dq, ds, K, F)));
+        auto y1 = unfused.forward(engine, tx).to_vec(ctx);
+        auto y2 = fused.forward(engine, tx).to_vec(ctx);
+        REQUIRE(y1.size() == B * S * K && y2.size() == y1.size());
+        double mref = 0, merr = 0;
+        for (size_t i = 0; i < y1.size(); ++i) {
+            mref = std::fmax(mref, std::fabs(y1[i]));
+            merr = std::fmax(merr, std::fabs((double)y1[i] - y2[i]));
+        }
+        REQUIRE(mref > 0 && merr / mref <= 1e-5);
+    }
 
     // errors are exceptions carrying the BackendError variant, and the context survives
     bool threw = false;

@@ -30,6 +30,17 @@ def _worker(rank: int, world: int, port: int, q):
         y = assemble([p.numpy() for p in pieces])
         y_ref = O.qlinear_rowscale(x, w, s)
         ok = y.shape == y_ref.shape and np.array_equal(y.view(np.uint32), y_ref.view(np.uint32))
+        # a pair-interleaved gate|up weight: a rank's rows are whole (gate, up) pairs, so silu(gate) * up of its shard
+        # is a block of columns of the whole [M, N/2] result
+        from rusty_b200.backend import interleave_pairs
+        F = N // 2
+        wp, sp = interleave_pairs(w[:F], w[F:]), interleave_pairs(s[:F], s[F:])
+        act_local = O.swiglu_pairs(O.qlinear_rowscale(x, wp[rows], sp[rows]))
+        pieces = [torch.empty(M, F // world, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(pieces, torch.from_numpy(act_local))
+        act = assemble([p.numpy() for p in pieces])
+        act_ref = O.mul(O.silu(O.qlinear_rowscale(x, w[:F], s[:F])), O.qlinear_rowscale(x, w[F:], s[F:]))
+        ok = ok and act.shape == act_ref.shape and np.array_equal(act.view(np.uint32), act_ref.view(np.uint32))
         # the timing protocol of the bench: max over ranks
         t = torch.tensor([float(rank + 1)], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -52,6 +63,23 @@ def test_two_cpu_ranks_reassemble_bit_exactly():
     assert sorted(r[0] for r in results) == [0, 1]
     assert all(r[1] for r in results)
     assert all(r[2] == 2.0 for r in results)
+
+
+def test_arena_layout_is_the_same_on_every_rank():
+    from rusty_b200.shard import ARENA_ALIGN, arena_layout
+    sizes = [(6144, 32 * 6144 * 4), (4096, 32 * 4096 * 4), (14336, 32 * 14336 * 4), (4096, 32 * 4096 * 4), (-1, 100)]
+    offsets, total = arena_layout(sizes)
+    assert offsets == {6144: 0, 4096: 786432, 14336: 786432 + 524288, -1: 786432 + 524288 + 1835008}
+    assert all(o % ARENA_ALIGN == 0 for o in offsets.values()) and total == offsets[-1] + 256
+    import pytest
+    with pytest.raises(ValueError):
+        arena_layout([(1, 10), (1, 20)])
+
+
+def test_interleave_pairs():
+    from rusty_b200.backend import interleave_pairs
+    a, b = np.arange(6).reshape(3, 2), 10 + np.arange(6).reshape(3, 2)
+    assert interleave_pairs(a, b).tolist() == [[0, 1], [10, 11], [2, 3], [12, 13], [4, 5], [14, 15]]
 
 
 def test_shard_rows_rule():
