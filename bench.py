@@ -330,6 +330,36 @@ def main():
     barrier()
     finite = bool(np.isfinite(y_host.array).all())
 
+    # ---- the same step ending in one greedy token per row chosen on the device (what a greedy decoder reads back):
+    # N > 1 keeps the LM head's logits local and exchanges arg-max candidates instead ----
+    greedy = None
+    if hasattr(runner, "capture_greedy"):
+        runner.capture_greedy()
+        tok_host = PinnedArray((M,), np.uint32)
+        for _ in range(args.warmup):
+            runner.greedy_graph.launch()
+        barrier()
+        g0, g1 = Event(ctx), Event(ctx)
+        g0.record()
+        for _ in range(args.steps):
+            runner.greedy_graph.launch()
+        g1.record()
+        g_ms = max_over_ranks(g0.elapsed_ms(g1) / args.steps)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            upload_async(ctx, stack.inputs[d_in], x_host)
+            runner.greedy_graph.launch()
+            download_async(ctx, runner.tokens, tok_host)
+            ctx.sync()
+        g_e2e = max_over_ranks((time.perf_counter() - t0) / args.steps)
+        barrier()
+        greedy = {"value": M / (g_ms * 1e-3), "unit": "tokens/s", "ms_per_step": g_ms,
+                  "e2e": {"value": M / g_e2e, "unit": "tokens/s", "ms_per_step": g_e2e * 1e3,
+                          "h2d_bytes_per_step": x_host.nbytes, "d2h_bytes_per_step": tok_host.nbytes},
+                  "tokens_in_range": bool((tok_host.array < shape.vocab).all())}
+        tok_host.free()
+
     value = M / (ms_step * 1e-3)
     alg_bytes = stack.algorithmic_bytes()
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
@@ -357,6 +387,7 @@ def main():
                 "d2h_bytes_per_step": y_host.nbytes, "ms_per_step": e2e_s * 1e3, "logits_finite": finite},
         "gpu_launches": int(launches),
         "clocks": clocks,
+        "greedy": greedy,
     }
 
     if rank == 0 and world == 1 and not args.no_extras:

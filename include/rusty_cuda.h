@@ -299,6 +299,21 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_pushed_batch(rusty_cuda_ctx* ctx, 
                                                            const rusty_cuda_buf* const* xs, int x_dtype, uint32_t M,
                                                            rusty_cuda_buf* const* ys, int y_dtype);
 
+/* ---- the step after the LM head: greedy token choice on the device -------------
+ * Sampler::sample with temperature <= 0 (rusty-loader/src/tokenizer.rs:151-158): per activation row the index of
+ * the largest logit, the LAST one among equals, 0 for a row without candidates; NaN never wins (the reference panics
+ * on it).  out_idx: u32[M]; out_val (may be NULL): f32[M], the maxima.  The WGSL `top_k` kernel
+ * (kernels.wgsl:168-188) with k = 1 differs only in taking the FIRST of equal maxima. */
+RUSTY_CUDA_API int rusty_cuda_argmax_rows_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* logits, uint32_t M, uint32_t N,
+                                              rusty_cuda_buf* out_idx, rusty_cuda_buf* out_val);
+/* With output-feature shards (no counterpart in the reference): logits_shard is this rank's [M, Nl] block of
+ * columns [rank*Nl, (rank+1)*Nl); each rank stores its per-row candidate into `table` — a buffer of the arena at the
+ * same offset on every rank, nranks * M * 8 bytes — of every rank, and every rank ends with the global indices.
+ * Counts as two pushed operations of the arena's protocol. */
+RUSTY_CUDA_API int rusty_cuda_argmax_rows_sharded(rusty_cuda_ctx* ctx, rusty_cuda_arena* arena,
+                                                  const rusty_cuda_buf* logits_shard, uint32_t M, uint32_t Nl,
+                                                  rusty_cuda_buf* table, rusty_cuda_buf* out_idx, rusty_cuda_buf* out_val);
+
 /* ---- stream capture and timing ---------------------------------------------
  * rusty submits one command buffer per op (lib.rs:4452); a decode step here is
  * hundreds of short kernels, so the sequence can be recorded once into a CUDA

@@ -238,3 +238,18 @@ def swiglu_pairs(s) -> np.ndarray:
     out = np.empty((M, F2 // 2), np.float32)
     lib().oracle_swiglu_pairs(s2.ctypes.data_as(_f32p), out.ctypes.data_as(_f32p), C.c_uint32(M), C.c_uint32(F2 // 2))
     return out
+
+
+def greedy_sample(logits) -> int:
+    """Sampler::sample with temperature <= 0: index of the maximum, the last one among equals."""
+    a, pa = _f32(np.ravel(logits))
+    lib().oracle_greedy_sample.restype = C.c_uint32
+    return int(lib().oracle_greedy_sample(pa, C.c_size_t(a.size)))
+
+
+def top_k(values, k: int) -> np.ndarray:
+    """`top_k` shader: k indices, largest first, first index among equals."""
+    a, pa = _f32(np.ravel(values))
+    out = np.zeros(k, np.uint32)
+    lib().oracle_top_k(pa, C.c_size_t(a.size), C.c_uint32(k), out.ctypes.data_as(C.POINTER(C.c_uint32)))
+    return out

@@ -317,3 +317,46 @@ ORACLE_API void oracle_swiglu_pairs(const float* s, float* out, uint32_t M, uint
             oracle_mul(&act, &u, &out[(size_t)m * F + j], 1);
         }
 }
+
+/* ---- the step after the LM head -------------------------------------------
+ * Greedy sampling (rusty-loader/src/tokenizer.rs:151-158, temperature <= 0): the index of the maximum logit;
+ * Iterator::max_by keeps the LAST of several equal maxima; an empty slice gives 0.  (partial_cmp().unwrap()
+ * panics on NaN there; NaN is skipped here.) */
+ORACLE_API uint32_t oracle_greedy_sample(const float* logits, size_t n) {
+    uint32_t best = 0;
+    int have = 0;
+    float bv = 0.0f;
+    for (size_t i = 0; i < n; ++i) {
+        float v = logits[i];
+        if (v != v) continue;
+        if (!have || v >= bv) {
+            bv = v;
+            best = (uint32_t)i;
+            have = 1;
+        }
+    }
+    return best;
+}
+
+/* WGSL `top_k` (rusty-backend/src/kernels.wgsl:168-188): k rounds of "first index of the largest value not taken
+ * yet", starting each round from max_v = -1e9 and max_idx = 0 with a strict `>`. */
+ORACLE_API void oracle_top_k(const float* in, size_t len, uint32_t k, uint32_t* out_idx) {
+    for (uint32_t i = 0; i < k; ++i) {
+        float max_v = -1e9f;
+        uint32_t max_idx = 0;
+        for (size_t j = 0; j < len; ++j) {
+            float v = in[j];
+            int used = 0;
+            for (uint32_t p = 0; p < i; ++p)
+                if (out_idx[p] == (uint32_t)j) {
+                    used = 1;
+                    break;
+                }
+            if (!used && v > max_v) {
+                max_v = v;
+                max_idx = (uint32_t)j;
+            }
+        }
+        out_idx[i] = max_idx;
+    }
+}

@@ -312,6 +312,14 @@ class ComputeEngine:
         total = int(np.prod(out.shape, dtype=np.int64))
         check(lib().rusty_cuda_mul_f32(ctx.handle, a.buffer(), b.buffer(), out.buffer(), total), ctx.handle)
 
+    def argmax_rows(self, ctx: CudaContext, logits: UnifiedTensor, out_idx: UnifiedTensor,
+                    out_val: Optional[UnifiedTensor] = None) -> None:
+        """Greedy token per row (Sampler::sample with temperature <= 0, rusty-loader/src/tokenizer.rs:151-158):
+        out_idx is u32[M] (allocate it with 4*M bytes), out_val the optional f32[M] maxima."""
+        m = int(np.prod(logits.shape[:-1], dtype=np.int64))
+        check(lib().rusty_cuda_argmax_rows_f32(ctx.handle, logits.buffer(), m, int(logits.shape[-1]), out_idx.buffer(),
+                                               out_val.buffer() if out_val is not None else None), ctx.handle)
+
     def qlinear(self, ctx: CudaContext, x: UnifiedTensor, w: QLinear, out: UnifiedTensor) -> None:
         """out[M,N] = x[M,K] (.) w, fused dequantise + multiply."""
         m = int(np.prod(x.shape[:-1], dtype=np.int64))

@@ -303,7 +303,8 @@ __device__ __forceinline__ void finalize_store_f(const TcParams& p, YT* y, int n
         // (rusty-graph/src/lib.rs:317-323; silu as kernels.wgsl:104-113)
         const float up = __shfl_down_sync(0xffffffffu, v, 1);
         live = live && !(n & 1);
-        v = (v * (1.0f / (1.0f + expf(-v)))) * up;
+        // ex2.approx-based exp and an approximate reciprocal: a few instructions instead of ~40, relative error ~1e-6
+        v = __fdividef(v, 1.0f + __expf(-v)) * up;
         col >>= 1;
     }
     if (!live) return;
@@ -316,6 +317,37 @@ template <typename YT>
 __device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, const float* s_rowf,
                                                const PeerOut& po, bool live) {
     finalize_store_f<YT>(p, y, n, m, acc, scale_n, s_rowf[m], po, live);
+}
+
+// Four outputs at once: the four conversion chains (int64 -> f32, two multiplies, and for pairs a shuffle, exp and
+// reciprocal) are independent and written so that they overlap; one at a time they cost ~150 ns each in the single
+// warp per scheduler that runs them.  Output k is row m[k] of feature n[k]; live[k] says whether it exists.  Every lane
+// of the warp must call this together, and lane parity must equal the parity of n[k] (pair epilogue).
+template <typename YT>
+__device__ __forceinline__ void finalize_store4(const TcParams& p, YT* y, const int (&n)[4], const int (&m)[4], const long long (&acc)[4],
+                                                const float (&scale_n)[4], const float* s_rowf, const PeerOut& po, const bool (&live)[4]) {
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = __ll2float_rn(acc[k]) * s_rowf[m[k]] * scale_n[k];
+    if (p.act) {
+        // rows 2j / 2j+1 are gate_j / up_j: the even lane takes its neighbour's value and writes silu(gate) * up
+        // (rusty-graph/src/lib.rs:317-323; silu as kernels.wgsl:104-113, with ex2.approx and an approximate reciprocal)
+        float up[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) up[k] = __shfl_down_sync(0xffffffffu, v[k], 1);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = __fdividef(v[k], 1.0f + __expf(-v[k])) * up[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (live[k] && !(p.act && (n[k] & 1))) {
+            const int col = p.act ? (p.y_col0 + n[k]) >> 1 : p.y_col0 + n[k];
+            YT* dst = y + (size_t)m[k] * p.ldy + col;
+            store_y<YT>(dst, v[k]);
+            // exchange fused into the epilogue: the same element of every other rank's y, over NVLink
+            for (int g = 0; g < po.n; ++g) store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<char*>(dst) + po.delta[g]), v[k]);
+        }
+    }
 }
 
 // Four consecutive activations x[m, k..k+3] as f32 (zeros beyond K); K % 4 == 0.
@@ -590,6 +622,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             if (lane == 0) mbar_arrive(dig_ready);
         }
         int cut_t[2], cut_j[2], cut_n[2], n_cut = 0;  // shared tiles this CTA added a piece to
+        bool announced = false;
         Sched sched(p);
         Segment sg;
         for (int i = 0;; ++i) {
@@ -597,13 +630,18 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             // Shared tiles: once all pieces of a tile have been added, each CTA that holds one of them turns an equal share
             // of the tile's rows into y and leaves zeros behind (the arrival counters are cleared by the next pre-pass).  All pieces are added before anybody waits here, and the
             // CTAs of the grid are resident together (one wave), so the wait cannot depend on a CTA that has not started.
-            if (ok && n_cut > 0 && (!have || sg.nseg == 1) && threadIdx.x == 64) {
-                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // this CTA's adds have been performed
-                __threadfence();
-                for (int e = 0; e < n_cut; ++e)
-                    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.counters + cut_t[e]) : "memory");
+            // Announce this CTA's pieces once its last shared segment is behind it (the adds complete about when the
+            // weight stream ends); convert after the CTA's last whole tile, when the other pieces have arrived too.
+            if (ok && n_cut > 0 && !announced && (!have || sg.nseg == 1)) {
+                if (threadIdx.x == 64) {
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // this CTA's adds have been performed
+                    __threadfence();
+                    for (int e = 0; e < n_cut; ++e)
+                        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.counters + cut_t[e]) : "memory");
+                }
+                announced = true;
             }
-            for (int e = 0; ok && e < n_cut && (!have || sg.nseg == 1); ++e) {
+            for (int e = 0; ok && e < n_cut && !have; ++e) {
                 const int t = cut_t[e], nseg = cut_n[e], j = cut_j[e];
                 if (threadIdx.x == 64) {
                     const long long t0 = clock64();
@@ -659,20 +697,27 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         stage_at[u * EPI_THREADS + et] = (live && t * BM + rw[u] < p.N) ? (rw[u] | (mq[u] << 8)) : -1;
                     }
 #pragma unroll 1
-                    for (int u = 0; u < 4; ++u) {
-                        const int at = stage_at[u * EPI_THREADS + et];
-                        const bool live = at >= 0;
-                        const longlong2 two = *reinterpret_cast<const longlong2*>(&stage_red[u * EPI_THREADS + et]);
-                        const float scu = stage_sc[u * EPI_THREADS + et];
-                        const int nn = t * BM + (at & 0xff), m = live ? 2 * (at >> 8) : 0;
-                        finalize_store<YT>(p, y, nn, m, two.x, scu, s_rowf, po, live && m < p.M);
-                        finalize_store<YT>(p, y, nn, m + 1, two.y, scu, s_rowf, po, live && m + 1 < p.M);
+                    for (int u = 0; u < 4; u += 2) {  // two items = four outputs per trip
+                        const int at0 = stage_at[u * EPI_THREADS + et], at1 = stage_at[(u + 1) * EPI_THREADS + et];
+                        const bool v0 = at0 >= 0, v1 = at1 >= 0;
+                        const longlong2 t0 = *reinterpret_cast<const longlong2*>(&stage_red[u * EPI_THREADS + et]);
+                        const longlong2 t1 = *reinterpret_cast<const longlong2*>(&stage_red[(u + 1) * EPI_THREADS + et]);
+                        const float s0 = stage_sc[u * EPI_THREADS + et], s1 = stage_sc[(u + 1) * EPI_THREADS + et];
+                        const int n0 = t * BM + (at0 & 0xff), n1 = t * BM + (at1 & 0xff);
+                        const int m0 = v0 ? 2 * (at0 >> 8) : 0, m1 = v1 ? 2 * (at1 >> 8) : 0;
+                        const long long a4[4] = {t0.x, t0.y, t1.x, t1.y};
+                        const int n4[4] = {n0, n0, n1, n1}, m4[4] = {m0, m0 + 1, m1, m1 + 1};
+                        const float s4[4] = {s0, s0, s1, s1};
+                        const bool l4[4] = {v0 && m0 < p.M, v0 && m0 + 1 < p.M, v1 && m1 < p.M, v1 && m1 + 1 < p.M};
+                        finalize_store4<YT>(p, y, n4, m4, a4, s4, s_rowf, po, l4);
                     }
                 }
                 if (threadIdx.x == 64) DBG(11);
+                // the batch was parked in the staging tile at slots indexed by thread, the whole tile that may follow
+                // is staged there at slots indexed by row: no warp may start on it while another still reads its batch
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
             }
             if (!have || !ok) break;
-            if (sg.nseg == 1) n_cut = 0;  // the shared tiles recorded so far have just been converted
             const int ab = i & 1;
             const int n = sg.t * BM + r;
             const bool row_ok = n < p.N;
@@ -736,32 +781,12 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     }
                     asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 }
-            } else if (sg.nseg == 1) {
-                const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
-                for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
-                    int32_t c[4][8];
-#pragma unroll
-                    for (int d = 0; d < 4; ++d)
-                        if (d < p.D) tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c[d]);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int mm = 0; mm < 8; ++mm) {
-                        if (m0 + mm < p.M) {  // the same for the whole warp
-                            long long acc = c[0][mm];
-#pragma unroll
-                            for (int d = 1; d < 4; ++d)
-                                if (d < p.D) acc = acc * 128 + c[d][mm];
-                            finalize_store<YT>(p, y, n, m0 + mm, acc, sc, s_rowf, po, row_ok);
-                        }
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[ab]);
             } else {
-                // This CTA's piece of a shared tile: fold the digit planes into one exact 64-bit integer per output,
-                // stage the piece in shared memory ([m/2][row] x 16 bytes) and add it into the tile's sum in global
-                // memory with ONE bulk reduce (cp.reduce.async.bulk ... add.u64: the adds happen in L2 at line rate).
+                // Fold the digit planes into one exact 64-bit integer per output and stage them in shared memory
+                // ([m/2][row] x 16 bytes).  A whole tile is converted from there in a rolled loop (unrolled register
+                // code that runs once per tile costs an instruction fetch per line and was twice as slow); a piece of
+                // a shared tile is added into the tile's sum in global memory with ONE bulk reduce
+                // (cp.reduce.async.bulk ... add.u64: the adds happen in L2 at line rate).
                 for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
                     int32_t c[4][8];
 #pragma unroll
@@ -790,6 +815,22 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[ab]);
                 if (threadIdx.x == 64) DBG(7 + 4 * (i & 1));
+                if (sg.nseg == 1) {
+                    // every thread reads back only what it staged itself: no barrier needed
+                    const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+#pragma unroll 1
+                    for (int m = 0; m < p.M; m += 4) {  // Mpad is a multiple of 8: the staged rows m .. m+3 exist
+                        const longlong2 t0 = *reinterpret_cast<const longlong2*>(&stage_red[(size_t)(m >> 1) * BM + r]);
+                        const longlong2 t1 = *reinterpret_cast<const longlong2*>(&stage_red[(size_t)((m >> 1) + 1) * BM + r]);
+                        const long long a4[4] = {t0.x, t0.y, t1.x, t1.y};
+                        const int n4[4] = {n, n, n, n}, m4[4] = {m, m + 1, m + 2, m + 3};
+                        const float s4[4] = {sc, sc, sc, sc};
+                        const bool l4[4] = {row_ok, row_ok && m + 1 < p.M, row_ok && m + 2 < p.M, row_ok && m + 3 < p.M};
+                        finalize_store4<YT>(p, y, n4, m4, a4, s4, s_rowf, po, l4);
+                    }
+                    if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
+                    continue;
+                }
                 const int lt = sg.t - p.dp_tiles;
                 int4* tile_sum = reinterpret_cast<int4*>(p.part) + (size_t)lt * (p.Mpad / 2) * BM;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // staged values -> visible to the bulk-copy engine

@@ -82,6 +82,16 @@ struct rusty_cuda_arena {
     PeerPush pp{};
 };
 
+namespace rusty {
+const PeerPush* arena_push_state(const rusty_cuda_arena* arena) { return arena && arena->attached ? &arena->pp : nullptr; }
+bool arena_holds(const rusty_cuda_arena* arena, const void* ptr, size_t bytes) {
+    const uint8_t* lo = arena->base + ARENA_CTL_BYTES;
+    const uint8_t* p = (const uint8_t*)ptr;
+    return p >= lo && p <= lo + arena->data_bytes && bytes <= (size_t)(lo + arena->data_bytes - p);
+}
+rusty_cuda_ctx* arena_ctx(const rusty_cuda_arena* arena) { return arena ? arena->ctx : nullptr; }
+}  // namespace rusty
+
 extern "C" {
 
 int rusty_cuda_arena_create(rusty_cuda_ctx* ctx, size_t bytes, int nranks, int rank, rusty_cuda_arena** out) {

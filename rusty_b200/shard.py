@@ -198,6 +198,16 @@ def forward_pushed(ctx: CudaContext, arena: Arena, ql_shard, x: UnifiedTensor, M
                                                   y_full.buffer(), int(y_full.dtype)), ctx.handle)
 
 
+def argmax_rows_sharded(ctx: CudaContext, arena: Arena, logits_shard: UnifiedTensor, table: UnifiedTensor,
+                        out_idx: UnifiedTensor, out_val=None) -> None:
+    """Greedy token per row over column shards: only (value, index) candidates cross NVLink, never the logits.
+    `table` is an arena buffer of world * M * 8 bytes at the same offset on every rank; out_idx is u32[M]."""
+    M, Nl = int(np.prod(logits_shard.shape[:-1], dtype=np.int64)), int(logits_shard.shape[-1])
+    check(lib().rusty_cuda_argmax_rows_sharded(ctx.handle, arena._h, logits_shard.buffer(), M, Nl, table.buffer(),
+                                               out_idx.buffer(), out_val.buffer() if out_val is not None else None),
+          ctx.handle)
+
+
 class PushedStack:
     """Runs a LinearStack built with (rank, world): every Linear computes this rank's output columns and stores them
     into every rank's copy of the full output (no collective call).  Outputs of equal width share one arena buffer;
@@ -212,11 +222,14 @@ class PushedStack:
         for a, b in zip(keys, keys[1:]):
             assert a != b, "two consecutive Linears would share an output buffer"
         sizes = [(k, M * (n if k != -1 else n) * ydt.size_bytes()) for k, n in zip(keys, stack.full_n)]
+        sizes.append(("candidates", stack.world * M * 8))   # greedy tail: per-rank (value, index) of every row
         offsets, total = arena_layout(sizes)
         self.arena = Arena(ctx, total, stack.world, stack.rank)
         self.arena.connect(dist)
         self.full_outputs = {k: self.arena.tensor(offsets[k], [M, n], ydt) for k, n in zip(keys, stack.full_n)}
         self._ys = [self.full_outputs[k] for k in keys]
+        self._table = self.arena.tensor(offsets["candidates"], [stack.world * M * 8], DType.U8)
+        self.tokens = UnifiedTensor.from_bytes_with_dtype(ctx, np.zeros(M, np.uint32), [M * 4], DType.U8)
         self.graph = None
         self._dist = dist
 
@@ -237,6 +250,26 @@ class PushedStack:
         with g:
             self.step()
         self.graph = g
+        return g
+
+    def step_greedy(self) -> None:
+        """Every Linear but the LM head pushed; the LM head stays local ([M, vocab / world] on this rank) and only the
+        per-rank arg-max candidates are exchanged: every rank ends with the M greedy tokens."""
+        s = self.stack
+        n = len(s.qls) - 1
+        arr = C.c_void_p * n
+        check(lib().rusty_cuda_qlinear_forward_pushed_batch(
+            self.ctx.handle, self.arena._h, n, arr(*[q._h for q in s.qls[:n]]), arr(*[x.buffer() for x in s._xs[:n]]),
+            int(s.x_dtype), s.M, arr(*[y.buffer() for y in self._ys[:n]]), int(s.y_dtype)), self.ctx.handle)
+        check(lib().rusty_cuda_qlinear_forward(self.ctx.handle, s.qls[n]._h, s._xs[n].buffer(), int(s.x_dtype), s.M,
+                                               s.logits.buffer(), int(s.y_dtype)), self.ctx.handle)
+        argmax_rows_sharded(self.ctx, self.arena, s.logits, self._table, self.tokens)
+
+    def capture_greedy(self) -> Graph:
+        g = Graph(self.ctx)
+        with g:
+            self.step_greedy()
+        self.greedy_graph = g
         return g
 
     def replay(self) -> None:

@@ -132,6 +132,23 @@ class LinearStack:
         self.graph = g
         return g
 
+    # ---- the step a greedy decoder needs: every Linear, then one token per row chosen on the device ----
+    def step_greedy(self) -> None:
+        from .backend import ComputeEngine
+        if getattr(self, "tokens", None) is None:
+            self.tokens = UnifiedTensor.from_bytes_with_dtype(self.ctx, np.zeros(self.M, np.uint32), [self.M * 4], DType.U8)
+        self.step()
+        ComputeEngine(self.ctx).argmax_rows(self.ctx, self.logits, self.tokens)
+
+    def capture_greedy(self) -> Graph:
+        self.step_greedy()   # allocates the token buffer outside the capture
+        self.ctx.sync()
+        g = Graph(self.ctx)
+        with g:
+            self.step_greedy()
+        self.greedy_graph = g
+        return g
+
     def replay(self) -> None:
         self.graph.launch()
 

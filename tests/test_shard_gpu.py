@@ -158,6 +158,42 @@ sys.exit(0 if ok else 1)
 '''
 
 
+# Greedy token over column shards of the logits: only candidates travel.
+_ARGMAX_SCRIPT = r'''
+import os, sys
+import numpy as np
+sys.path.insert(0, {root!r})
+import torch, torch.distributed as dist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+import rusty_b200
+from rusty_b200 import DType, UnifiedTensor
+from rusty_b200.shard import Arena, argmax_rows_sharded
+ctx = rusty_b200.CudaContext(rank)
+M, N = 32, 4096 * world
+Nl = N // world
+arena = Arena(ctx, world * M * 8, world, rank)
+arena.connect(dist)
+table = arena.tensor(0, [world * M * 8], DType.U8)
+ok = True
+for step in range(3):
+    logits = np.random.default_rng(100 + step).standard_normal((M, N)).astype(np.float32)
+    logits[0, [5, N - 3]] = 50.0        # equal maxima in the first and the last shard: the last wins
+    logits[1, :] = np.nan               # no candidate anywhere
+    logits[2, 17] = 60.0                # the winner lives in rank 0's columns
+    shard = UnifiedTensor.new(ctx, np.ascontiguousarray(logits[:, rank * Nl:(rank + 1) * Nl]), [M, Nl])
+    idx = UnifiedTensor.from_bytes_with_dtype(ctx, np.full(M, 0xFFFFFFFF, np.uint32), [M * 4], DType.U8)
+    argmax_rows_sharded(ctx, arena, shard, table, idx)
+    got = idx.to_bytes(ctx).view(np.uint32)
+    want = np.array([0 if np.isnan(r).all() else (N - 1 - int(np.nanargmax(r[::-1]))) for r in logits], np.uint32)
+    ok = ok and np.array_equal(got, want) and got[0] == N - 3 and got[1] == 0 and got[2] == 17
+sys.stdout.write("rank %d %s\n" % (rank, "ok" if ok else "MISMATCH")); sys.stdout.flush()
+ctx.sync(); dist.barrier()
+arena.destroy(); ctx.destroy(); dist.destroy_process_group()
+sys.exit(0 if ok else 1)
+'''
+
+
 def _run(world: int, tmp_path, script_text: str = None, extra_env=None):
     script = tmp_path / "rank.py"
     script.write_text((script_text or _RANK_SCRIPT).format(root=ROOT))
@@ -205,3 +241,14 @@ def test_absent_rank_is_reported_as_timeout(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _run(2, tmp_path, _TIMEOUT_SCRIPT, {"RUSTY_PEER_WAIT_MS": "300"})
+
+
+def test_sharded_argmax_single_rank(tmp_path):
+    _run(1, tmp_path, _ARGMAX_SCRIPT)
+
+
+def test_sharded_argmax_two_ranks(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(2, tmp_path, _ARGMAX_SCRIPT)
