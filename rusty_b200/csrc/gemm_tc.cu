@@ -1025,6 +1025,20 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     if (grid > p.tiles * p.kb_total / 4) grid = p.tiles * p.kb_total / 4 > 0 ? p.tiles * p.kb_total / 4 : 1;
     p.sk_tiles = p.tiles % grid;
     p.dp_tiles = p.tiles - p.sk_tiles;
+    // Whole tiles only, dealt evenly (r or r-1 per CTA), when that still keeps most SMs streaming: ~110 SMs at the
+    // tensor-core rate already draw the full HBM bandwidth, and a CTA without shared tiles skips the bulk
+    // reduce-add, the wait for the other pieces and the shared conversion (5-10 us at the end of the kernel).
+    // RUSTY_TC_DP_PERCENT: least share of the SMs (default 72; 101 turns the rule off).
+    {
+        static const int dp_percent = getenv("RUSTY_TC_DP_PERCENT") ? atoi(getenv("RUSTY_TC_DP_PERCENT")) : 72;
+        const int r = (p.tiles + ctx->sm_count - 1) / ctx->sm_count;      // tiles per CTA
+        const int g_dp = r > 0 ? (p.tiles + r - 1) / r : 0;              // CTAs that then have work
+        if (!fused && p.sk_tiles > 0 && g_dp * 100 >= ctx->sm_count * dp_percent) {
+            grid = g_dp;
+            p.sk_tiles = 0;
+            p.dp_tiles = p.tiles;
+        }
+    }
     p.sk_per_cta = 0;
     p.sk_ctas = 0;
     if (p.sk_tiles > 0) {
