@@ -66,7 +66,7 @@ __device__ __forceinline__ void s8x4_to_f32(uint32_t w, float (&f)[4]) {
 }
 
 // MB activation rows (1 or 2), NJ passes of 4096 k.
-#define TDBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+#define TDBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = (long long)globaltimer_ns(); } while (0)
 
 template <int MB, int NJ>
 __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams p) {
@@ -278,7 +278,12 @@ int launch_gemv_tma(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.x_bf16 = a.x_dtype == RUSTY_CUDA_BF16;
     p.y_bf16 = a.y_dtype == RUSTY_CUDA_BF16;
     p.status = ctx->status_dev;
-    p.dbg = (long long*)ctx->tc_dbg;
+    p.dbg = nullptr;
+    if (ctx->tc_dbg) {  // development aid: one timeline region (304 CTAs x 16 slots) per launch, round robin
+        const int regions = (int)((size_t)ctx->tc_dbg_slots * 152 / 304);
+        p.dbg = (long long*)ctx->tc_dbg + (size_t)(regions > 0 ? ctx->tc_dbg_seq % regions : 0) * 304 * 16;
+        ctx->tc_dbg_seq++;
+    }
     const int MB = a.M == 1 ? 1 : 2;
     const size_t stage_stride = ((size_t)p.rows_per_stage * p.K + 127) & ~(size_t)127;
     // a quarter of an SM's shared memory: two CTAs of this kernel (16 compute warps per SM hide the conversion and
