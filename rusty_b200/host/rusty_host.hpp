@@ -260,6 +260,46 @@ private:
     std::shared_ptr<LoRAAdapter> lora_;
 };
 
+// Several GPUs, one process each (no counterpart in the reference): an arena with the same layout on every rank whose
+// buffers the fused linear of every rank writes into.  Handles (RUSTY_CUDA_IPC_HANDLE_BYTES each) travel over any
+// host channel; all ranks issue the same sequence of pushed forwards.
+class Arena {
+public:
+    Arena(const CudaContext& ctx, size_t bytes, int nranks, int rank) : ctx_(ctx), nranks_(nranks) {
+        check(rusty_cuda_arena_create(ctx.raw(), bytes, nranks, rank, &raw_), ctx.raw());
+    }
+    ~Arena() { rusty_cuda_arena_destroy(raw_); }
+    Arena(const Arena&) = delete;
+    Arena& operator=(const Arena&) = delete;
+    std::vector<unsigned char> export_handle() const {
+        std::vector<unsigned char> h(RUSTY_CUDA_IPC_HANDLE_BYTES);
+        check(rusty_cuda_arena_export(raw_, h.data()), ctx_.raw());
+        return h;
+    }
+    // handles of all ranks back to back, in rank order
+    void attach(const std::vector<unsigned char>& handles) {
+        if (handles.size() != (size_t)nranks_ * RUSTY_CUDA_IPC_HANDLE_BYTES) throw std::invalid_argument("Arena::attach: one handle per rank");
+        check(rusty_cuda_arena_attach(raw_, handles.data()), ctx_.raw());
+    }
+    // y_full[M, N] of a pushed forward: columns [rank*N/G, (rank+1)*N/G) come from rank's kernel
+    void forward_pushed(const QWeight& shard, const UnifiedTensor& x, rusty_cuda_buf* y_full, DType y_dtype) const {
+        const size_t rows = numel(x.shape) / x.shape.back();
+        check(rusty_cuda_qlinear_forward_pushed(ctx_.raw(), raw_, shard.raw(), x.buffer(), (int)x.dtype, (uint32_t)rows, y_full, (int)y_dtype),
+              ctx_.raw());
+    }
+    rusty_cuda_buf* buffer(size_t offset, size_t bytes) const {
+        rusty_cuda_buf* b = nullptr;
+        check(rusty_cuda_arena_buf(raw_, offset, bytes, &b), ctx_.raw());
+        return b;  // release with rusty_cuda_buf_release
+    }
+    void wait() const { check(rusty_cuda_arena_wait(ctx_.raw(), raw_), ctx_.raw()); }
+    rusty_cuda_arena* raw() const { return raw_; }
+private:
+    const CudaContext& ctx_;
+    int nranks_;
+    rusty_cuda_arena* raw_ = nullptr;
+};
+
 // MLP keeps the reference contract (rusty-graph/src/lib.rs:310-323): down(silu(gate(x)) * up(x)).  `fused` builds it
 // from ONE pair-interleaved gate|up weight whose kernel applies silu(gate) * up in its epilogue.
 class MLP {
