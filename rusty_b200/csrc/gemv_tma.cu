@@ -44,6 +44,7 @@ struct TgParams {
     int stages;
     int tiles;
     int ldy, y_col0;
+    int act;  // RUSTY_CUDA_ACT_SWIGLU_PAIRS: rows 2j, 2j+1 -> column (y_col0 + 2j) / 2
     int x_bf16, y_bf16;
     rusty_cuda_dev_status* status;
     long long* dbg;   // optional per-CTA timeline (development aid), null in normal use
@@ -118,19 +119,31 @@ __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams 
         for (int t = blockIdx.x; t < p.tiles; t += gridDim.x) {
             if (!mbar_wait(&done[stage], phase, abort_flag, p.status, 22)) break;
             const int row0 = t * p.rows_per_stage;
-            if (lane < p.rows_per_stage * MB) {
+            {
                 const int r = lane / MB, m = lane % MB;
                 const int n = row0 + r;
-                if (n < p.N && m < p.M) {
+                bool live = lane < p.rows_per_stage * MB && n < p.N && m < p.M;
+                float s = 0.0f;
+                if (live) {
                     const float* pp = sPart + ((size_t)(stage * 4 + r) * MB + m) * CW;
-                    float s = 0.0f;
 #pragma unroll
                     for (int w = 0; w < CW; ++w) s += pp[w];
                     s *= __ldg(p.scales + n);
+                }
+                size_t col = (size_t)p.y_col0 + n;
+                if (p.act) {
+                    // rows r, r+1 of the tile are one (gate, up) pair (tiles hold an even number of rows): the even row's lane
+                    // takes the value MB lanes further on and writes silu(gate) * up (MLP::forward composition)
+                    const float up = __shfl_down_sync(0xffffffffu, s, MB);
+                    live = live && !(r & 1);
+                    s = __fdividef(s, 1.0f + __expf(-s)) * up;
+                    col >>= 1;
+                }
+                if (live) {
                     if (p.y_bf16)
-                        reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + p.y_col0 + n] = __float2bfloat16_rn(s);
+                        reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + col] = __float2bfloat16_rn(s);
                     else
-                        reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + p.y_col0 + n] = s;
+                        reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + col] = s;
                 }
             }
             __syncwarp();
@@ -253,7 +266,7 @@ namespace rusty {
 
 bool gemv_tma_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
     if (a.layout != RUSTY_CUDA_LAYOUT_NK || a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
-    if (a.act) return false;  // the pair epilogue lives in the CUDA-core GEMV and the int8 tensor-core kernel
+    if (a.act && a.K > 8192) return false;  // a stage then holds one row: no (gate, up) pair inside a tile
     if (a.M < 1 || a.M > 2) return false;
     if (a.K % 16 != 0 || a.K > (uint32_t)((a.M == 1 ? MAXJ : 2) * CHUNKS_PER_PASS * 16)) return false;
     static const bool off = getenv("RUSTY_NO_GEMV_TMA") != nullptr;
@@ -275,6 +288,7 @@ int launch_gemv_tma(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.tiles = (p.N + p.rows_per_stage - 1) / p.rows_per_stage;
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
+    p.act = a.act;
     p.x_bf16 = a.x_dtype == RUSTY_CUDA_BF16;
     p.y_bf16 = a.y_dtype == RUSTY_CUDA_BF16;
     p.status = ctx->status_dev;
