@@ -207,6 +207,8 @@ struct TcParams {
     int dp_tiles, sk_tiles, sk_per_cta, sk_ctas;
     int sk_ways;             // > 0: every shared tile is cut into this many near-equal pieces, one per CTA (CTA = tile * ways + piece)
     int ldy, y_col0;
+    int cluster_ways;        // > 0: the CTAs that hold the pieces of a tile form a thread-block cluster and sum them through
+                             // distributed shared memory (== sk_ways, every CTA holds exactly one piece)
     int act;                 // RUSTY_CUDA_ACT_SWIGLU_PAIRS: rows 2j, 2j+1 -> y[:, (y_col0 + 2j) / 2] = silu(gate) * up
     int stages;
     int red_bytes;           // epilogue staging area: a partial tile (Mpad x 128 x 8 bytes), at least 12 KiB
@@ -390,6 +392,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     uint64_t* dig_ready = reinterpret_cast<uint64_t*>(s_factor + 4);  // fused mode: the digit tiles of x are in place
 
     __shared__ float s_rowf[64];  // 1/s_m * 128^-(D-1) per activation row of this pass (at most 64 rows)
+    __shared__ __align__(8) uint64_t cl_bar[2];  // cluster mode: [0] every piece of the tile is staged, [1] every CTA has read them
     __shared__ long long s_peer_delta[PEER_MAX_RANKS];
     if (threadIdx.x == 0) {
         int k = 0;  // the other ranks, compacted (own rank left out); static indices into the parameter
@@ -412,6 +415,10 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             mbar_init(&acc_empty[a], 4);
         }
         mbar_init(dig_ready, 4);
+        if (p.cluster_ways > 0) {
+            mbar_init(&cl_bar[0], (uint32_t)p.cluster_ways);
+            mbar_init(&cl_bar[1], (uint32_t)p.cluster_ways);
+        }
         *abort_flag = 0;
         *last_flag = 0;
         fence_barrier_init();
@@ -421,6 +428,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (p.cluster_ways > 0) cluster_sync_all();  // nobody arrives on a neighbour's barrier before it is initialised
     if (threadIdx.x == 0) DBG(1);
 
     if (warp == 0) {
@@ -831,6 +839,73 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
                     continue;
                 }
+                if (p.cluster_ways > 0) {
+                    // The pieces of this tile sit in the staging tiles of the cluster's CTAs.  Tell everybody that this
+                    // one is staged, wait for all, then sum an equal share of the rows straight out of the
+                    // neighbours' shared memory and convert it: no global partial sums, no counters.
+                    const int ways = p.cluster_ways;
+                    const uint32_t my = cluster_ctarank();
+                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                    if (threadIdx.x == 64) {
+                        fence_acq_rel_cluster();
+                        for (int c = 0; c < ways; ++c) mbar_arrive_cluster(mapa_u32(smem_u32(&cl_bar[0]), (uint32_t)c));
+                    }
+                    if (!mbar_wait(&cl_bar[0], 0u, abort_flag, p.status, 9)) { ok = false; }
+                    fence_acq_rel_cluster();
+                    if (threadIdx.x == 64) DBG(8 + 4 * (i & 1));
+                    if (ok) {
+                        const int lo = 2 * ((int)my * (BM / 2) / ways), rows = 2 * (((int)my + 1) * (BM / 2) / ways) - lo;
+                        const int items = rows * (p.Mpad / 2);
+                        const uint32_t stage_addr = smem_u32(stage_red);
+                        if (rows > 0) {
+                            int row = et % rows, mp = et / rows;
+                            const int step_row = EPI_THREADS % rows, step_mp = EPI_THREADS / rows;
+#pragma unroll 1
+                            for (int base = 0; base < items; base += 2 * EPI_THREADS) {  // two items = four outputs per trip
+                                long long a4[4] = {0, 0, 0, 0};
+                                int n4[4], m4[4];
+                                float s4[4];
+                                bool l4[4];
+#pragma unroll
+                                for (int u = 0; u < 2; ++u) {
+                                    const bool in = base + u * EPI_THREADS + et < items;
+                                    const int rw = lo + row, nn = sg.t * BM + rw;
+                                    const uint32_t off = stage_addr + (uint32_t)((mp * BM + rw) * 16);
+                                    if (in) {
+                                        for (int c = 0; c < ways; ++c) {
+                                            const int4 v = ld_dsmem_v4(mapa_u32(off, (uint32_t)c));
+                                            a4[2 * u] += ((long long)v.y << 32) | (unsigned int)v.x;
+                                            a4[2 * u + 1] += ((long long)v.w << 32) | (unsigned int)v.z;
+                                        }
+                                    }
+                                    const bool live = in && nn < p.N;
+                                    n4[2 * u] = n4[2 * u + 1] = nn;
+                                    m4[2 * u] = live ? 2 * mp : 0;
+                                    m4[2 * u + 1] = m4[2 * u] + 1;
+                                    s4[2 * u] = s4[2 * u + 1] = live ? __ldg(p.scales + nn) : 0.0f;
+                                    l4[2 * u] = live && 2 * mp < p.M;
+                                    l4[2 * u + 1] = live && 2 * mp + 1 < p.M;
+                                    row += step_row;
+                                    mp += step_mp;
+                                    if (row >= rows) {
+                                        row -= rows;
+                                        ++mp;
+                                    }
+                                }
+                                finalize_store4<YT>(p, y, n4, m4, a4, s4, s_rowf, po, l4);
+                            }
+                        }
+                    }
+                    // nobody's staging tile may go away (CTA exit) or be reused while a neighbour still reads it
+                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                    if (threadIdx.x == 64) {
+                        fence_acq_rel_cluster();
+                        for (int c = 0; c < ways; ++c) mbar_arrive_cluster(mapa_u32(smem_u32(&cl_bar[1]), (uint32_t)c));
+                    }
+                    if (!mbar_wait(&cl_bar[1], 0u, abort_flag, p.status, 10)) ok = false;
+                    if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
+                    continue;
+                }
                 const int lt = sg.t - p.dp_tiles;
                 int4* tile_sum = reinterpret_cast<int4*>(p.part) + (size_t)lt * (p.Mpad / 2) * BM;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // staged values -> visible to the bulk-copy engine
@@ -1119,6 +1194,30 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_i8_tc: cudaFuncSetAttribute");
         cur = smem;
+    }
+    // Pieces of one tile held by consecutive CTAs: launch them as a thread-block cluster and sum through distributed
+    // shared memory, when every cluster can be resident at once (one wave).  Opt-in: RUSTY_TC_CLUSTER=1.
+    static const bool want_cluster = getenv("RUSTY_TC_CLUSTER") && atoi(getenv("RUSTY_TC_CLUSTER")) == 1;
+    if (want_cluster && !fused && p.sk_ways >= 2 && p.sk_ways <= 8 && p.dp_tiles == 0 && grid == p.sk_tiles * p.sk_ways) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(TC_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute cattr[1];
+        cattr[0].id = cudaLaunchAttributeClusterDimension;
+        cattr[0].val.clusterDim.x = (unsigned)p.sk_ways;
+        cattr[0].val.clusterDim.y = 1;
+        cattr[0].val.clusterDim.z = 1;
+        cfg.attrs = cattr;
+        cfg.numAttrs = 1;
+        int max_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters >= grid / p.sk_ways) {
+            p.cluster_ways = p.sk_ways;
+            le = launch_pdl_cluster(kern, dim3(grid), dim3(TC_THREADS), smem, ctx->stream, (unsigned)p.sk_ways, map_w, map_x, p);
+            if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_i8_tc (cluster)");
+            return after_launch(ctx, "qlinear_i8_tc");
+        }
+        cudaGetLastError();
     }
     le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, ctx->stream, map_w, map_x, p);
     if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_i8_tc");

@@ -338,3 +338,44 @@ print("ok")
     env = dict(os.environ, RUSTY_TC_MIN_ROWS="1")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+# ---- shared tiles summed through a thread-block cluster's distributed shared memory (opt-in variant) ----
+
+def test_tc_cluster_variant_gives_the_same_bits(ctx, oracle):
+    """RUSTY_TC_CLUSTER=1: the CTAs that hold the pieces of a tile form a cluster and add them out of each other's
+    shared memory instead of going through global memory.  Integer sums: the result must equal the default path bit
+    for bit.  Child processes, so that the override does not leak."""
+    import subprocess, sys, os
+    code = f'''
+import sys, numpy as np
+sys.path.insert(0, {repr(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))})
+import rusty_b200
+from rusty_b200 import QLinear, UnifiedTensor, capi
+from rusty_b200.workloads import sym_row_linear
+ctx = rusty_b200.CudaContext(0); eng = rusty_b200.ComputeEngine(ctx)
+out = []
+for (M, K, N, act) in [(32, 4096, 4096, 0), (32, 4096, 6144, 0), (7, 1024, 640, 0), (32, 14336, 4096, 0), (32, 2048, 4096, 1), (33, 512, 300, 0)]:
+    x, q, s = sym_row_linear(K + N + M, M, K, N)
+    ql = QLinear.from_host(ctx, q, s)
+    if act: ql.set_activation(capi.ACT_SWIGLU_PAIRS)
+    xt = UnifiedTensor.new(ctx, x, [M, K])
+    y = UnifiedTensor.new(ctx, np.full(M * ql.out_features, np.nan, np.float32), [M, ql.out_features])
+    eng.qlinear(ctx, xt, ql, y)
+    out.append(y.to_vec(ctx).copy())
+ctx.sync()
+np.save(sys.argv[1], np.concatenate(out))
+print("ok")
+'''
+    import tempfile
+    results = []
+    for flag in ("0", "1"):
+        with tempfile.NamedTemporaryFile(suffix=".npy", delete=False) as f:
+            path = f.name
+        env = dict(os.environ, RUSTY_TC_CLUSTER=flag)
+        r = subprocess.run([sys.executable, "-c", code, path], capture_output=True, text=True, env=env, timeout=600)
+        assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+        results.append(np.load(path))
+        os.unlink(path)
+    assert np.isfinite(results[0]).all()
+    assert np.array_equal(results[0].view(np.uint32), results[1].view(np.uint32))
