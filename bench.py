@@ -420,9 +420,9 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"],
                      # DRAM bytes per step: dram__bytes_read+write of the fused linear measured with ncu on one Linear of
-                     # this stack (profiles/qlinear_i8_tc_m32_k4096_n14336.md: 63.49 MB for 61.14 MB algorithmic), scaled
+                     # this stack (profiles/qlinear_i8_tc_m32_k4096_n14336.md: 59.44 MB for 61.14 MB algorithmic), scaled
                      # to the step by algorithmic bytes (traffic grows with the weight bytes streamed)
-                     "traffic": alg_bytes * (63.49 / 61.14) if M > 4 else None, "peak_source": peaks["source"],
+                     "traffic": alg_bytes * (59.44 / 61.14) if M > 4 else None, "peak_source": peaks["source"],
                      "algorithmic_bytes_per_step_per_gpu": alg_bytes,
                      "note": "whole step (all launches of the fused linear kernel) / device time, per GPU"},
         "e2e": {"value": M / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": x_host.nbytes,

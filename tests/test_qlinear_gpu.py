@@ -215,6 +215,18 @@ def test_tc_shapes_f32(ctx, engine, oracle, M, K, N):
         assert rel_err(got, ref) <= TOL_FP32
 
 
+@pytest.mark.parametrize("K,N", [(4096, 768), (4096, 512), (14336, 512), (4096, 3584), (4096, 16032), (4096, 1536), (4096, 7168)])
+def test_tc_shard_shapes_of_the_decode_stack(ctx, engine, oracle, K, N):
+    """What a rank runs when the Llama-3-8B-shaped stack is cut 4 or 8 ways (few row tiles, up to 28 pieces per tile)."""
+    M = 32
+    x, q, s = sym_row_linear(K + N, M, K, N)
+    ql = QLinear.from_host(ctx, q, s)
+    assert ql.plan(M) == "tcgen05"
+    got = _forward(ctx, engine, ql, x)
+    ctx.sync()
+    assert rel_err(got, oracle.matmul_bt(x, oracle.dequantize_rowscale(q, s), mt=True)) <= TOL_FP32
+
+
 def test_tc_is_closer_to_exact_than_the_reference_arithmetic(ctx, engine, oracle):
     """Integer tensor-core sums are exact; the result sits nearer the float64
     dot products than the reference's own sequential f32 accumulation does."""
