@@ -333,6 +333,15 @@ RUSTY_CUDA_API int rusty_cuda_event_record(rusty_cuda_ctx* ctx, rusty_cuda_event
 RUSTY_CUDA_API int rusty_cuda_event_elapsed_ms(rusty_cuda_ctx* ctx, rusty_cuda_event* start, rusty_cuda_event* stop,
                                                float* ms);
 RUSTY_CUDA_API int rusty_cuda_event_destroy(rusty_cuda_event* ev);
+
+/* ---- development aid (no counterpart in the reference) ----------------------------
+ * Attach a device buffer into which the int8 tensor-core kernel pair writes %globaltimer stamps (nanoseconds), one
+ * region of 152 x 16 int64 slots per launch pair in the order of the calls, round robin over the regions that fit:
+ * rows 0..147 = the GEMM's CTAs (slot 0 start, 1 set-up done, 2 first weight copy issued, 3 producer done, 4 first
+ * MMA, 5 last MMA committed, 6-13 epilogue stages, 14 before tear-down, 15 exit), row 150 = the digit pre-pass
+ * (0 start, 1 the kernel before has finished, 2 end, 3 the other ranks have been heard from).  NULL detaches.  Attach
+ * before recording a graph: the region addresses are fixed at enqueue time.  `python -m rusty_b200.timeline` prints one. */
+RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf);
 /* Overwrite `bytes` bytes at `offset` with `value` (cudaMemsetAsync); used by
  * harnesses to flush L2 between timed iterations and to clear outputs. */
 RUSTY_CUDA_API int rusty_cuda_buf_fill_u8(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf, size_t offset, int value,

@@ -104,6 +104,7 @@ SIGNATURES = {
     "rusty_cuda_event_record": ([_vp, _vp], _int),
     "rusty_cuda_event_elapsed_ms": ([_vp, _vp, _vp, C.POINTER(C.c_float)], _int),
     "rusty_cuda_event_destroy": ([_vp], _int),
+    "rusty_cuda_debug_set_timeline": ([_vp, _vp], _int),
     "rusty_cuda_buf_fill_u8": ([_vp, _vp, _sz, _int, _sz], _int),
     "rusty_cuda_qlinear_plan": ([_vp, _int, _u32, _int, C.c_char_p, _sz], _int),
 }

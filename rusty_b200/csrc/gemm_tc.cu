@@ -1236,8 +1236,8 @@ int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
 
 }  // namespace rusty
 
-// Development aid: point the tensor-core kernel's per-CTA timeline at a caller
-// buffer (148 CTAs x 16 clock64 slots), or detach it with NULL.
+// Development aid: point the kernels' timeline (%globaltimer stamps, one region of 152 x 16 slots per launch pair)
+// at a caller buffer, or detach it with NULL.
 extern "C" RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf) {
     if (!ctx) return RUSTY_CUDA_ERR_INVALID_OPERATION;
     ctx->tc_dbg = buf ? buf->ptr : nullptr;
