@@ -127,3 +127,38 @@ def test_config1_digest(oracle, kat):
     u, sg, bg = affine_g64_from_sym(q, 0)
     ya = oracle.qlinear_affine(x, u, sg, bg, u.shape)
     assert hashlib.sha256(ya.tobytes()).digest() == kat["cfg1_affine_y_sha256"].tobytes()
+
+
+# ---- glue after the linears: SiLU, mul, pair-interleaved SwiGLU, greedy sampling, top_k ----
+
+def test_silu_mul_hand_values(oracle):
+    x = np.array([0.0, 1.0, -1.0, 10.0, -10.0], np.float32)
+    got = oracle.silu(x)
+    want = x.astype(np.float64) / (1.0 + np.exp(-x.astype(np.float64)))     # kernels.wgsl:104-113 in exact arithmetic
+    assert got[0] == 0.0 and np.allclose(got, want, rtol=3e-7, atol=0)
+    assert abs(float(got[1]) - 0.7310585786300049) < 1e-7 and abs(float(got[2]) + 0.2689414213699951) < 1e-7
+    a = np.array([1.5, -2.0, 3.0], np.float32)
+    b = np.array([2.0, 0.5, -1.0], np.float32)
+    assert oracle.mul(a, b).tolist() == [3.0, -1.0, -3.0]                     # kernels.wgsl:146-151
+
+
+def test_swiglu_pairs_is_silu_of_the_gate_times_up(oracle):
+    """MLP::forward (rusty-graph/src/lib.rs:317-323) applies SiLU to the GATE projection; columns (2j, 2j+1) hold
+    (gate_j, up_j)."""
+    rng = np.random.default_rng(0)
+    g = rng.standard_normal((3, 5)).astype(np.float32) * 3
+    u = rng.standard_normal((3, 5)).astype(np.float32)
+    s = np.empty((3, 10), np.float32)
+    s[:, 0::2], s[:, 1::2] = g, u
+    got = oracle.swiglu_pairs(s)
+    assert np.array_equal(got.view(np.uint32), oracle.mul(oracle.silu(g), u).view(np.uint32))
+    assert not np.array_equal(got, oracle.mul(oracle.silu(u), g))              # the unused fused shader's order differs
+
+
+def test_greedy_sample_and_top_k_tie_rules(oracle):
+    x = np.array([1.0, 5.0, 3.0, 5.0, 2.0], np.float32)
+    assert oracle.greedy_sample(x) == 3             # Iterator::max_by keeps the last maximum (tokenizer.rs:151-158)
+    assert oracle.top_k(x, 3).tolist() == [1, 3, 2]  # strict '>' keeps the first (kernels.wgsl:168-188)
+    assert oracle.greedy_sample(np.array([], np.float32)) == 0
+    assert oracle.greedy_sample(np.array([np.nan, -1.0, np.nan], np.float32)) == 1
+    assert oracle.top_k(np.array([-2e9, -3e9], np.float32), 1).tolist() == [0]   # nothing beats the -1e9 start: index 0
