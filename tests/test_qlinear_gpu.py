@@ -215,7 +215,8 @@ def test_tc_shapes_f32(ctx, engine, oracle, M, K, N):
         assert rel_err(got, ref) <= TOL_FP32
 
 
-@pytest.mark.parametrize("K,N", [(4096, 768), (4096, 512), (14336, 512), (4096, 3584), (4096, 16032), (4096, 1536), (4096, 7168)])
+@pytest.mark.parametrize("K,N", [(4096, 768), (4096, 512), (14336, 512), (4096, 3584), (4096, 16032), (4096, 1536), (4096, 7168),
+                                 (14336, 1024), (4096, 1024), (4096, 32064)])
 def test_tc_shard_shapes_of_the_decode_stack(ctx, engine, oracle, K, N):
     """What a rank runs when the Llama-3-8B-shaped stack is cut 4 or 8 ways (few row tiles, up to 28 pieces per tile)."""
     M = 32
