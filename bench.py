@@ -167,7 +167,12 @@ class CpuSample:
         self.xs = {k: rng.standard_normal((M, k), dtype=np.float32) for _p, _n, k in self.per_layer}
         self.sample_weights = sum(n * k for _p, n, k in self.per_layer)
         self.total_weights = shape.weight_bytes()
-        self.threads = O.num_threads()
+        # every core this process may run on, whatever OMP_NUM_THREADS says (torchrun exports 1)
+        try:
+            cores = len(os.sched_getaffinity(0))
+        except AttributeError:
+            cores = os.cpu_count() or 1
+        self.threads = O.set_num_threads(cores)
 
     def two_step(self) -> float:
         t0 = time.perf_counter()
@@ -190,10 +195,26 @@ class CpuSample:
                 % (self.M, self.total_weights, self.sample_weights))
 
 
+def workload_config(args, M: int, desc: str) -> dict:
+    """The `config` object both arms print: what is computed, not how."""
+    stack_name = WORKLOADS[args.workload][0]
+    from rusty_b200.workloads import STACKS
+    shape = STACKS[stack_name]
+    layers = shape.layers if args.layers is None else args.layers
+    return {"workload": args.workload, "desc": desc, "batch_rows": M, "layers": layers,
+            "linears_per_step": 4 * layers + 1,
+            "weights": "int8 [out,in], f32 scale per output row; q|k|v and gate|up run as one Linear each",
+            "activations": "f32 in, f32 out, fp32 accumulate",
+            "l2": "inputs larger than L2: every step streams all %.2f GB of weights, each layer from its own buffer"
+                  % (sum(n * k for _p, n, k in shape.per_layer()) * layers / 1e9 + shape.vocab * shape.d / 1e9)}
+
+
 def run_reference(args, rank: int):
     """--impl reference: the reference's own arithmetic for the path on the host
     cores (the oracle port; the Rust + WGSL original cannot be built or run on a
-    box without a Rust toolchain and a graphics stack)."""
+    box without a Rust toolchain and a graphics stack).  One step = ONE layer of
+    the stack (a bounded sample); the per-step time of the whole stack is that
+    sample scaled by weight bytes, and both are printed."""
     if rank != 0:
         return
     stack_name, M, desc = WORKLOADS[args.workload]
@@ -208,7 +229,9 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "desc": desc, "batch_rows": M},
+        "config": workload_config(args, M, desc),
+        "sample_ms_measured": t_sample * 1e3,
+        "ms_per_step_is": "extrapolated: measured sample (one layer) x total weight bytes / sample weight bytes",
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cs.threads, "kind": "port", "sample": cs.describe()},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -409,19 +432,17 @@ def main():
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "desc": desc, "batch_rows": M, "linears_per_step": stack.num_linears(),
-                   "weights": "int8 [out,in], f32 scale per output row; q|k|v and gate|up run as one Linear each" + (
-                       "; gate|up rows pair-interleaved, silu(gate)*up applied in the kernel epilogue ([M, ffn] out)" if stack.swiglu else ""), "activations": "f32 in, f32 out, fp32 accumulate",
-                   "parallelism": ("1 GPU" if world == 1 else f"output-feature shards x{world}, " + (
-                       "outputs stored into every rank's memory by the kernel epilogue (NVLink peer stores)"
-                       if args.exchange == "push" else "NCCL all-gather after each Linear")),
-                   "l2": "inputs larger than L2: each step streams %.2f GB of weights per GPU" % (stack.weight_bytes() / 1e9),
-                   "kernels": runner.plans(), "layers": stack.layers},
+        "config": workload_config(args, M, desc),
+        "impl_detail": {"swiglu_epilogue": bool(stack.swiglu),
+                        "parallelism": ("1 GPU" if world == 1 else f"output-feature shards x{world}, " + (
+                            "outputs stored into every rank's memory by the kernel epilogue (NVLink peer stores)"
+                            if args.exchange == "push" else "NCCL all-gather after each Linear")),
+                        "weight_gb_per_gpu_per_step": stack.weight_bytes() / 1e9, "kernels": runner.plans()},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"],
-                     # DRAM bytes per step: dram__bytes_read+write of the fused linear measured with ncu on one Linear of
-                     # this stack (profiles/qlinear_i8_tc_m32_k4096_n14336.md: 59.44 MB for 61.14 MB algorithmic), scaled
-                     # to the step by algorithmic bytes (traffic grows with the weight bytes streamed)
+                     # DRAM bytes per step: dram__bytes_read+write of the fused linear captured with ncu on one Linear of
+                     # this stack (32 x 4096 x 14336: 59.44 MB for 61.14 MB algorithmic), scaled to the step by
+                     # algorithmic bytes (traffic grows with the weight bytes streamed)
                      "traffic": alg_bytes * (59.44 / 61.14) if M > 4 else None, "peak_source": peaks["source"],
                      "algorithmic_bytes_per_step_per_gpu": alg_bytes,
                      "note": "whole step (all launches of the fused linear kernel) / device time, per GPU"},

@@ -100,6 +100,10 @@ RUSTY_CUDA_API const char* rusty_cuda_last_error(rusty_cuda_ctx* ctx);
 /* device.poll(Maintain::Wait) (lib.rs:233): drain the stream; reports any
  * asynchronous kernel error and any device-side timeout flag. */
 RUSTY_CUDA_API int rusty_cuda_sync(rusty_cuda_ctx* ctx);
+/* The kernels' internal scratch regions are separated by guard zones that nothing may write.  Drains the stream,
+ * reads the guards back and returns RUSTY_CUDA_ERR_KERNEL_EXECUTION if one was damaged (an out-of-bounds write by a
+ * kernel of this library).  No counterpart in the reference (wgpu validates buffer bounds itself). */
+RUSTY_CUDA_API int rusty_cuda_ctx_self_check(rusty_cuda_ctx* ctx);
 /* Number of kernels this context has launched so far (host-side counter). */
 RUSTY_CUDA_API int rusty_cuda_ctx_launch_count(rusty_cuda_ctx* ctx, uint64_t* count);
 /* The context's CUDA stream as an opaque pointer (cudaStream_t), for callers
@@ -211,14 +215,22 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t 
  * device.  Raw device pointers in, nothing allocated or freed, no context needed:
  *     y[M,N] (f32) = x[M,K] (f32) . (w[N,K] (int8, row-major) * scales[N])^T      on `stream` (a cudaStream_t).
  * The kernel's scratch is a fixed ~1.5 MiB array that lives inside the library on every GPU that loads it,
- * which caps the shapes: M <= 8 rows and K <= 8192 (K % 16 == 0, w 16-byte aligned); larger calls are
- * rejected with RUSTY_CUDA_ERR_INVALID_DIMENSIONS.  The current device must be the one the pointers belong
- * to.  The first call on each device looks the array's address up; make that call before any stream capture.
+ * which caps the shapes: M <= 8 rows, K <= 8192 (K % 16 == 0, w 16-byte aligned) and N <= 262144 (one arrival
+ * counter per 128-row tile); larger calls are rejected with RUSTY_CUDA_ERR_INVALID_DIMENSIONS before anything is
+ * launched.  The current device must be the one the pointers belong to.  The first call on each device looks the
+ * array's address up; make that call before any stream capture.
  * All calls share the one array: it is cleared where the kernel needs zeros, it otherwise keeps the previous
- * call's contents, and two calls that overlap on the GPU (different streams) race on it. */
+ * call's contents, and two calls that overlap on the GPU (different streams) race on it.
+ * The call only enqueues.  A bounded device-side wait that gives up (it cannot, unless two calls raced) leaves y
+ * incomplete and raises a flag in the array, which rusty_cuda_qlinear_i8_static_status reports. */
 RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w_i8, const float* scales, const float* x_f32,
                                                         float* y_f32, uint32_t M, uint32_t N, uint32_t K,
                                                         void* stream);
+/* Drains `stream` and returns RUSTY_CUDA_ERR_TIMEOUT when the most recent static forward on the current device gave
+ * up on a wait, RUSTY_CUDA_OK otherwise (the next static forward clears the flag).  Allocates nothing.  No
+ * counterpart in the reference.  The _decode form maps a raw status word to the same codes on the host alone. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_i8_static_status(void* stream);
+RUSTY_CUDA_API int rusty_cuda_qlinear_i8_static_status_decode(unsigned int timeout_flag, unsigned int timeout_where);
 
 /* ---- output-feature sharding across the GPUs of one node -------------------
  * No counterpart in the reference (single device, no collective anywhere); this
@@ -334,14 +346,8 @@ RUSTY_CUDA_API int rusty_cuda_event_elapsed_ms(rusty_cuda_ctx* ctx, rusty_cuda_e
                                                float* ms);
 RUSTY_CUDA_API int rusty_cuda_event_destroy(rusty_cuda_event* ev);
 
-/* ---- development aid (no counterpart in the reference) ----------------------------
- * Attach a device buffer into which the int8 tensor-core kernel pair writes %globaltimer stamps (nanoseconds), one
- * region of 152 x 16 int64 slots per launch pair in the order of the calls, round robin over the regions that fit:
- * rows 0..147 = the GEMM's CTAs (slot 0 start, 1 set-up done, 2 first weight copy issued, 3 producer done, 4 first
- * MMA, 5 last MMA committed, 6-13 epilogue stages, 14 before tear-down, 15 exit), row 150 = the digit pre-pass
- * (0 start, 1 the kernel before has finished, 2 end, 3 the other ranks have been heard from).  NULL detaches.  Attach
- * before recording a graph: the region addresses are fixed at enqueue time.  `python -m rusty_b200.timeline` prints one. */
-RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf);
+/* ---- harness helper (no counterpart in the reference) ------------------------------
+ */
 /* Overwrite `bytes` bytes at `offset` with `value` (cudaMemsetAsync); used by
  * harnesses to flush L2 between timed iterations and to clear outputs. */
 RUSTY_CUDA_API int rusty_cuda_buf_fill_u8(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf, size_t offset, int value,

@@ -65,6 +65,12 @@ def num_threads() -> int:
     return lib().oracle_num_threads()
 
 
+def set_num_threads(n: int) -> int:
+    """Use `n` host threads in the threaded (timing) variants, whatever OMP_NUM_THREADS says; returns the count in force."""
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 def matmul_tiled(a, b, fma: bool = False) -> np.ndarray:
     a, pa = _f32(a)
     b, pb = _f32(b)

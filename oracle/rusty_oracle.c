@@ -197,6 +197,14 @@ ORACLE_API void oracle_qlinear_rowscale(const float* x, const int8_t* q, const f
  * above, rows spread over host threads; the per-output summation order is
  * unchanged so results are bit-identical to the scalar versions).
  * ------------------------------------------------------------------------- */
+/* Fix the thread count of the threaded variants explicitly (a launcher may have exported OMP_NUM_THREADS=1). */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
 ORACLE_API int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

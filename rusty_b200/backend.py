@@ -72,6 +72,10 @@ class CudaContext:
     def sync(self) -> None:
         check(lib().rusty_cuda_sync(self.handle), self.handle)
 
+    def self_check(self) -> None:
+        """Raises if a kernel wrote outside its region of the context's internal scratch (guard zones)."""
+        check(lib().rusty_cuda_ctx_self_check(self.handle), self.handle)
+
     def launch_count(self) -> int:
         n = C.c_uint64()
         check(lib().rusty_cuda_ctx_launch_count(self.handle, C.byref(n)), self.handle)

@@ -49,6 +49,8 @@ def _deps_mtime() -> float:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = _nvcc()
+    # RUSTY_TIMELINE=1 in the environment: a development build whose kernels can write %globaltimer stamps
+    extra = ["-DRUSTY_TIMELINE"] if os.environ.get("RUSTY_TIMELINE") == "1" else []
     os.makedirs(OBJ, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     hdr_t = _deps_mtime()
@@ -58,7 +60,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(OBJ, os.path.basename(s)[:-3] + ".o")
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr_t):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append(cmd)
 
     def run(cmd):

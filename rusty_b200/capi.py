@@ -51,6 +51,7 @@ SIGNATURES = {
     "rusty_cuda_ctx_adapter_info": ([_vp, C.c_char_p, _sz], _int),
     "rusty_cuda_last_error": ([_vp], C.c_char_p),
     "rusty_cuda_sync": ([_vp], _int),
+    "rusty_cuda_ctx_self_check": ([_vp], _int),
     "rusty_cuda_ctx_launch_count": ([_vp, C.POINTER(C.c_uint64)], _int),
     "rusty_cuda_ctx_stream": ([_vp, _vpp], _int),
     "rusty_cuda_buf_alloc": ([_vp, _sz, _int, _vpp], _int),
@@ -77,6 +78,8 @@ SIGNATURES = {
     "rusty_cuda_qlinear_forward": ([_vp, _vp, _vp, _int, _u32, _vp, _int], _int),
     "rusty_cuda_qlinear_forward_batch": ([_vp, _sz, _vpp, _vpp, _int, _u32, _vpp, _int], _int),
     "rusty_cuda_qlinear_i8_forward_static": ([_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp], _int),
+    "rusty_cuda_qlinear_i8_static_status": ([_vp], _int),
+    "rusty_cuda_qlinear_i8_static_status_decode": ([C.c_uint, C.c_uint], _int),
     "rusty_cuda_comm_unique_id": ([_vp], _int),
     "rusty_cuda_comm_create": ([_vp, _int, _int, _vp, _vpp], _int),
     "rusty_cuda_comm_destroy": ([_vp], _int),
@@ -104,7 +107,6 @@ SIGNATURES = {
     "rusty_cuda_event_record": ([_vp, _vp], _int),
     "rusty_cuda_event_elapsed_ms": ([_vp, _vp, _vp, C.POINTER(C.c_float)], _int),
     "rusty_cuda_event_destroy": ([_vp], _int),
-    "rusty_cuda_debug_set_timeline": ([_vp, _vp], _int),
     "rusty_cuda_buf_fill_u8": ([_vp, _vp, _sz, _int, _sz], _int),
     "rusty_cuda_qlinear_plan": ([_vp, _int, _u32, _int, C.c_char_p, _sz], _int),
 }

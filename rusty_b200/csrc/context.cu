@@ -57,6 +57,20 @@ int after_launch(rusty_cuda_ctx* ctx, const char* kernel) {
 
 using namespace rusty;
 
+namespace rusty {
+cudaError_t ensure_dynamic_smem(const void* kernel, int device, size_t bytes) {
+    static std::mutex mu;
+    static std::unordered_map<uint64_t, size_t> high;  // (kernel address mixed with the device ordinal) -> bytes opted in
+    const uint64_t key = (uint64_t)reinterpret_cast<uintptr_t>(kernel) * 1315423911ull + (uint64_t)(uint32_t)device;
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = high.find(key);
+    if (it != high.end() && it->second >= bytes) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) high[key] = bytes;
+    return e;
+}
+}  // namespace rusty
+
 extern "C" {
 
 int rusty_cuda_device_count(int* count) {
@@ -150,6 +164,18 @@ const char* rusty_cuda_last_error(rusty_cuda_ctx* ctx) {
         if ((ctx)->capturing)                                                                                 \
             return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, what ": not allowed while a graph capture is open"); \
     } while (0)
+
+int rusty_cuda_ctx_self_check(rusty_cuda_ctx* ctx) {
+    RUSTY_REQUIRE_CTX(ctx);
+    RUSTY_NOT_CAPTURING(ctx, "self_check");
+    DeviceGuard g(ctx->device);
+    cudaError_t e = cudaSuccess;
+    const int bad = tc_workspace_check_guards(ctx, &e);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "self_check: reading the guard zones");
+    if (bad >= 0)
+        return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "self_check: guard zone %d of the kernel workspace was overwritten", bad);
+    return RUSTY_CUDA_OK;
+}
 
 int rusty_cuda_sync(rusty_cuda_ctx* ctx) {
     RUSTY_REQUIRE_CTX(ctx);

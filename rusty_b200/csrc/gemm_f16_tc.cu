@@ -55,7 +55,6 @@ struct F16Params {
     unsigned int* counters;   // [sk_units] arrivals per cut tile (zero between uses)
     int ldy, y_col0;
     uint32_t idesc;
-    int dbg_mode;         // tuning aid (RUSTY_F16_DBG): 1 = converters skip their work, 2 = MMA thread issues nothing
     rusty_cuda_dev_status* status;
 };
 
@@ -229,7 +228,7 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                         const uint64_t db = make_smem_desc(smem_u32(sX + (size_t)xs * x_stage_bytes));
 #pragma unroll
                         for (int k16 = 0; k16 < XK / 16; ++k16)
-                            if (p.dbg_mode != 2) umma_f16_ts(tmem_base, a_tmem + (uint32_t)((h * (XK / 16) + k16) * 8), db + (uint64_t)(2 * k16), p.idesc,
+                            umma_f16_ts(tmem_base, a_tmem + (uint32_t)((h * (XK / 16) + k16) * 8), db + (uint64_t)(2 * k16), p.idesc,
                                         (s > pc.s0 || h > 0 || k16 > 0) ? 1u : 0u);
                         umma_commit(&x_empty[xs]);
                         if (++xs == p.x_stages) { xs = 0; xph ^= 1u; }
@@ -257,27 +256,18 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 // row r of the swizzled tile: logical 16-byte chunk c sits at physical chunk c ^ (r & 7)
                 const uint4* row = reinterpret_cast<const uint4*>(sW + (size_t)ws * W_STAGE_BYTES + (size_t)r * WK);
                 uint4 raw[4];
-                if (p.dbg_mode != 1) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) raw[c] = row[(half * 4 + c) ^ (r & 7)];
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) raw[c] = make_uint4(0, 0, 0, 0);
-                }
+                for (int c = 0; c < 4; ++c) raw[c] = row[(half * 4 + c) ^ (r & 7)];
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&w_empty[ws]);  // this warp's share is in registers
                 if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
                 uint32_t cv[32];
-                if (p.dbg_mode != 1) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[c], cv + 8 * c);
-                }
+                for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[c], cv + 8 * c);
                 if (!mbar_wait(&a_empty[ab], aph ^ 1u, abort_flag, p.status, 17)) { ok = false; break; }
                 tc_fence_after();
-                if (p.dbg_mode != 1) {
-                    tmem_st32(tmem_a0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * A_COLS + half * 32), cv);
-                    tmem_st_wait();
-                }
+                tmem_st32(tmem_a0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * A_COLS + half * 32), cv);
+                tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[ab]);
@@ -404,10 +394,6 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
     p.status = ctx->status_dev;
-    {
-        static const int dbg = getenv("RUSTY_F16_DBG") ? atoi(getenv("RUSTY_F16_DBG")) : 0;
-        p.dbg_mode = dbg;
-    }
     // bf16 A x bf16 B -> f32: c_format=F32(1)@4, a_format=BF16(1)@7, b_format=BF16(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     const size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
@@ -450,12 +436,9 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     }
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
     auto kern = yb ? qlinear_f16_tc_kernel<__nv_bfloat16> : qlinear_f16_tc_kernel<float>;
-    static size_t smem_set[2][16] = {{0}};
-    size_t& cur = smem_set[yb ? 1 : 0][ctx->device & 15];
-    if (smem > cur) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_f16_tc: cudaFuncSetAttribute");
-        cur = smem;
     }
     cudaError_t le = launch_pdl(kern, dim3(grid), dim3(F16_THREADS), smem, ctx->stream, map_w, map_x, p);
     if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_f16_tc");

@@ -38,6 +38,15 @@ using namespace rusty_tc;
 
 namespace {
 
+// Kernel timeline (%globaltimer stamps per CTA), compiled in only with -DRUSTY_TIMELINE (a development build).
+#ifdef RUSTY_TIMELINE
+#define DBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = (long long)globaltimer_ns(); } while (0)
+#define PDBG(cond, slot) do { if (dbg && (cond)) dbg[slot] = (long long)globaltimer_ns(); } while (0)
+#else
+#define DBG(slot) do { } while (0)
+#define PDBG(cond, slot) do { } while (0)
+#endif
+
 constexpr int BM = 128;            // weight rows per tile = UMMA M
 constexpr int BK = 128;            // k-elements (bytes) per pipeline stage
 constexpr int UMMA_K = 32;         // k-elements per tcgen05.mma kind::i8
@@ -87,10 +96,10 @@ __global__ void __launch_bounds__(DIG_THREADS) digitize_x_kernel(const XT* __res
     __shared__ float red[DIG_THREADS / 32];
     __shared__ float s_scale;
     const int tid = threadIdx.x;
-    if (dbg && tid == 0 && m == 0) dbg[0] = (long long)globaltimer_ns();
+    PDBG(tid == 0 && m == 0, 0);
     pdl_launch_dependents();
     pdl_wait();  // x may come from the previous kernel, and that kernel may still be reading the digit planes
-    if (dbg && tid == 0 && m == 0) dbg[1] = (long long)globaltimer_ns();
+    PDBG(tid == 0 && m == 0, 1);
     // arrival counters of the GEMM's shared tiles: the kernel before has finished with them, the GEMM after this
     // kernel counts from zero
     for (int i = m * DIG_THREADS + tid; i < n_counters; i += gridDim.x * DIG_THREADS) counters[i] = 0u;
@@ -99,7 +108,7 @@ __global__ void __launch_bounds__(DIG_THREADS) digitize_x_kernel(const XT* __res
         // wait until every rank has finished (and delivered) all earlier pushes
         if (tid == 0) peer_wait_all(push, 30);
         __syncthreads();
-        if (dbg && tid == 0 && m == 0) dbg[3] = (long long)globaltimer_ns();
+        PDBG(tid == 0 && m == 0, 3);
     }
     if (m >= M) {
         for (int k = tid * 4; k < K; k += DIG_THREADS * 4)
@@ -185,7 +194,7 @@ __global__ void __launch_bounds__(DIG_THREADS) digitize_x_kernel(const XT* __res
     } else {
         for (int k = tid * 4; k < K; k += DIG_THREADS * 4) emit(k, load_row4<XT>(xr + k));  // K % 4 == 0 (K % 16 == 0 is required by the caller)
     }
-    if (dbg && tid == 0 && m == 0) dbg[2] = (long long)globaltimer_ns();
+    PDBG(tid == 0 && m == 0, 2);
 }
 
 // ----------------------------------------------------------------------------
@@ -363,7 +372,6 @@ __device__ __forceinline__ float4 load_x4(const TcParams& p, int m, int k) {
     return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_raw) + (size_t)m * p.K + k);
 }
 
-#define DBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = (long long)globaltimer_ns(); } while (0)
 
 template <typename YT>
 __global__ void __launch_bounds__(TC_THREADS, 2)
@@ -954,17 +962,94 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 // ----------------------------------------------------------------------------
 // Host side
 // ----------------------------------------------------------------------------
+// Workspace layout.  Every region is followed by a guard zone filled with a fixed byte that no kernel may touch;
+// rusty_cuda_ctx_self_check reads the guards back (the tool-free stand-in for a memory checker).
+constexpr size_t WS_GUARD = 1024;
+constexpr unsigned char WS_GUARD_BYTE = 0xA5;
 constexpr size_t WS_XQ_BYTES = 24u << 20;      // digit planes: up to 256 rows x K <= 96K
 constexpr size_t WS_INVS_BYTES = 4096;
 constexpr size_t WS_ACC_BYTES = 48u << 20;     // split-K partial sums
 constexpr size_t WS_CNT_BYTES = 64u << 10;     // arrival counters, kept at zero between kernels (small-batch mode, prefill kernels)
 constexpr size_t WS_CNT2_BYTES = 64u << 10;    // arrival counters of the GEMM with a pre-pass, which clears them
-constexpr size_t WS_TOTAL = WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES + WS_CNT_BYTES + WS_CNT2_BYTES;
+constexpr size_t WS_OFF_XQ = 0;
+constexpr size_t WS_OFF_INVS = WS_OFF_XQ + WS_XQ_BYTES + WS_GUARD;
+constexpr size_t WS_OFF_ACC = WS_OFF_INVS + WS_INVS_BYTES + WS_GUARD;
+constexpr size_t WS_OFF_CNT = WS_OFF_ACC + WS_ACC_BYTES + WS_GUARD;
+constexpr size_t WS_OFF_CNT2 = WS_OFF_CNT + WS_CNT_BYTES + WS_GUARD;
+constexpr size_t WS_TOTAL = WS_OFF_CNT2 + WS_CNT2_BYTES + WS_GUARD;
+constexpr size_t WS_GUARD_AT[5] = {WS_OFF_INVS - WS_GUARD, WS_OFF_ACC - WS_GUARD, WS_OFF_CNT - WS_GUARD, WS_OFF_CNT2 - WS_GUARD,
+                                   WS_TOTAL - WS_GUARD};
+
+// The schedule of one launch: how the row tiles are dealt to the CTAs.  One place for the regular entry points and the
+// entry point with built-in scratch, so that their guards cannot drift apart.
+//   whole tiles (tile = cta, cta + grid, ...) for the first dp_tiles tiles; the last sk_tiles tiles are cut along K.
+// `sums_tiles_cap` / `counter_cap`: how many cut tiles the caller's scratch can park / how many arrival counters
+// (indexed by the GLOBAL tile number) it holds.  Returns false when N needs more counters than there are.
+struct TcSchedule {
+    int grid, dp_tiles, sk_tiles, sk_per_cta, sk_ctas, sk_ways;
+};
+bool plan_tc_schedule(int tiles, int kb_total, int sm_count, bool fused, int dp_percent, size_t sums_tiles_cap, size_t counter_cap,
+                      TcSchedule* out) {
+    if ((size_t)tiles > counter_cap) return false;
+    TcSchedule s{};
+    // Whole waves of row tiles are taken tile-per-CTA; the remainder (fewer tiles than SMs) is cut stream-K fashion so
+    // every SM streams the same number of k-blocks.  A cut needs >= 4 k-blocks per CTA and room for the parked tiles.
+    int grid = sm_count;
+    if (grid > tiles * kb_total / 4) grid = tiles * kb_total / 4 > 0 ? tiles * kb_total / 4 : 1;
+    s.sk_tiles = tiles % grid;
+    s.dp_tiles = tiles - s.sk_tiles;
+    // Whole tiles only, dealt evenly (r or r-1 per CTA), when that still keeps most SMs streaming: ~110 SMs at the
+    // tensor-core rate already draw the full HBM bandwidth, and a CTA without shared tiles skips the bulk
+    // reduce-add, the wait for the other pieces and the shared conversion (5-10 us at the end of the kernel).
+    {
+        const int r = (tiles + sm_count - 1) / sm_count;   // tiles per CTA
+        const int g_dp = r > 0 ? (tiles + r - 1) / r : 0;  // CTAs that then have work
+        if (!fused && s.sk_tiles > 0 && g_dp * 100 >= sm_count * dp_percent) {
+            grid = g_dp;
+            s.sk_tiles = 0;
+            s.dp_tiles = tiles;
+        }
+    }
+    if (s.sk_tiles > 0) {
+        const int sk_work = s.sk_tiles * kb_total;
+        s.sk_per_cta = (sk_work + grid - 1) / grid;
+        if (s.sk_per_cta < 4) s.sk_per_cta = 4;
+        // Prefer cuts that line up with tile borders (every CTA then holds one piece and a tile has exactly
+        // `ways` pieces) when that keeps at least 85% of the SMs busy.
+        const int ways = grid / s.sk_tiles;
+        if (ways >= 1) {
+            const int aligned = (kb_total + ways - 1) / ways;
+            if (aligned >= 4 && (long long)s.sk_per_cta * 100 >= (long long)aligned * 85) s.sk_per_cta = aligned;
+        }
+        s.sk_ctas = (sk_work + s.sk_per_cta - 1) / s.sk_per_cta;
+        // No whole tiles at all and room for `ways` CTAs per tile: cut every tile at the same places, so that each CTA
+        // holds exactly one piece (runs of a fixed length drift across tile borders and leave most CTAs with two).
+        if (s.dp_tiles == 0 && ways >= 2 && kb_total / ways >= 4) {
+            s.sk_ways = ways;
+            s.sk_ctas = s.sk_tiles * ways;
+            s.sk_per_cta = (kb_total + ways - 1) / ways;
+        }
+        if ((size_t)s.sk_tiles > sums_tiles_cap) {
+            s.dp_tiles = tiles;  // no room to park partial tiles: whole tiles only
+            s.sk_tiles = 0;
+            s.sk_per_cta = 0;
+            s.sk_ctas = 0;
+            s.sk_ways = 0;
+            if (grid > tiles) grid = tiles;
+        }
+    }
+    if (s.dp_tiles == 0 && s.sk_ctas > 0) grid = s.sk_ctas;
+    s.grid = grid;
+    *out = s;
+    return true;
+}
 
 int pick_digits(int x_dtype, uint32_t rows) {
-    // 4 digits (28 bits under the row maximum) while the B operand stays narrow, else 3 (21 bits).
-    uint32_t mpad = (rows + 7) / 8 * 8;
-    return (x_dtype == RUSTY_CUDA_F32 && mpad * 4 <= 64) ? 4 : 3;
+    // f32 activations: 4 planes = 28 bits below the row maximum.  Three planes (21 bits) hold the fp32 tolerance only
+    // while the row's largest element stays within ~25x of its rms: with one outlier of 1000x every other element
+    // keeps 11 bits and the result is ~5e-5 off.  bf16 activations carry 8 significant bits each: 3 planes.
+    (void)rows;
+    return x_dtype == RUSTY_CUDA_F32 ? 4 : 3;
 }
 
 template <typename XT>
@@ -990,6 +1075,7 @@ int tc_workspace_reserve(rusty_cuda_ctx* ctx) {
         return fail(ctx, RUSTY_CUDA_ERR_MEMORY_ALLOCATION, "tensor-core workspace: cudaMalloc(%zu) failed", (size_t)WS_TOTAL);
     }
     e = cudaMemsetAsync(p, 0, WS_TOTAL, ctx->stream);
+    for (size_t g = 0; e == cudaSuccess && g < 5; ++g) e = cudaMemsetAsync((uint8_t*)p + WS_GUARD_AT[g], WS_GUARD_BYTE, WS_GUARD, ctx->stream);
     if (e != cudaSuccess) {
         cudaFree(p);
         return check_cuda(ctx, e, "tensor-core workspace: memset");
@@ -1003,10 +1089,25 @@ int tc_workspace_reserve(rusty_cuda_ctx* ctx) {
 // kernels: both leave zeros behind, and kernels on one stream never overlap in their epilogues.
 void tc_workspace_sums(rusty_cuda_ctx* ctx, float** sums, size_t* sums_bytes, unsigned int** counters, size_t* cnt_bytes) {
     uint8_t* ws = (uint8_t*)ctx->tc_ws;
-    *sums = ws ? (float*)(ws + WS_XQ_BYTES + WS_INVS_BYTES) : nullptr;
+    *sums = ws ? (float*)(ws + WS_OFF_ACC) : nullptr;
     *sums_bytes = WS_ACC_BYTES;
-    *counters = ws ? (unsigned int*)(ws + WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES) : nullptr;
+    *counters = ws ? (unsigned int*)(ws + WS_OFF_CNT) : nullptr;
     *cnt_bytes = WS_CNT_BYTES;
+}
+
+// Reads the guard zones back (drains the stream).  Returns the index of the first damaged guard, or -1.
+int tc_workspace_check_guards(rusty_cuda_ctx* ctx, cudaError_t* err) {
+    *err = cudaSuccess;
+    if (!ctx->tc_ws) return -1;
+    std::vector<unsigned char> host(WS_GUARD);
+    for (int g = 0; g < 5; ++g) {
+        *err = cudaMemcpyAsync(host.data(), (uint8_t*)ctx->tc_ws + WS_GUARD_AT[g], WS_GUARD, cudaMemcpyDeviceToHost, ctx->stream);
+        if (*err == cudaSuccess) *err = cudaStreamSynchronize(ctx->stream);
+        if (*err != cudaSuccess) return -1;
+        for (size_t i = 0; i < WS_GUARD; ++i)
+            if (host[i] != WS_GUARD_BYTE) return g;
+    }
+    return -1;
 }
 
 void tc_workspace_release(rusty_cuda_ctx* ctx) {
@@ -1047,10 +1148,10 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     const int NB = (fused && D * Mpad <= 8) ? 8 : (D * Mpad + 15) / 16 * 16;
     uint8_t* ws = (uint8_t*)ctx->tc_ws;
     int8_t* xq = (int8_t*)ws;
-    float* inv_s = (float*)(ws + WS_XQ_BYTES);
-    int32_t* acc = (int32_t*)(ws + WS_XQ_BYTES + WS_INVS_BYTES);
+    float* inv_s = (float*)(ws + WS_OFF_INVS);
+    int32_t* acc = (int32_t*)(ws + WS_OFF_ACC);
     // two sets of arrival counters: one kept at zero by its users, one cleared by the pre-pass of this path
-    unsigned int* counters = (unsigned int*)(ws + WS_XQ_BYTES + WS_INVS_BYTES + WS_ACC_BYTES + (fused ? 0 : WS_CNT_BYTES));
+    unsigned int* counters = (unsigned int*)(ws + (fused ? WS_OFF_CNT : WS_OFF_CNT2));
     if ((size_t)D * Mpad * a.K > WS_XQ_BYTES)
         return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: %d digit rows x K=%u exceed the workspace", D * Mpad, a.K);
 
@@ -1092,60 +1193,18 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.K = (int)a.K;
     p.tiles = (p.N + BM - 1) / BM;
     p.kb_total = (p.K + BK - 1) / BK;
-    // Whole waves of row tiles are taken tile-per-CTA; the remainder (fewer tiles
-    // than SMs) is cut stream-K fashion so every SM streams the same number of
-    // k-blocks.  A cut needs >= 4 k-blocks per CTA, a counter per tile and room
-    // for two parked partial tiles per CTA; otherwise the remainder is taken whole too.
-    int grid = ctx->sm_count;
-    if (grid > p.tiles * p.kb_total / 4) grid = p.tiles * p.kb_total / 4 > 0 ? p.tiles * p.kb_total / 4 : 1;
-    p.sk_tiles = p.tiles % grid;
-    p.dp_tiles = p.tiles - p.sk_tiles;
-    // Whole tiles only, dealt evenly (r or r-1 per CTA), when that still keeps most SMs streaming: ~110 SMs at the
-    // tensor-core rate already draw the full HBM bandwidth, and a CTA without shared tiles skips the bulk
-    // reduce-add, the wait for the other pieces and the shared conversion (5-10 us at the end of the kernel).
-    // RUSTY_TC_DP_PERCENT: least share of the SMs (default 72; 101 turns the rule off).
-    {
-        static const int dp_percent = getenv("RUSTY_TC_DP_PERCENT") ? atoi(getenv("RUSTY_TC_DP_PERCENT")) : 72;
-        const int r = (p.tiles + ctx->sm_count - 1) / ctx->sm_count;      // tiles per CTA
-        const int g_dp = r > 0 ? (p.tiles + r - 1) / r : 0;              // CTAs that then have work
-        if (!fused && p.sk_tiles > 0 && g_dp * 100 >= ctx->sm_count * dp_percent) {
-            grid = g_dp;
-            p.sk_tiles = 0;
-            p.dp_tiles = p.tiles;
-        }
-    }
-    p.sk_per_cta = 0;
-    p.sk_ctas = 0;
-    if (p.sk_tiles > 0) {
-        const int sk_work = p.sk_tiles * p.kb_total;
-        p.sk_per_cta = (sk_work + grid - 1) / grid;
-        if (p.sk_per_cta < 4) p.sk_per_cta = 4;
-        // Prefer cuts that line up with tile borders (every CTA then holds one piece and a tile has exactly
-        // `ways` pieces) when that keeps at least 85% of the SMs busy.
-        const int ways = grid / p.sk_tiles;
-        if (ways >= 1) {
-            const int aligned = (p.kb_total + ways - 1) / ways;
-            if (aligned >= 4 && (long long)p.sk_per_cta * 100 >= (long long)aligned * 85) p.sk_per_cta = aligned;
-        }
-        p.sk_ctas = (sk_work + p.sk_per_cta - 1) / p.sk_per_cta;
-        // No whole tiles at all and room for `ways` CTAs per tile: cut every tile at the same places, so that each CTA
-        // holds exactly one piece (runs of a fixed length drift across tile borders and leave most CTAs with two).
-        if (p.dp_tiles == 0 && ways >= 2 && p.kb_total / ways >= 4) {
-            p.sk_ways = ways;
-            p.sk_ctas = p.sk_tiles * ways;
-            p.sk_per_cta = (p.kb_total + ways - 1) / ways;
-        }
-        const size_t need = (size_t)p.sk_tiles * (fused ? 4 : Mpad) * BM * 8;
-        if (need > WS_ACC_BYTES || (size_t)p.tiles * 4 > WS_CNT_BYTES) {
-            p.dp_tiles = p.tiles;  // no room to park partial tiles: whole tiles only
-            p.sk_tiles = 0;
-            p.sk_per_cta = 0;
-            p.sk_ctas = 0;
-            p.sk_ways = 0;
-            if (grid > p.tiles) grid = p.tiles;
-        }
-    }
-    if (p.dp_tiles == 0 && p.sk_ctas > 0) grid = p.sk_ctas;
+    // RUSTY_TC_DP_PERCENT: least share of the SMs that whole tiles must keep streaming (default 72; 101 turns the rule off).
+    static const int dp_percent = getenv("RUSTY_TC_DP_PERCENT") ? atoi(getenv("RUSTY_TC_DP_PERCENT")) : 72;
+    TcSchedule sc{};
+    if (!plan_tc_schedule(p.tiles, p.kb_total, ctx->sm_count, fused, dp_percent, WS_ACC_BYTES / ((size_t)(fused ? 4 : Mpad) * BM * 8),
+                          WS_CNT_BYTES / 4, &sc))
+        return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: N=%u has more row tiles than arrival counters", a.N);
+    int grid = sc.grid;
+    p.dp_tiles = sc.dp_tiles;
+    p.sk_tiles = sc.sk_tiles;
+    p.sk_per_cta = sc.sk_per_cta;
+    p.sk_ctas = sc.sk_ctas;
+    p.sk_ways = sc.sk_ways;
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
     p.act = a.act;
@@ -1188,12 +1247,9 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
 
     auto kern = yb ? qlinear_i8_tc_kernel<__nv_bfloat16> : qlinear_i8_tc_kernel<float>;
-    static size_t smem_set[2][16] = {{0}};
-    size_t& cur = smem_set[yb ? 1 : 0][ctx->device & 15];
-    if (smem > cur) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_i8_tc: cudaFuncSetAttribute");
-        cur = smem;
     }
     // Pieces of one tile held by consecutive CTAs: launch them as a thread-block cluster and sum through distributed
     // shared memory, when every cluster can be resident at once (one wave).  Opt-in: RUSTY_TC_CLUSTER=1.
@@ -1236,8 +1292,9 @@ int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
 
 }  // namespace rusty
 
-// Development aid: point the kernels' timeline (%globaltimer stamps, one region of 152 x 16 slots per launch pair)
-// at a caller buffer, or detach it with NULL.
+#ifdef RUSTY_TIMELINE
+// Development builds only (-DRUSTY_TIMELINE; not part of the C ABI): point the kernels' timeline (%globaltimer stamps,
+// one region of 152 x 16 int64 slots per launch pair, round robin) at a caller buffer, or detach it with NULL.
 extern "C" RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx, rusty_cuda_buf* buf) {
     if (!ctx) return RUSTY_CUDA_ERR_INVALID_OPERATION;
     ctx->tc_dbg = buf ? buf->ptr : nullptr;
@@ -1245,6 +1302,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx,
     ctx->tc_dbg_slots = buf ? (int)(buf->bytes / (152 * 16 * 8)) : 0;
     return RUSTY_CUDA_OK;
 }
+#endif
 
 // ----------------------------------------------------------------------------
 // Entry point for callers that must not allocate device memory.
@@ -1261,13 +1319,17 @@ namespace {
 
 constexpr uint32_t STATIC_MAX_ROWS = 8;       // activation rows per call
 constexpr uint32_t STATIC_MAX_K = 8192;       // input features
+constexpr uint32_t STATIC_MAX_N = 262144;     // output features: one arrival counter per 128-row tile, indexed by tile number
 constexpr int STATIC_MAX_CTAS = 160;          // CTAs launched at most (one per SM)
 constexpr size_t ST_XQ_BYTES = (size_t)4 * 8 * STATIC_MAX_K;            // 4 digit planes x 8 padded rows
 constexpr size_t ST_FACTOR_BYTES = 256;
-constexpr size_t ST_SUMS_BYTES = (size_t)STATIC_MAX_CTAS * 8 * 8 * BM;  // one parked 8-row tile (int64) per cut tile
-constexpr size_t ST_CNT_BYTES = 1024;
+constexpr size_t ST_SUMS_TILES = STATIC_MAX_CTAS;                        // cut tiles parked at most (fewer than CTAs)
+constexpr size_t ST_SUMS_BYTES = ST_SUMS_TILES * 8 * 8 * BM;            // one parked 8-row tile (int64) per cut tile
+constexpr size_t ST_CNT_BYTES = (size_t)(STATIC_MAX_N / BM) * 4;        // 2048 counters
 constexpr size_t ST_STATUS_BYTES = 256;
 constexpr size_t ST_TOTAL = ST_XQ_BYTES + ST_FACTOR_BYTES + ST_SUMS_BYTES + ST_CNT_BYTES + ST_STATUS_BYTES;  // ~1.5 MiB
+static_assert(ST_CNT_BYTES / 4 * BM == STATIC_MAX_N, "one arrival counter per row tile up to STATIC_MAX_N");
+static_assert(STATIC_MAX_N % BM == 0, "the N cap is a whole number of row tiles");
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) unsigned char g_static_scratch[ST_TOTAL];
@@ -1281,6 +1343,12 @@ struct StaticDev {
 std::mutex g_static_mu;
 StaticDev g_static_dev[64];
 
+int static_status_to_code(unsigned int timeout_flag, unsigned int timeout_where) {
+    if (timeout_flag == 0u) return RUSTY_CUDA_OK;
+    return rusty::fail(nullptr, RUSTY_CUDA_ERR_TIMEOUT, "qlinear_i8_forward_static: a bounded device-side wait gave up (site %u); y is incomplete",
+                       timeout_where);
+}
+
 }  // namespace
 
 extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w_i8, const float* scales, const float* x_f32,
@@ -1290,10 +1358,10 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     if (!w_i8 || !scales || !x_f32 || !y_f32)
         return fail(nullptr, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_i8_forward_static: null pointer");
     if (M == 0 || N == 0) return RUSTY_CUDA_OK;
-    if (M > STATIC_MAX_ROWS || K > STATIC_MAX_K || K == 0 || K % 16 != 0)
+    if (M > STATIC_MAX_ROWS || K > STATIC_MAX_K || K == 0 || K % 16 != 0 || N > STATIC_MAX_N)
         return fail(nullptr, RUSTY_CUDA_ERR_INVALID_DIMENSIONS,
-                    "qlinear_i8_forward_static: M=%u K=%u outside the fixed scratch (M <= %u, K <= %u, K %% 16 == 0)", M, K,
-                    STATIC_MAX_ROWS, STATIC_MAX_K);
+                    "qlinear_i8_forward_static: M=%u N=%u K=%u outside the fixed scratch (M <= %u, N <= %u, K <= %u, K %% 16 == 0)", M,
+                    N, K, STATIC_MAX_ROWS, STATIC_MAX_N, STATIC_MAX_K);
     if ((reinterpret_cast<uintptr_t>(w_i8) & 15) != 0)
         return fail(nullptr, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_i8_forward_static: weights must be 16-byte aligned");
     if (!encode_tiled_fn())
@@ -1350,17 +1418,17 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     p.K = (int)K;
     p.tiles = (p.N + BM - 1) / BM;
     p.kb_total = (p.K + BK - 1) / BK;
-    int grid = sd.sm_count < STATIC_MAX_CTAS ? sd.sm_count : STATIC_MAX_CTAS;
-    if (grid > p.tiles * p.kb_total / 4) grid = p.tiles * p.kb_total / 4 > 0 ? p.tiles * p.kb_total / 4 : 1;
-    p.sk_tiles = p.tiles % grid;  // < grid <= STATIC_MAX_CTAS parked tiles: fits ST_SUMS_BYTES by construction
-    p.dp_tiles = p.tiles - p.sk_tiles;
-    if (p.sk_tiles > 0) {
-        const int sk_work = p.sk_tiles * p.kb_total;
-        p.sk_per_cta = (sk_work + grid - 1) / grid;
-        if (p.sk_per_cta < 4) p.sk_per_cta = 4;
-        p.sk_ctas = (sk_work + p.sk_per_cta - 1) / p.sk_per_cta;
-    }
-    if (p.dp_tiles == 0 && p.sk_ctas > 0) grid = p.sk_ctas;
+    // the same schedule rules as the regular entry points, with this scratch's capacities
+    TcSchedule sc{};
+    if (!plan_tc_schedule(p.tiles, p.kb_total, sd.sm_count < STATIC_MAX_CTAS ? sd.sm_count : STATIC_MAX_CTAS, /*fused=*/false,
+                          /*dp_percent=*/72, ST_SUMS_TILES, ST_CNT_BYTES / 4, &sc))
+        return fail(nullptr, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_i8_forward_static: N=%u has more row tiles than arrival counters", N);
+    const int grid = sc.grid;
+    p.dp_tiles = sc.dp_tiles;
+    p.sk_tiles = sc.sk_tiles;
+    p.sk_per_cta = sc.sk_per_cta;
+    p.sk_ctas = sc.sk_ctas;
+    p.sk_ways = sc.sk_ways;
     p.ldy = (int)N;
     p.y_col0 = 0;
     p.status = status;
@@ -1391,3 +1459,34 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: launch");
     return RUSTY_CUDA_OK;
 }
+
+// The kernel behind the entry point above bounds every wait; when one runs out it raises a flag in the built-in scratch
+// and leaves y incomplete.  This call drains `stream` and reports that flag of the most recent static forward on the
+// current device (the next static forward clears it).  Allocates nothing.
+extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_static_status(void* stream) {
+    using namespace rusty;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return check_cuda(nullptr, e == cudaSuccess ? cudaErrorInvalidDevice : e, "cudaGetDevice");
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (g_static_dev[dev].ready) base = g_static_dev[dev].base;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!base) {  // no static forward has run on this device yet: nothing to report, only drain
+        e = cudaStreamSynchronize(st);
+        return e == cudaSuccess ? RUSTY_CUDA_OK : check_cuda(nullptr, e, "qlinear_i8_static_status: synchronize");
+    }
+    rusty_cuda_dev_status h{};
+    e = cudaMemcpyAsync(&h, base + ST_XQ_BYTES + ST_FACTOR_BYTES + ST_SUMS_BYTES + ST_CNT_BYTES, sizeof(h), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_static_status");
+    return static_status_to_code(h.timeout_flag, h.timeout_where);
+}
+
+// Host-side decoding of the status word, exposed for tests that have no GPU.
+extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_static_status_decode(unsigned int timeout_flag, unsigned int timeout_where) {
+    return static_status_to_code(timeout_flag, timeout_where);
+}
+

@@ -351,11 +351,9 @@ int launch_nk(rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a, const void* x, v
     const int nchunks = (a.K + CHUNK - 1) / CHUNK;
     size_t smem = (size_t)MB * nchunks * CHUNK * 4 + (AFFINE ? (size_t)MB * nchunks * 32 * 4 : 0);
     auto kern = gemv_nk_kernel<MB, R, U, AFFINE, XT, YT>;
-    static size_t smem_set[16] = {0};  // per device: largest dynamic smem already opted in for this instantiation
-    if (smem > smem_set[ctx->device & 15]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = rusty::ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return rusty::check_cuda(ctx, e, "gemv_nk: cudaFuncSetAttribute");
-        smem_set[ctx->device & 15] = smem;
     }
     int ngroups = (a.N + R - 1) / R;
     int blocks = (ngroups + GEMV_WARPS - 1) / GEMV_WARPS;
@@ -375,11 +373,9 @@ int launch_kn(rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a, const void* x, v
     constexpr int U = 4;
     size_t smem = (size_t)MB * a.K * 4 + (size_t)KN_SLICES * MB * KN_COLS * 4;
     auto kern = gemv_kn_kernel<MB, U, AFFINE, XT, YT>;
-    static size_t smem_set[16] = {0};
-    if (smem > smem_set[ctx->device & 15]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = rusty::ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return rusty::check_cuda(ctx, e, "gemv_kn: cudaFuncSetAttribute");
-        smem_set[ctx->device & 15] = smem;
     }
     int blocks = (a.N + KN_COLS - 1) / KN_COLS;
     kern<<<blocks, KN_THREADS, smem, ctx->stream>>>(a.w, a.scales, a.biases, (const XT*)x, (YT*)y, M, (int)a.N, (int)a.K,

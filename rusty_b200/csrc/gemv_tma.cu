@@ -67,7 +67,11 @@ __device__ __forceinline__ void s8x4_to_f32(uint32_t w, float (&f)[4]) {
 }
 
 // MB activation rows (1 or 2), NJ passes of 4096 k.
+#ifdef RUSTY_TIMELINE
 #define TDBG(slot) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 16 + (slot)] = (long long)globaltimer_ns(); } while (0)
+#else
+#define TDBG(slot) do { } while (0)
+#endif
 
 template <int MB, int NJ>
 __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams p) {
@@ -249,11 +253,9 @@ __global__ void __launch_bounds__(TG_THREADS, 2) gemv_tma_kernel(const TgParams 
 template <int MB, int NJ>
 int launch_tg(rusty_cuda_ctx* ctx, const TgParams& p, int grid, size_t smem) {
     auto kern = gemv_tma_kernel<MB, NJ>;
-    static size_t smem_set[16] = {0};
-    if (smem > smem_set[ctx->device & 15]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = rusty::ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return rusty::check_cuda(ctx, e, "gemv_tma: cudaFuncSetAttribute");
-        smem_set[ctx->device & 15] = smem;
     }
     cudaError_t le = launch_pdl(kern, dim3(grid), dim3(TG_THREADS), smem, ctx->stream, p);
     if (le != cudaSuccess) return rusty::check_cuda(ctx, le, "gemv_tma");

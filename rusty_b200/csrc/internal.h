@@ -104,6 +104,11 @@ inline void count_launch(rusty_cuda_ctx* ctx, uint64_t n = 1) { ctx->launches.fe
 // Checks the launch error of the kernel just enqueued.
 int after_launch(rusty_cuda_ctx* ctx, const char* kernel);
 
+// Raise a kernel's dynamic shared-memory limit on `device` (current) to at least `bytes`.  The per-(kernel, device)
+// high-water mark sits in one mutex-guarded table keyed by the full device ordinal: contexts on different host
+// threads may launch the same kernel at once.
+cudaError_t ensure_dynamic_smem(const void* kernel, int device, size_t bytes);
+
 // Kernel launchers implemented in the .cu files -----------------------------
 int launch_matmul_f32(rusty_cuda_ctx* ctx, const float* a, const float* b, float* out, uint32_t M, uint32_t K,
                       uint32_t N);
@@ -162,6 +167,7 @@ bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 uint32_t tc_min_rows();
 int tc_workspace_reserve(rusty_cuda_ctx* ctx);
 void tc_workspace_release(rusty_cuda_ctx* ctx);
+int tc_workspace_check_guards(rusty_cuda_ctx* ctx, cudaError_t* err);
 void tc_workspace_sums(rusty_cuda_ctx* ctx, float** sums, size_t* sums_bytes, unsigned int** counters, size_t* cnt_bytes);
 int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 bool tc_pushes_fused(uint32_t M);
@@ -170,9 +176,6 @@ bool tc_pushes_fused(uint32_t M);
 bool f16tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 uint32_t f16tc_min_rows();
-// The same with CTA pairs (tcgen05 cta_group::2): each CTA loads half of the activation tile.
-bool f16tc2_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
-int launch_f16tc2(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 
 // True when the kernel chosen for this shape stores into the peers' arenas itself.
 bool qlinear_pushes_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);

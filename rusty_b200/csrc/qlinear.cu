@@ -43,7 +43,6 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
     a.M = M;
     a.act = ql->act;
     // the bf16 prefill kernels have no activation epilogue: batches of pairs go through the int8 kernel in 64-row passes
-    if (!a.act && f16tc2_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16_pair";
     if (!a.act && f16tc_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16";
     if (tc_supported(ql->ctx, a) && M >= tc_min_rows() && (!a.act || tc_pushes_fused(M))) return "tcgen05";
     if (gemv_tma_supported(ql->ctx, a)) return "gemv_tma";
@@ -98,7 +97,6 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
         a.push = push;
     }
     DeviceGuard g(ctx->device);
-    if (!a.act && f16tc2_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc2(ctx, a);
     if (!a.act && f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
     if (tc_supported(ctx, a) && M >= tc_min_rows() && (!a.act || tc_pushes_fused(M))) return launch_tc(ctx, a);
     if (gemv_tma_supported(ctx, a)) return launch_gemv_tma(ctx, a);

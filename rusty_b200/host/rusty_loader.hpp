@@ -257,9 +257,13 @@ public:
             const TensorInfo& t = kv.second;
             const size_t es = dtype_size(t.dtype);
             if (es == 0) throw LoaderError("Safetensors", path + ": " + kv.first + ": unknown dtype " + t.dtype);
-            size_t count = 1;
-            for (size_t d : t.shape) count *= d;
-            if (t.begin > t.end || t.end > data_len_ || t.end - t.begin != count * es)
+            // checked products: a crafted shape such as [2^32, 2^32] must not wrap to a small element count
+            size_t count = 1, nbytes = 0;
+            bool overflow = false;
+            for (size_t d : t.shape) overflow = overflow || __builtin_mul_overflow(count, d, &count);
+            overflow = overflow || __builtin_mul_overflow(count, es, &nbytes);
+            if (overflow) throw LoaderError("Safetensors", path + ": " + kv.first + ": shape overflows the address space");
+            if (t.begin > t.end || t.end > data_len_ || t.end - t.begin != nbytes)
                 throw LoaderError("Safetensors", path + ": " + kv.first + ": data_offsets do not match shape and dtype");
         }
     }

@@ -91,3 +91,13 @@ def test_product_package_does_not_import_the_oracle():
                 text = open(os.path.join(dirpath, f), errors="replace").read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), f
                 assert "liboracle" not in text and "rusty_oracle" not in text, f
+
+
+def test_static_entry_status_word_decodes_on_the_host():
+    """The allocation-free entry point reports a device-side wait that gave up through a status word; the mapping
+    from that word to a status code is host code and needs no GPU."""
+    from rusty_b200 import capi
+    lib = capi.lib()
+    assert lib.rusty_cuda_qlinear_i8_static_status_decode(0, 0) == capi.OK
+    assert lib.rusty_cuda_qlinear_i8_static_status_decode(1, 8) == capi.ERR_TIMEOUT
+    assert b"site 8" in lib.rusty_cuda_last_error(None)

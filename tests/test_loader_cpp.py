@@ -69,6 +69,14 @@ def test_error_variants(exe, checkpoint, tmp_path):
     bad.write_bytes((4).to_bytes(8, "little") + b"{{{{")
     r = subprocess.run([exe, "info", str(bad)], capture_output=True, text=True, timeout=60)
     assert r.returncode == 3 and r.stdout.strip() == "LoaderError Json"
+    # a crafted shape whose element count wraps around 2^64: [2^32, 2^32] over zero bytes must be refused, not
+    # accepted as an empty tensor with huge dimensions
+    import json
+    hdr = json.dumps({"w.weight": {"dtype": "U8", "shape": [2 ** 32, 2 ** 32], "data_offsets": [0, 0]}}).encode()
+    wrap = tmp_path / "wrap.safetensors"
+    wrap.write_bytes(len(hdr).to_bytes(8, "little") + hdr)
+    r = subprocess.run([exe, "info", str(wrap), "w.weight"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 3 and r.stdout.strip() == "LoaderError Safetensors", r.stdout + r.stderr
     r = subprocess.run([exe, "shard", checkpoint, "norm", "0", "1"], capture_output=True, text=True, timeout=60)
     assert r.returncode == 3 and r.stdout.strip() == "LoaderError MissingWeight"   # norm has no quantised parts
     r = subprocess.run([exe, "shard", checkpoint, "layers.0.q_proj", "0", "3"], capture_output=True, text=True, timeout=60)

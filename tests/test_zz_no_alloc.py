@@ -28,7 +28,8 @@ def _static_forward(ctx, ql, x, y, M, N, K):
         M, N, K, C.c_void_p(ctx.stream()))
 
 
-@pytest.mark.parametrize("M,K,N", [(8, 4096, 4096), (5, 1024, 1000), (1, 8192, 384)])
+# the last shape has more row tiles than SMs with a remainder: whole tiles AND cut tiles in one launch, N % 128 != 0
+@pytest.mark.parametrize("M,K,N", [(8, 4096, 4096), (5, 1024, 1000), (1, 8192, 384), (8, 4096, 128 * 200 + 40)])
 def test_static_scratch_entry_matches_regular_entry_twice(ctx, engine, oracle, M, K, N):
     xh, qh, sh = sym_row_linear(900 + M + N, M, K, N)
     ql = QLinear.from_host(ctx, qh, sh)
@@ -40,6 +41,7 @@ def test_static_scratch_entry_matches_regular_entry_twice(ctx, engine, oracle, M
         y = UnifiedTensor.new(ctx, np.full(M * N, np.nan, np.float32), [M, N])
         rc = _static_forward(ctx, ql, x, y, M, N, K)
         assert rc == capi.OK, capi.lib().rusty_cuda_last_error(None)
+        assert capi.lib().rusty_cuda_qlinear_i8_static_status(C.c_void_p(ctx.stream())) == capi.OK   # no wait gave up
         got = y.to_vec(ctx).reshape(M, N)
         assert rel_err(got, want) <= TOL_FP32, f"call {call}"
     ref = oracle.matmul_bt(xh, oracle.dequantize_rowscale(qh, sh), mt=True)
@@ -59,4 +61,8 @@ def test_static_scratch_entry_refuses_what_does_not_fit(ctx):
     assert lib.rusty_cuda_qlinear_i8_forward_static(*args, 1, 16, 16384, C.c_void_p(ctx.stream())) == capi.ERR_INVALID_DIMENSIONS
     assert lib.rusty_cuda_qlinear_i8_forward_static(*args, 1, 16, 72, C.c_void_p(ctx.stream())) == capi.ERR_INVALID_DIMENSIONS
     assert lib.rusty_cuda_qlinear_i8_forward_static(None, *args[1:], 1, 16, 64, C.c_void_p(ctx.stream())) == capi.ERR_INVALID_OPERATION
+    # more output features than the built-in arrival counters cover (one per 128-row tile): refused on the host,
+    # nothing is launched and none of the (too small) buffers is touched
+    assert lib.rusty_cuda_qlinear_i8_forward_static(*args, 1, 262144 + 1, 64, C.c_void_p(ctx.stream())) == capi.ERR_INVALID_DIMENSIONS
+    assert b"N <= 262144" in lib.rusty_cuda_last_error(None)
     ctx.sync()
