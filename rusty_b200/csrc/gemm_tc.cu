@@ -11,11 +11,11 @@
 //     x[m,k] * s_m = d0 + d1/128 + d2/128^2 (+ d3/128^3),  |d0| <= 127, |d1..| <= 64,
 // by a small pre-pass; each digit plane is one column block of the B operand.
 // The integer dot products are exact, the digit planes are recombined in
-// double precision and multiplied by 1/s_m and scale[n] once, so the result is
+// 64-bit integers and multiplied by 1/s_m and scale[n] once, so the result is
 // the correctly rounded value of the dot product of the (digit-truncated)
-// activations: D=4 keeps 28 bits below the row maximum (f32 inputs lose
-// nothing that matters), D=3 keeps 21.  Results do not depend on how K is
-// split over CTAs: integer partial sums are order-independent.
+// activations: D=4 (f32 activations) keeps 28 bits below the row maximum, D=3
+// (bf16 activations) 21.  Results do not depend on how K is split over CTAs:
+// integer partial sums are order-independent.
 //
 // Data movement per CTA (persistent, one per SM, warp-specialised):
 //   warp 0  : TMA producer — 128x128-byte weight tiles (HBM, read once) and the
@@ -24,9 +24,10 @@
 //   warp 1  : allocates TMEM, issues tcgen05.mma (M=128, N=NB, K=32) from one
 //             elected lane, frees ring slots with tcgen05.commit;
 //   warps 2-5: epilogue — tcgen05.ld the int32 accumulators (double-buffered in
-//             TMEM), combine digits, scale, store y; or, when K is split over
-//             several CTAs, add partial sums into an int32 scratch with
-//             red.global and let the last CTA of a tile finalise.
+//             TMEM), fold the digits into int64 in a shared-memory staging tile,
+//             scale, store y; or, when K is split over several CTAs, add the
+//             staged piece into the tile's sum in L2 with one bulk reduce and
+//             convert an equal share of the rows once all pieces have arrived.
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the kernel
 // raises the context's timeout flag, drains and frees its TMEM.
 #include <cstdlib>
@@ -216,8 +217,6 @@ struct TcParams {
     int dp_tiles, sk_tiles, sk_per_cta, sk_ctas;
     int sk_ways;             // > 0: every shared tile is cut into this many near-equal pieces, one per CTA (CTA = tile * ways + piece)
     int ldy, y_col0;
-    int cluster_ways;        // > 0: the CTAs that hold the pieces of a tile form a thread-block cluster and sum them through
-                             // distributed shared memory (== sk_ways, every CTA holds exactly one piece)
     int act;                 // RUSTY_CUDA_ACT_SWIGLU_PAIRS: rows 2j, 2j+1 -> y[:, (y_col0 + 2j) / 2] = silu(gate) * up
     int stages;
     int red_bytes;           // epilogue staging area: a partial tile (Mpad x 128 x 8 bytes), at least 12 KiB
@@ -226,11 +225,6 @@ struct TcParams {
     rusty_cuda_dev_status* status;
     long long* dbg;          // optional per-CTA timeline (16 slots each), null in normal use
     PeerPush push;           // nranks > 1: every output is also stored into the other ranks' arenas
-    // Fused small-batch mode (M <= 4): no pre-pass and no digit planes in global memory.  The CTA finds the row
-    // maxima of x itself and its epilogue warps write the digit tile of every stage straight into shared memory.
-    int fused;               // 1: x_raw is used, Mpad == M, D == 4, NB == 16
-    int x_bf16;
-    const void* x_raw;       // [M, K] f32 or bf16
 };
 
 // One piece of work: k-blocks [kb0, kb1) of row tile t.  nseg > 1: the tile is
@@ -302,34 +296,6 @@ struct PeerOut {
     int n;                   // number of other ranks (0: no exchange)
     const long long* delta;  // [n] in shared memory
 };
-// Every lane of the warp must call this together (the pair epilogue exchanges values between neighbouring lanes);
-// `live` says whether this lane's output exists.  Lane parity equals the parity of n at every call site.
-template <typename YT>
-__device__ __forceinline__ void finalize_store_f(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, float row_factor,
-                                                 const PeerOut& po, bool live) {
-    float v = __ll2float_rn(acc) * row_factor * scale_n;
-    int col = p.y_col0 + n;
-    if (p.act) {
-        // rows 2j / 2j+1 are gate_j / up_j: the even lane takes its neighbour's value and writes silu(gate) * up
-        // (rusty-graph/src/lib.rs:317-323; silu as kernels.wgsl:104-113)
-        const float up = __shfl_down_sync(0xffffffffu, v, 1);
-        live = live && !(n & 1);
-        // ex2.approx-based exp and an approximate reciprocal: a few instructions instead of ~40, relative error ~1e-6
-        v = __fdividef(v, 1.0f + __expf(-v)) * up;
-        col >>= 1;
-    }
-    if (!live) return;
-    YT* dst = y + (size_t)m * p.ldy + col;
-    store_y<YT>(dst, v);
-    // exchange fused into the epilogue: the same element of every other rank's y, over NVLink
-    for (int g = 0; g < po.n; ++g) store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<char*>(dst) + po.delta[g]), v);
-}
-template <typename YT>
-__device__ __forceinline__ void finalize_store(const TcParams& p, YT* y, int n, int m, long long acc, float scale_n, const float* s_rowf,
-                                               const PeerOut& po, bool live) {
-    finalize_store_f<YT>(p, y, n, m, acc, scale_n, s_rowf[m], po, live);
-}
-
 // Four outputs at once: the four conversion chains (int64 -> f32, two multiplies, and for pairs a shuffle, exp and
 // reciprocal) are independent and written so that they overlap; one at a time they cost ~150 ns each in the single
 // warp per scheduler that runs them.  Output k is row m[k] of feature n[k]; live[k] says whether it exists.  Every lane
@@ -361,18 +327,6 @@ __device__ __forceinline__ void finalize_store4(const TcParams& p, YT* y, const 
     }
 }
 
-// Four consecutive activations x[m, k..k+3] as f32 (zeros beyond K); K % 4 == 0.
-__device__ __forceinline__ float4 load_x4(const TcParams& p, int m, int k) {
-    if (k >= p.K) return make_float4(0.f, 0.f, 0.f, 0.f);
-    if (p.x_bf16) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.x_raw) + (size_t)m * p.K + k);
-        return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
-                           __uint_as_float(raw.y & 0xffff0000u));
-    }
-    return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_raw) + (size_t)m * p.K + k);
-}
-
-
 template <typename YT>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -384,23 +338,15 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     uint8_t* sA = smem;
     uint8_t* sB = smem + (size_t)p.stages * A_STAGE_BYTES;
     // epilogue staging for the bulk reduce-add of a partial tile: [Mpad/2][128] x 16 bytes
-    // fused mode: sB is not a ring but ALL digit tiles of x (one per k-block), written once by the epilogue warps
-    int4* stage_red = reinterpret_cast<int4*>(sB + (size_t)(p.fused ? p.kb_total : p.stages) * b_stage_bytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (p.fused ? (size_t)0 : (size_t)p.red_bytes));
+    int4* stage_red = reinterpret_cast<int4*>(sB + (size_t)p.stages * b_stage_bytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (size_t)p.red_bytes);
     uint64_t* full = bars;                      // [stages]
     uint64_t* empty = bars + p.stages;          // [stages]
     uint64_t* acc_full = bars + 2 * p.stages;   // [2]
     uint64_t* acc_empty = acc_full + 2;         // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
-    float* s_red = reinterpret_cast<float*>(tmem_slot + 4);   // [16] row-maximum partials (fused mode)
-    float* s_scale = s_red + 16;                               // [4] s_m
-    float* s_factor = s_scale + 4;                             // [4] 1/s_m * 128^-3
-    uint64_t* dig_ready = reinterpret_cast<uint64_t*>(s_factor + 4);  // fused mode: the digit tiles of x are in place
-
     __shared__ float s_rowf[64];  // 1/s_m * 128^-(D-1) per activation row of this pass (at most 64 rows)
-    __shared__ __align__(8) uint64_t cl_bar[2];  // cluster mode: [0] every piece of the tile is staged, [1] every CTA has read them
     __shared__ long long s_peer_delta[PEER_MAX_RANKS];
     if (threadIdx.x == 0) {
         int k = 0;  // the other ranks, compacted (own rank left out); static indices into the parameter
@@ -422,13 +368,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             mbar_init(&acc_full[a], 1);
             mbar_init(&acc_empty[a], 4);
         }
-        mbar_init(dig_ready, 4);
-        if (p.cluster_ways > 0) {
-            mbar_init(&cl_bar[0], (uint32_t)p.cluster_ways);
-            mbar_init(&cl_bar[1], (uint32_t)p.cluster_ways);
-        }
         *abort_flag = 0;
-        *last_flag = 0;
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, p.tmem_cols);
@@ -436,7 +376,6 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (p.cluster_ways > 0) cluster_sync_all();  // nobody arrives on a neighbour's barrier before it is initialised
     if (threadIdx.x == 0) DBG(1);
 
     if (warp == 0) {
@@ -449,25 +388,12 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             bool ok = true;
             Sched sched(p);
             Segment sg;
-            if (p.fused) {
-                // weights only; they never depend on earlier kernels, so this role does not wait for them at all
-                while (ok && sched.next(sg)) {
-                    for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-                        if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
-                        mbar_expect_tx(&full[stage], (uint32_t)A_STAGE_BYTES);
-                        tma_load_2d(sA + (size_t)stage * A_STAGE_BYTES, &map_w, kb * BK, sg.t * BM, &full[stage], pol_w);
-                        ++issued;
-                        if (issued == 1) DBG(2);
-                        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-                    }
-                }
-            }
             // The weights do not depend on earlier kernels: start streaming them at once.  The digit planes do, so
             // the first ring-full of stages gets its weight tile now and its digit tile after pdl_wait().
             int early = 0;           // stages whose weight tile is already in flight
             int early_kb[8];
             bool waited = false;
-            while (!p.fused && ok && sched.next(sg)) {
+            while (ok && sched.next(sg)) {
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
                     if (!waited && early < p.stages) {
                         mbar_expect_tx(&full[early], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
@@ -493,7 +419,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (!waited && !p.fused) {  // fewer k-blocks than ring slots
+            if (!waited) {  // fewer k-blocks than ring slots
                 pdl_wait();
                 for (int e = 0; e < early; ++e)
                     tma_load_2d(sB + (size_t)e * b_stage_bytes, &map_x, early_kb[e] * BK, 0, &full[e], pol_x);
@@ -518,7 +444,6 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             bool ok = true;
             Sched sched(p);
             Segment sg;
-            if (p.fused && !mbar_wait(dig_ready, 0, abort_flag, p.status, 6)) ok = false;
             for (int i = 0; ok && sched.next(sg); ++i) {
                 const int ab = i & 1;
                 if (!mbar_wait(&acc_empty[ab], (((uint32_t)i >> 1) & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
@@ -529,7 +454,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     tc_fence_after();
                     if (kb == sg.kb0 && i == 0) DBG(4);
                     const uint64_t da = make_smem_desc(smem_u32(sA + (size_t)stage * A_STAGE_BYTES));
-                    const uint64_t db = make_smem_desc(smem_u32(sB + (size_t)(p.fused ? kb : stage) * b_stage_bytes));
+                    const uint64_t db = make_smem_desc(smem_u32(sB + (size_t)stage * b_stage_bytes));
 #pragma unroll
                     for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
                         // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
@@ -551,92 +476,10 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         pdl_wait();                             // x, y, the sums and the counters belong to earlier kernels until now
         bool ok = true;
         const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
-        if (!p.fused) {
-            // per-row factors of the pre-pass: once into shared memory (a load from global memory per output costs
-            // an L2 round trip each time)
-            if (et < p.Mpad) s_rowf[et] = __ldcg(p.row_factor + et);
-            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-        }
-        if (p.fused) {
-            // zero every digit tile once (rows that hold no digit plane stay zero for the whole kernel)
-            for (int i = et; i < p.kb_total * b_stage_bytes / 16; i += EPI_THREADS) reinterpret_cast<uint4*>(sB)[i] = make_uint4(0, 0, 0, 0);
-            // row maxima of x -> power-of-two scale per row (the same rule as the pre-pass kernel).  x is read in
-            // chunks of 4096 elements, 8 independent 16-byte loads per thread, so a chunk costs one L2 round trip.
-            float mx[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                if (m < p.M) {
-                    for (int c0 = 0; c0 < p.K; c0 += 4096) {
-                        float4 v[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = load_x4(p, m, c0 + (j * EPI_THREADS + et) * 4);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float a4[4] = {fabsf(v[j].x), fabsf(v[j].y), fabsf(v[j].z), fabsf(v[j].w)};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) mx[m] = (a4[e] <= 3.0e38f) ? fmaxf(mx[m], a4[e]) : __int_as_float(0x7f800000);
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xffffffffu, mx[m], off));
-                if (lane == 0) s_red[(warp - 2) * 4 + m] = mx[m];
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-            if (et < p.M) {
-                const float v = fmaxf(fmaxf(s_red[et], s_red[4 + et]), fmaxf(s_red[8 + et], s_red[12 + et]));
-                float sc = 1.0f;
-                if (v > 0.0f && v <= 3.0e38f) {
-                    int e;
-                    frexpf(v, &e);
-                    sc = ldexpf(1.0f, 7 - e);
-                    if (v * sc > 127.0f) sc *= 0.5f;
-                }
-                s_scale[et] = sc;
-                s_factor[et] = (v <= 3.0e38f) ? ldexpf(1.0f / sc, -21) : __int_as_float(0x7fc00000);
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-            // all digit tiles: elements k..k+3 of row m -> 4 packed bytes at (k % 128) of row d*M + m in tile k / 128
-            // (128-byte swizzle: 16-byte chunk index XOR row % 8)
-            for (int m = 0; m < p.M; ++m) {
-                const float sm = s_scale[m];
-                for (int c0 = 0; c0 < p.K; c0 += 4096) {
-                    float4 v[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = load_x4(p, m, c0 + (j * EPI_THREADS + et) * 4);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int k = c0 + (j * EPI_THREADS + et) * 4;
-                        if (k >= p.K) continue;
-                        const float xe[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-                        uint32_t packed[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float rr = xe[e] * sm;
-#pragma unroll
-                            for (int d = 0; d < 4; ++d) {
-                                const float qd = rintf(rr);
-                                packed[d] |= ((uint32_t)(int)qd & 0xFFu) << (8 * e);
-                                rr = (rr - qd) * 128.0f;
-                            }
-                        }
-                        uint8_t* tile = sB + (size_t)(k / BK) * b_stage_bytes;
-                        const int kk = k % BK;
-#pragma unroll
-                        for (int d = 0; d < 4; ++d) {
-                            const int row = d * p.M + m;
-                            *reinterpret_cast<uint32_t*>(tile + row * BK + ((((kk >> 4) ^ (row & 7)) << 4) | (kk & 15))) = packed[d];
-                        }
-                    }
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(dig_ready);
-        }
+        // per-row factors of the pre-pass: once into shared memory (a load from global memory per output costs
+        // an L2 round trip each time)
+        if (et < p.Mpad) s_rowf[et] = __ldcg(p.row_factor + et);
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         int cut_t[2], cut_j[2], cut_n[2], n_cut = 0;  // shared tiles this CTA added a piece to
         bool announced = false;
         Sched sched(p);
@@ -741,63 +584,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             tc_fence_after();
             if (threadIdx.x == 64) DBG(6 + 4 * (i & 1));
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * p.NB);
-            if (p.fused) {
-                uint32_t c[16];
-                tmem_ld16(taddr, c);
-                tmem_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[ab]);
-                long long acc[4];
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    acc[m] = 0;
-                    if (m < p.M) {
-#pragma unroll
-                        for (int d = 0; d < 4; ++d) {
-                            int32_t v = 0;
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (j == d * p.M + m) v = (int32_t)c[j];
-                            acc[m] = acc[m] * 128 + v;
-                        }
-                    }
-                }
-                const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
-                if (sg.nseg == 1) {
-                    if (row_ok)
-                        for (int m = 0; m < p.M; ++m) finalize_store_f<YT>(p, y, n, m, acc[m], sc, s_factor[m], po, true);
-                } else {
-                    // a piece of a K-cut tile: 64-bit integer reductions straight from registers (exact, any order)
-                    const int lt = sg.t - p.dp_tiles;
-                    unsigned long long* tile_sum = reinterpret_cast<unsigned long long*>(p.part) + (size_t)lt * 4 * BM;
-                    if (row_ok)
-                        for (int m = 0; m < p.M; ++m) atomicAdd(tile_sum + (size_t)m * BM + r, (unsigned long long)acc[m]);
-                    __threadfence();
-                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-                    if (threadIdx.x == 64) {
-                        unsigned prev = atomicAdd(p.counters + sg.t, 1u);
-                        *reinterpret_cast<volatile int*>(last_flag) = (prev == (unsigned)(sg.nseg - 1)) ? 1 : 0;
-                    }
-                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-                    if (*reinterpret_cast<volatile int*>(last_flag) != 0) {
-                        __threadfence();
-                        if (row_ok) {
-                            long long tot[4];
-#pragma unroll
-                            for (int m = 0; m < 4; ++m) tot[m] = m < p.M ? (long long)__ldcg(tile_sum + (size_t)m * BM + r) : 0;
-#pragma unroll
-                            for (int m = 0; m < 4; ++m)
-                                if (m < p.M) {
-                                    __stcg(tile_sum + (size_t)m * BM + r, 0ull);
-                                    finalize_store_f<YT>(p, y, n, m, tot[m], sc, s_factor[m], po, true);
-                                }
-                        }
-                        if (threadIdx.x == 64) p.counters[sg.t] = 0u;
-                    }
-                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-                }
-            } else {
+            {
                 // Fold the digit planes into one exact 64-bit integer per output and stage them in shared memory
                 // ([m/2][row] x 16 bytes).  A whole tile is converted from there in a rolled loop (unrolled register
                 // code that runs once per tile costs an instruction fetch per line and was twice as slow); a piece of
@@ -844,73 +631,6 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         const bool l4[4] = {row_ok, row_ok && m + 1 < p.M, row_ok && m + 2 < p.M, row_ok && m + 3 < p.M};
                         finalize_store4<YT>(p, y, n4, m4, a4, s4, s_rowf, po, l4);
                     }
-                    if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
-                    continue;
-                }
-                if (p.cluster_ways > 0) {
-                    // The pieces of this tile sit in the staging tiles of the cluster's CTAs.  Tell everybody that this
-                    // one is staged, wait for all, then sum an equal share of the rows straight out of the
-                    // neighbours' shared memory and convert it: no global partial sums, no counters.
-                    const int ways = p.cluster_ways;
-                    const uint32_t my = cluster_ctarank();
-                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-                    if (threadIdx.x == 64) {
-                        fence_acq_rel_cluster();
-                        for (int c = 0; c < ways; ++c) mbar_arrive_cluster(mapa_u32(smem_u32(&cl_bar[0]), (uint32_t)c));
-                    }
-                    if (!mbar_wait(&cl_bar[0], 0u, abort_flag, p.status, 9)) { ok = false; }
-                    fence_acq_rel_cluster();
-                    if (threadIdx.x == 64) DBG(8 + 4 * (i & 1));
-                    if (ok) {
-                        const int lo = 2 * ((int)my * (BM / 2) / ways), rows = 2 * (((int)my + 1) * (BM / 2) / ways) - lo;
-                        const int items = rows * (p.Mpad / 2);
-                        const uint32_t stage_addr = smem_u32(stage_red);
-                        if (rows > 0) {
-                            int row = et % rows, mp = et / rows;
-                            const int step_row = EPI_THREADS % rows, step_mp = EPI_THREADS / rows;
-#pragma unroll 1
-                            for (int base = 0; base < items; base += 2 * EPI_THREADS) {  // two items = four outputs per trip
-                                long long a4[4] = {0, 0, 0, 0};
-                                int n4[4], m4[4];
-                                float s4[4];
-                                bool l4[4];
-#pragma unroll
-                                for (int u = 0; u < 2; ++u) {
-                                    const bool in = base + u * EPI_THREADS + et < items;
-                                    const int rw = lo + row, nn = sg.t * BM + rw;
-                                    const uint32_t off = stage_addr + (uint32_t)((mp * BM + rw) * 16);
-                                    if (in) {
-                                        for (int c = 0; c < ways; ++c) {
-                                            const int4 v = ld_dsmem_v4(mapa_u32(off, (uint32_t)c));
-                                            a4[2 * u] += ((long long)v.y << 32) | (unsigned int)v.x;
-                                            a4[2 * u + 1] += ((long long)v.w << 32) | (unsigned int)v.z;
-                                        }
-                                    }
-                                    const bool live = in && nn < p.N;
-                                    n4[2 * u] = n4[2 * u + 1] = nn;
-                                    m4[2 * u] = live ? 2 * mp : 0;
-                                    m4[2 * u + 1] = m4[2 * u] + 1;
-                                    s4[2 * u] = s4[2 * u + 1] = live ? __ldg(p.scales + nn) : 0.0f;
-                                    l4[2 * u] = live && 2 * mp < p.M;
-                                    l4[2 * u + 1] = live && 2 * mp + 1 < p.M;
-                                    row += step_row;
-                                    mp += step_mp;
-                                    if (row >= rows) {
-                                        row -= rows;
-                                        ++mp;
-                                    }
-                                }
-                                finalize_store4<YT>(p, y, n4, m4, a4, s4, s_rowf, po, l4);
-                            }
-                        }
-                    }
-                    // nobody's staging tile may go away (CTA exit) or be reused while a neighbour still reads it
-                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-                    if (threadIdx.x == 64) {
-                        fence_acq_rel_cluster();
-                        for (int c = 0; c < ways; ++c) mbar_arrive_cluster(mapa_u32(smem_u32(&cl_bar[1]), (uint32_t)c));
-                    }
-                    if (!mbar_wait(&cl_bar[1], 0u, abort_flag, p.status, 10)) ok = false;
                     if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
                     continue;
                 }
@@ -988,7 +708,7 @@ constexpr size_t WS_GUARD_AT[5] = {WS_OFF_INVS - WS_GUARD, WS_OFF_ACC - WS_GUARD
 struct TcSchedule {
     int grid, dp_tiles, sk_tiles, sk_per_cta, sk_ctas, sk_ways;
 };
-bool plan_tc_schedule(int tiles, int kb_total, int sm_count, bool fused, int dp_percent, size_t sums_tiles_cap, size_t counter_cap,
+bool plan_tc_schedule(int tiles, int kb_total, int sm_count, int dp_percent, size_t sums_tiles_cap, size_t counter_cap,
                       TcSchedule* out) {
     if ((size_t)tiles > counter_cap) return false;
     TcSchedule s{};
@@ -1004,7 +724,7 @@ bool plan_tc_schedule(int tiles, int kb_total, int sm_count, bool fused, int dp_
     {
         const int r = (tiles + sm_count - 1) / sm_count;   // tiles per CTA
         const int g_dp = r > 0 ? (tiles + r - 1) / r : 0;  // CTAs that then have work
-        if (!fused && s.sk_tiles > 0 && g_dp * 100 >= sm_count * dp_percent) {
+        if (s.sk_tiles > 0 && g_dp * 100 >= sm_count * dp_percent) {
             grid = g_dp;
             s.sk_tiles = 0;
             s.dp_tiles = tiles;
@@ -1121,7 +841,7 @@ uint32_t tc_min_rows() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("RUSTY_TC_MIN_ROWS");
-        v = e ? atoi(e) : 5;
+        v = e ? atoi(e) : 3;
         if (v < 1) v = 1;
     }
     return (uint32_t)v;
@@ -1136,22 +856,19 @@ bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a) {
 }
 
 // The kernel pair below stores into the peers' arenas itself, except in the small-batch mode that has no pre-pass.
-bool tc_pushes_fused(uint32_t M) { return M > 4; }
+bool tc_pushes_fused(uint32_t M) { return M >= tc_min_rows(); }
 
 // One launch pair (digitise + GEMM) for up to 64 activation rows.
 static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void* x, void* y, uint32_t rows) {
-    // Small batches whose activations a CTA can scan by itself (<= 64 KiB) skip the pre-pass kernel.
-    static const bool no_fuse = getenv("RUSTY_TC_NO_FUSED_X") != nullptr;
-    const bool fused = !no_fuse && rows <= 4 && (size_t)rows * a.K <= 16384;
-    const int M = (int)rows, Mpad = fused ? M : (M + 7) / 8 * 8;
-    const int D = fused ? 4 : pick_digits(a.x_dtype, rows);
-    const int NB = (fused && D * Mpad <= 8) ? 8 : (D * Mpad + 15) / 16 * 16;
+    const int M = (int)rows, Mpad = (M + 7) / 8 * 8;
+    const int D = pick_digits(a.x_dtype, rows);
+    const int NB = (D * Mpad + 15) / 16 * 16;
     uint8_t* ws = (uint8_t*)ctx->tc_ws;
     int8_t* xq = (int8_t*)ws;
     float* inv_s = (float*)(ws + WS_OFF_INVS);
     int32_t* acc = (int32_t*)(ws + WS_OFF_ACC);
     // two sets of arrival counters: one kept at zero by its users, one cleared by the pre-pass of this path
-    unsigned int* counters = (unsigned int*)(ws + (fused ? WS_OFF_CNT : WS_OFF_CNT2));
+    unsigned int* counters = (unsigned int*)(ws + WS_OFF_CNT2);   // this set is cleared by the pre-pass
     if ((size_t)D * Mpad * a.K > WS_XQ_BYTES)
         return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: %d digit rows x K=%u exceed the workspace", D * Mpad, a.K);
 
@@ -1168,10 +885,9 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     }
     PeerPush push{};
     if (a.push && a.push->nranks > 1) {
-        if (fused) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "tensor-core path: the small-batch mode does not push to peers");
         push = *a.push;
     }
-    if (!fused) {
+    {
         le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr, counters, n_tiles)
                                           : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr, counters, n_tiles);
         if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
@@ -1196,7 +912,7 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     // RUSTY_TC_DP_PERCENT: least share of the SMs that whole tiles must keep streaming (default 72; 101 turns the rule off).
     static const int dp_percent = getenv("RUSTY_TC_DP_PERCENT") ? atoi(getenv("RUSTY_TC_DP_PERCENT")) : 72;
     TcSchedule sc{};
-    if (!plan_tc_schedule(p.tiles, p.kb_total, ctx->sm_count, fused, dp_percent, WS_ACC_BYTES / ((size_t)(fused ? 4 : Mpad) * BM * 8),
+    if (!plan_tc_schedule(p.tiles, p.kb_total, ctx->sm_count, dp_percent, WS_ACC_BYTES / ((size_t)Mpad * BM * 8),
                           WS_CNT_BYTES / 4, &sc))
         return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: N=%u has more row tiles than arrival counters", a.N);
     int grid = sc.grid;
@@ -1211,9 +927,6 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.status = ctx->status_dev;
     p.dbg = dbg;
     p.push = push;
-    p.fused = fused ? 1 : 0;
-    p.x_bf16 = a.x_dtype == RUSTY_CUDA_BF16 ? 1 : 0;
-    p.x_raw = x;
     // int8 x int8 -> int32, both K-major: c_format=S32(2)@4, a_format=INT8(1)@7, b_format=INT8(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     uint32_t cols = 32;
@@ -1224,24 +937,22 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     // prefetch its weights while this one drains (RUSTY_TC_FULL_SMEM=1: take it all, 8 stages).
     static const bool full_smem = getenv("RUSTY_TC_FULL_SMEM") != nullptr;
     size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
-    // fused mode keeps every digit tile of x resident instead of a ring of them
-    const size_t dig_bytes = fused ? (size_t)p.kb_total * b_stage : 0;
-    if (!full_smem && NB <= 32 && dig_bytes + 4 * A_STAGE_BYTES + 4096 <= budget / 2)
+    if (!full_smem && NB <= 32 && 4 * A_STAGE_BYTES + 4096 <= budget / 2)
         budget = budget / 2 - 1024;  // narrow batches: leave room for the next kernel's CTA on the SM
     // epilogue staging of a partial tile; the shared finalize parks 4 x 128 sums, scales and positions there (12 KiB)
-    const size_t red_bytes = fused ? dig_bytes : ((size_t)Mpad * 8 * BM > 12288 ? (size_t)Mpad * 8 * BM : (size_t)12288);
+    const size_t red_bytes = (size_t)Mpad * 8 * BM > 12288 ? (size_t)Mpad * 8 * BM : (size_t)12288;
     int stages = budget > red_bytes + 2048
-                     ? (int)((budget - 1024 - 512 - red_bytes) / (size_t)(A_STAGE_BYTES + (fused ? 0 : b_stage)))
+                     ? (int)((budget - 1024 - 512 - red_bytes) / (size_t)(A_STAGE_BYTES + b_stage))
                      : 0;
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: tile does not fit shared memory");
     p.stages = stages;
     p.red_bytes = (int)red_bytes;
-    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + (fused ? 0 : b_stage)) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
+    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
 
     CUtensorMap map_w, map_x;
     if (!make_map_u8(&map_w, a.w, a.N, a.K, BM) ||
-        !make_map_u8(&map_x, xq, (uint64_t)D * (fused ? 8 : Mpad), a.K, (uint32_t)NB))
+        !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, a.K, (uint32_t)NB))
         return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "tensor-core path: cuTensorMapEncodeTiled failed");
 
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
@@ -1250,30 +961,6 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     {
         cudaError_t e = ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_i8_tc: cudaFuncSetAttribute");
-    }
-    // Pieces of one tile held by consecutive CTAs: launch them as a thread-block cluster and sum through distributed
-    // shared memory, when every cluster can be resident at once (one wave).  Opt-in: RUSTY_TC_CLUSTER=1.
-    static const bool want_cluster = getenv("RUSTY_TC_CLUSTER") && atoi(getenv("RUSTY_TC_CLUSTER")) == 1;
-    if (want_cluster && !fused && p.sk_ways >= 2 && p.sk_ways <= 8 && p.dp_tiles == 0 && grid == p.sk_tiles * p.sk_ways) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(TC_THREADS);
-        cfg.dynamicSmemBytes = smem;
-        cudaLaunchAttribute cattr[1];
-        cattr[0].id = cudaLaunchAttributeClusterDimension;
-        cattr[0].val.clusterDim.x = (unsigned)p.sk_ways;
-        cattr[0].val.clusterDim.y = 1;
-        cattr[0].val.clusterDim.z = 1;
-        cfg.attrs = cattr;
-        cfg.numAttrs = 1;
-        int max_clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters >= grid / p.sk_ways) {
-            p.cluster_ways = p.sk_ways;
-            le = launch_pdl_cluster(kern, dim3(grid), dim3(TC_THREADS), smem, ctx->stream, (unsigned)p.sk_ways, map_w, map_x, p);
-            if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_i8_tc (cluster)");
-            return after_launch(ctx, "qlinear_i8_tc");
-        }
-        cudaGetLastError();
     }
     le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, ctx->stream, map_w, map_x, p);
     if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_i8_tc");
@@ -1420,7 +1107,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     p.kb_total = (p.K + BK - 1) / BK;
     // the same schedule rules as the regular entry points, with this scratch's capacities
     TcSchedule sc{};
-    if (!plan_tc_schedule(p.tiles, p.kb_total, sd.sm_count < STATIC_MAX_CTAS ? sd.sm_count : STATIC_MAX_CTAS, /*fused=*/false,
+    if (!plan_tc_schedule(p.tiles, p.kb_total, sd.sm_count < STATIC_MAX_CTAS ? sd.sm_count : STATIC_MAX_CTAS,
                           /*dp_percent=*/72, ST_SUMS_TILES, ST_CNT_BYTES / 4, &sc))
         return fail(nullptr, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_i8_forward_static: N=%u has more row tiles than arrival counters", N);
     const int grid = sc.grid;

@@ -158,9 +158,9 @@ struct QLinearArgs {
 bool gemv_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 int launch_gemv(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 
-// One or two activation rows, weights staged by bulk copies (gemv_tma.cu).
-bool gemv_tma_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
-int launch_gemv_tma(rusty_cuda_ctx* ctx, const QLinearArgs& a);
+// One or two activation rows on the warp-level integer tensor-core path, weights staged by TMA (gemv_mma.cu).
+bool gemv_mma_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
+int launch_gemv_mma(rusty_cuda_ctx* ctx, const QLinearArgs& a);
 
 // Tensor-core (tcgen05 / TMEM) path.
 bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);

@@ -45,7 +45,7 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
     // the bf16 prefill kernels have no activation epilogue: batches of pairs go through the int8 kernel in 64-row passes
     if (!a.act && f16tc_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16";
     if (tc_supported(ql->ctx, a) && M >= tc_min_rows() && (!a.act || tc_pushes_fused(M))) return "tcgen05";
-    if (gemv_tma_supported(ql->ctx, a)) return "gemv_tma";
+    if (gemv_mma_supported(ql->ctx, a)) return "gemv_mma";
     if (gemv_supported(ql->ctx, a)) return "gemv";
     return "unsupported";
 }
@@ -99,7 +99,7 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
     DeviceGuard g(ctx->device);
     if (!a.act && f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
     if (tc_supported(ctx, a) && M >= tc_min_rows() && (!a.act || tc_pushes_fused(M))) return launch_tc(ctx, a);
-    if (gemv_tma_supported(ctx, a)) return launch_gemv_tma(ctx, a);
+    if (gemv_mma_supported(ctx, a)) return launch_gemv_mma(ctx, a);
     if (gemv_supported(ctx, a)) return launch_gemv(ctx, a);
     return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED,
                 "qlinear_forward: no kernel for N=%u K=%u layout=%d (K %% 16 == 0 for [N,K], N %% 16 == 0 for [K,N])", ql->N,

@@ -31,6 +31,19 @@ bool make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, 
     return r == CUDA_SUCCESS;
 }
 
+bool make_map_u8_rows_by_kblocks(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows, uint32_t box_kblocks) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || K % 128 != 0) return false;
+    cuuint64_t dims[3] = {128, rows, K / 128};
+    cuuint64_t strides[2] = {K, 128};
+    cuuint32_t box[3] = {128u, box_rows, box_kblocks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;

@@ -47,7 +47,7 @@ def _reference(oracle, x, gq, gs, uq, us):
 def test_fused_pairs_match_two_linears_silu_mul(ctx, engine, oracle, M, K, F):
     x, gq, gs, uq, us = _pairs_case(M * 7 + F, M, K, F)
     ql = QLinear.from_gate_up(ctx, gq, gs, uq, us)
-    assert ql.out_features == F and ql.plan(M) in ("gemv", "gemv_tma", "tcgen05")
+    assert ql.out_features == F and ql.plan(M) in ("gemv", "gemv_mma", "tcgen05")
     xt = UnifiedTensor.new(ctx, x, [M, K])
     y = UnifiedTensor.new(ctx, np.full(M * F, np.nan, np.float32), [M, F])
     engine.qlinear(ctx, xt, ql, y)
