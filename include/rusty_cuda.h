@@ -214,9 +214,9 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t 
  * a real-time loop whose device memory was carved up front, or a process whose own allocator owns the whole
  * device.  Raw device pointers in, nothing allocated or freed, no context needed:
  *     y[M,N] (f32) = x[M,K] (f32) . (w[N,K] (int8, row-major) * scales[N])^T      on `stream` (a cudaStream_t).
- * The kernel's scratch is a fixed ~1.5 MiB array that lives inside the library on every GPU that loads it,
- * which caps the shapes: M <= 8 rows, K <= 8192 (K % 16 == 0, w 16-byte aligned) and N <= 262144 (one arrival
- * counter per 128-row tile); larger calls are rejected with RUSTY_CUDA_ERR_INVALID_DIMENSIONS before anything is
+ * The kernel's scratch is a fixed ~2.8 MiB array that lives inside the library on every GPU that loads it,
+ * which caps the shapes: M <= 8 rows, K <= 8192 (K % 16 == 0, w 16-byte aligned) and N <= 262144;
+ * larger calls are rejected with RUSTY_CUDA_ERR_INVALID_DIMENSIONS before anything is
  * launched.  The current device must be the one the pointers belong to.  The first call on each device looks the
  * array's address up; make that call before any stream capture.
  * All calls share the one array: it is cleared where the kernel needs zeros, it otherwise keeps the previous

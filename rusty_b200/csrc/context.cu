@@ -187,6 +187,7 @@ int rusty_cuda_sync(rusty_cuda_ctx* ctx) {
         unsigned where = ctx->status_host->timeout_where;
         ctx->status_host->timeout_flag = 0;
         ctx->status_host->timeout_where = 0;
+        tc_workspace_clear_pieces(ctx);   // a kernel that gave up may have left pieces of K-cut tiles behind
         return fail(ctx, RUSTY_CUDA_ERR_TIMEOUT, "a bounded device-side wait gave up (site %u)", where);
     }
     return RUSTY_CUDA_OK;

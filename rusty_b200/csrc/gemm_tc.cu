@@ -51,9 +51,8 @@ namespace {
 constexpr int BM = 128;            // weight rows per tile = UMMA M
 constexpr int BK = 128;            // k-elements (bytes) per pipeline stage
 constexpr int UMMA_K = 32;         // k-elements per tcgen05.mma kind::i8
-constexpr int TC_THREADS = 192;    // producer warp, MMA warp, 4 epilogue warps
-constexpr int EPI_THREADS = 128;
-constexpr int A_STAGE_BYTES = BM * BK;
+constexpr int TC_MAX_THREADS = 384;  // producer warp, MMA warp, 4 or 8 epilogue warps (<= 320 threads; 384 caps the registers at 168)
+constexpr int A_TILE_BYTES = BM * BK;   // one 128-row weight tile of a stage; a stage holds tpu of them
 
 template <typename T>
 __device__ __forceinline__ void store_y(T* p, float v);
@@ -67,13 +66,6 @@ __device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16* p, float v
 // xq is [D*Mpad, K] int8, row d*Mpad + m; inv_s[m] = 1 / (s_m * 128^(D-1)).  One block per m
 // (rows M..Mpad-1 are written as zeros).
 // ----------------------------------------------------------------------------
-template <typename XT>
-__device__ __forceinline__ float x_to_f32(XT v);
-template <>
-__device__ __forceinline__ float x_to_f32<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ float x_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-
 // Four consecutive activations as f32 (p is 16-byte aligned for f32, 8-byte aligned for bf16: K % 16 == 0).
 template <typename XT>
 __device__ __forceinline__ float4 load_row4(const XT* p);
@@ -86,116 +78,99 @@ __device__ __forceinline__ float4 load_row4<__nv_bfloat16>(const __nv_bfloat16* 
                        __uint_as_float(raw.y & 0xffff0000u));
 }
 
-constexpr int DIG_THREADS = 1024;  // one block per activation row; a 4096-wide row is one 16-byte load per thread
+constexpr int DIG_THREADS = 512;
+constexpr int DIG_MAX_BLOCKS = 32;
+constexpr int DIG_MAXV = 8;   // passes of a row held in registers between the maximum and the digits
 
+// A few fat blocks on purpose: grid = min(32, Mpad) blocks of 512 threads, R = Mpad / grid activation rows per block
+// (1 or 2), 512 / R threads per row (its own named barrier).  The kernel is launched early (programmatic dependent
+// launch) and parks in griddepcontrol.wait while the GEMM before it still runs; many small parked blocks pile up on the
+// few SMs that GEMM left free and keep the next GEMM's CTAs from being placed there.  Thirty-two blocks of at most 64
+// registers a thread fit beside a GEMM CTA on any SM and cannot fill more than eight.  Rows M..Mpad-1 are written as
+// zeros.  A row of up to 16384 activations (one row per block) stays in registers between its maximum and its digits:
+// one round trip to memory, all loads in flight together.
 template <typename XT, int D>
-__global__ void __launch_bounds__(DIG_THREADS) digitize_x_kernel(const XT* __restrict__ x, int8_t* __restrict__ xq,
-                                                                 float* __restrict__ inv_s, int M, int Mpad, int K,
-                                                                 const PeerPush push, long long* dbg,
-                                                                 unsigned int* __restrict__ counters, int n_counters) {
-    const int m = blockIdx.x;
+__global__ void __launch_bounds__(DIG_THREADS, 2) digitize_x_kernel(const XT* __restrict__ x, int8_t* __restrict__ xq,
+                                                                    float* __restrict__ inv_s, int M, int Mpad, int K, int R,
+                                                                    const PeerPush push, long long* dbg) {
     __shared__ float red[DIG_THREADS / 32];
-    __shared__ float s_scale;
     const int tid = threadIdx.x;
-    PDBG(tid == 0 && m == 0, 0);
+    const int tpr = DIG_THREADS / R;               // threads per row (512 or 256)
+    const int grp = tid / tpr, tg = tid - grp * tpr;
+    const int m = blockIdx.x * R + grp;
+    PDBG(tid == 0 && blockIdx.x == 0, 0);
     pdl_launch_dependents();
     pdl_wait();  // x may come from the previous kernel, and that kernel may still be reading the digit planes
-    PDBG(tid == 0 && m == 0, 1);
-    // arrival counters of the GEMM's shared tiles: the kernel before has finished with them, the GEMM after this
-    // kernel counts from zero
-    for (int i = m * DIG_THREADS + tid; i < n_counters; i += gridDim.x * DIG_THREADS) counters[i] = 0u;
+    PDBG(tid == 0 && blockIdx.x == 0, 1);
     if (push.nranks > 1) {
         // x may hold columns pushed by the other ranks, and the GEMM that follows overwrites their copies of y:
         // wait until every rank has finished (and delivered) all earlier pushes
         if (tid == 0) peer_wait_all(push, 30);
         __syncthreads();
-        PDBG(tid == 0 && m == 0, 3);
+        PDBG(tid == 0 && blockIdx.x == 0, 3);
     }
+    const int step = tpr * 4;                       // activations one pass of the row's threads covers
     if (m >= M) {
-        for (int k = tid * 4; k < K; k += DIG_THREADS * 4)
+        for (int k = tg * 4; k < K; k += step)
 #pragma unroll
             for (int d = 0; d < D; ++d) *reinterpret_cast<uint32_t*>(xq + (size_t)(d * Mpad + m) * K + k) = 0u;
-        return;
+        return;   // whole row groups leave together: the named barrier below is per group
     }
     const XT* xr = x + (size_t)m * K;
-    // Rows of up to 16384 elements stay in registers between the maximum and the digits (one trip to memory).
-    constexpr int MAXV = 4;
-    const bool in_regs = K <= DIG_THREADS * 4 * MAXV;
-    float4 v[MAXV];
-    float mx = 0.0f;
-    if (in_regs) {
+    float4 v[DIG_MAXV];
 #pragma unroll
-        for (int j = 0; j < MAXV; ++j) {
-            const int k = (j * DIG_THREADS + tid) * 4;
-            v[j] = k < K ? load_row4<XT>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int j = 0; j < MAXV; ++j) {
-            const float a4[4] = {fabsf(v[j].x), fabsf(v[j].y), fabsf(v[j].z), fabsf(v[j].w)};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) mx = (a4[e] <= 3.0e38f) ? fmaxf(mx, a4[e]) : __int_as_float(0x7f800000);
-        }
-    } else {
-        for (int k = tid; k < K; k += DIG_THREADS) {
-            float a = fabsf(x_to_f32<XT>(xr[k]));
-            mx = (a <= 3.0e38f) ? fmaxf(mx, a) : __int_as_float(0x7f800000);  // NaN or inf anywhere poisons the row
-        }
+    for (int j = 0; j < DIG_MAXV; ++j) {
+        const int k = tg * 4 + j * step;
+        v[j] = k < K ? load_row4<XT>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    float mx = 0.0f;
+    auto fold = [&](const float4& f) {
+        const float a4[4] = {fabsf(f.x), fabsf(f.y), fabsf(f.z), fabsf(f.w)};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx = (a4[e] <= 3.0e38f) ? fmaxf(mx, a4[e]) : __int_as_float(0x7f800000);  // NaN or inf anywhere poisons the row
+    };
+#pragma unroll
+    for (int j = 0; j < DIG_MAXV; ++j) fold(v[j]);
+    for (int k = tg * 4 + DIG_MAXV * step; k < K; k += step) fold(load_row4<XT>(xr + k));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     if ((tid & 31) == 0) red[tid >> 5] = mx;
-    __syncthreads();
-    if (tid < 32) {
-        float vmax = red[tid];
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(tpr) : "memory");   // the row's threads only
+    const int wpr = tpr / 32;                       // warps per row: 16 or 8
+    float vmax = red[grp * wpr + (tid & (wpr - 1))];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
-        if (tid == 0) {
-            // s = the power of two that puts vmax*s into [64, 128) but not above 127
-            float s = 1.0f;
-            if (vmax >= 1.0e-30f && vmax <= 3.0e38f) {
-                const int e = (int)((__float_as_uint(vmax) >> 23) & 0xffu) - 126;  // vmax = f * 2^e, f in [0.5, 1)
-                s = __uint_as_float((uint32_t)(127 + 7 - e) << 23);                 // 2^(7-e): 7-e in [-121, 106]
-                if (vmax * s > 127.0f) s *= 0.5f;
-            } else if (vmax > 0.0f && vmax <= 3.0e38f) {
-                int e;
-                frexpf(vmax, &e);
-                s = ldexpf(1.0f, 7 - e > 120 ? 120 : 7 - e);  // tiny rows: any power of two that keeps |x*s| <= 127 will do
-            }
-            s_scale = s;
-            // 1/s_m * 128^-(D-1): both powers of two, so the product is exact
-            inv_s[m] = (vmax <= 3.0e38f) ? ldexpf(1.0f / s, -7 * (D - 1)) : __int_as_float(0x7fc00000);  // inf/nan poisons the row
-        }
+    for (int off = 8; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+    // s = the power of two that puts vmax*s into [64, 128) but not above 127
+    int e2 = 0;
+    if (vmax >= 1.0e-30f && vmax <= 3.0e38f) {
+        const int e = (int)((__float_as_uint(vmax) >> 23) & 0xffu) - 126;  // vmax = f * 2^e, f in [0.5, 1)
+        e2 = 7 - e;
+        if (vmax * __uint_as_float((uint32_t)(127 + e2) << 23) > 127.0f) --e2;
+    } else if (vmax > 0.0f && vmax <= 3.0e38f) {
+        int e;
+        frexpf(vmax, &e);
+        e2 = 7 - e > 120 ? 120 : 7 - e;  // tiny rows: any power of two that keeps |x*s| <= 127 will do
     }
-    __syncthreads();
-    const float s = s_scale;
-    auto emit = [&](int k, const float4& f) {
-        const float in4[4] = {f.x, f.y, f.z, f.w};
-        uint32_t packed[D];
+    const bool finite = vmax <= 3.0e38f;
+    const float sc = finite ? __uint_as_float((uint32_t)(127 + e2) << 23) : 0.0f;
+    // 1/s_m * 128^-(D-1): both powers of two, so the product is exact; inf/nan poisons the row
+    if (tg == 0) inv_s[m] = finite ? ldexpf(1.0f, -e2 - 7 * (D - 1)) : __int_as_float(0x7fc00000);
+    for (int k = tg * 4, i = 0; k < K; k += step, ++i) {   // one copy of the conversion code, in a loop
+        float4 f = v[0];
 #pragma unroll
-        for (int d = 0; d < D; ++d) packed[d] = 0u;
+        for (int j = 1; j < DIG_MAXV; ++j)
+            if (i == j) f = v[j];
+        if (i >= DIG_MAXV) f = load_row4<XT>(xr + k);
+        const uint32_t w0 = digits_of<D>(f.x * sc), w1 = digits_of<D>(f.y * sc), w2 = digits_of<D>(f.z * sc), w3 = digits_of<D>(f.w * sc);
+        // 4 elements x 4 digit bytes -> digit planes x 4 element bytes; byte b = digit b from the least significant,
+        // byte D-1 = the top digit = plane 0
+        const uint32_t t0 = __byte_perm(w0, w1, 0x5140), t1 = __byte_perm(w2, w3, 0x5140);
+        const uint32_t t2 = __byte_perm(w0, w1, 0x7362), t3 = __byte_perm(w2, w3, 0x7362);
+        const uint32_t by[4] = {__byte_perm(t0, t1, 0x5410), __byte_perm(t0, t1, 0x7632), __byte_perm(t2, t3, 0x5410), __byte_perm(t2, t3, 0x7632)};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float r = in4[e] * s;  // exact: s is a power of two
-#pragma unroll
-            for (int d = 0; d < D; ++d) {
-                float q = rintf(r);
-                packed[d] |= ((uint32_t)(int)q & 0xFFu) << (8 * e);
-                r = (r - q) * 128.0f;  // exact
-            }
-        }
-#pragma unroll
-        for (int d = 0; d < D; ++d) *reinterpret_cast<uint32_t*>(xq + (size_t)(d * Mpad + m) * K + k) = packed[d];
-    };
-    if (in_regs) {
-#pragma unroll
-        for (int j = 0; j < MAXV; ++j) {
-            const int k = (j * DIG_THREADS + tid) * 4;
-            if (k < K) emit(k, v[j]);
-        }
-    } else {
-        for (int k = tid * 4; k < K; k += DIG_THREADS * 4) emit(k, load_row4<XT>(xr + k));  // K % 4 == 0 (K % 16 == 0 is required by the caller)
+        for (int d = 0; d < D; ++d) *reinterpret_cast<uint32_t*>(xq + (size_t)(d * Mpad + m) * K + k) = by[D - 1 - d];
     }
-    PDBG(tid == 0 && m == 0, 2);
+    PDBG(tid == 0 && blockIdx.x == 0, 2);
 }
 
 // ----------------------------------------------------------------------------
@@ -204,12 +179,13 @@ __global__ void __launch_bounds__(DIG_THREADS) digitize_x_kernel(const XT* __res
 struct TcParams {
     const float* scales;     // [N]
     const float* row_factor; // [Mpad]: 1/s_m * 128^-(D-1)
-    int32_t* part;           // sums of tiles cut across CTAs: [sk_tiles][Mpad/2][128] x 16 bytes (two int64), zero between uses
-    unsigned int* counters;  // [tiles] arrivals per cut tile (zero between uses)
+    ulonglong2* part;        // pieces of tiles cut across CTAs: slot (2*cta + head/tail) x [Mpad/2][128] x 16 bytes = two tagged
+                             // int64 (value << 1 | 1: a word is valid as soon as it is not zero); all zero between launches
     void* y;
     int M, Mpad, D, NB;      // NB = UMMA N = roundup16(D*Mpad)
     int N, K;
-    int tiles, kb_total;     // row tiles, k-blocks per row tile
+    int tpu, bmu;            // row tiles of 128 per work unit (1 or 2: two tiles share every digit tile they multiply), rows per unit
+    int tiles, kb_total;     // work units (called tiles below), k-blocks per unit
     // Schedule.  The last `sk_tiles` row tiles are cut stream-K fashion: their
     // sk_tiles*kb_total k-blocks form one linear space dealt out in contiguous
     // runs of `sk_per_cta` to the first `sk_ctas` CTAs.  The other tiles are
@@ -218,6 +194,7 @@ struct TcParams {
     int sk_ways;             // > 0: every shared tile is cut into this many near-equal pieces, one per CTA (CTA = tile * ways + piece)
     int ldy, y_col0;
     int act;                 // RUSTY_CUDA_ACT_SWIGLU_PAIRS: rows 2j, 2j+1 -> y[:, (y_col0 + 2j) / 2] = silu(gate) * up
+    int epi_warps;           // 4 or 8 epilogue warps: two per tensor-memory lane quarter split the activation rows between them
     int stages;
     int red_bytes;           // epilogue staging area: a partial tile (Mpad x 128 x 8 bytes), at least 12 KiB
     uint32_t idesc;
@@ -328,15 +305,16 @@ __device__ __forceinline__ void finalize_store4(const TcParams& p, YT* y, const 
 }
 
 template <typename YT>
-__global__ void __launch_bounds__(TC_THREADS, 2)
+__global__ void __launch_bounds__(TC_MAX_THREADS, 1)
 qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                      const __grid_constant__ TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // carve: [A stages][B stages][barriers]
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int b_stage_bytes = p.NB * BK;
+    const int a_stage_bytes = p.tpu * A_TILE_BYTES;
     uint8_t* sA = smem;
-    uint8_t* sB = smem + (size_t)p.stages * A_STAGE_BYTES;
+    uint8_t* sB = smem + (size_t)p.stages * a_stage_bytes;
     // epilogue staging for the bulk reduce-add of a partial tile: [Mpad/2][128] x 16 bytes
     int4* stage_red = reinterpret_cast<int4*>(sB + (size_t)p.stages * b_stage_bytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (size_t)p.red_bytes);
@@ -357,6 +335,13 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     const PeerOut po = {p.push.nranks > 1 ? p.push.nranks - 1 : 0, s_peer_delta};  // visible after the set-up barrier below
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) DBG(0);
+#ifdef RUSTY_TIMELINE
+    if (threadIdx.x == 0 && p.dbg) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        p.dbg[(size_t)blockIdx.x * 16 + 12] = (long long)smid;
+    }
+#endif
     pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
@@ -366,7 +351,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 4);
+            mbar_init(&acc_empty[a], (uint32_t)p.epi_warps);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -396,8 +381,8 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             while (ok && sched.next(sg)) {
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
                     if (!waited && early < p.stages) {
-                        mbar_expect_tx(&full[early], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
-                        tma_load_2d(sA + (size_t)early * A_STAGE_BYTES, &map_w, kb * BK, sg.t * BM, &full[early], pol_w);
+                        mbar_expect_tx(&full[early], (uint32_t)(a_stage_bytes + b_stage_bytes));
+                        tma_load_2d(sA + (size_t)early * a_stage_bytes, &map_w, kb * BK, sg.t * p.bmu, &full[early], pol_w);
                         early_kb[early] = kb;
                         ++early;
                         ++issued;
@@ -412,8 +397,8 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         waited = true;
                     }
                     if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
-                    mbar_expect_tx(&full[stage], (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
-                    tma_load_2d(sA + (size_t)stage * A_STAGE_BYTES, &map_w, kb * BK, sg.t * BM, &full[stage], pol_w);
+                    mbar_expect_tx(&full[stage], (uint32_t)(a_stage_bytes + b_stage_bytes));
+                    tma_load_2d(sA + (size_t)stage * a_stage_bytes, &map_w, kb * BK, sg.t * p.bmu, &full[stage], pol_w);
                     tma_load_2d(sB + (size_t)stage * b_stage_bytes, &map_x, kb * BK, 0, &full[stage], pol_x);
                     ++issued;
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -448,17 +433,20 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 const int ab = i & 1;
                 if (!mbar_wait(&acc_empty[ab], (((uint32_t)i >> 1) & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(ab * p.NB);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(ab * p.tpu * p.NB);   // accumulator h of the unit at + h * NB
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
                     if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
                     tc_fence_after();
                     if (kb == sg.kb0 && i == 0) DBG(4);
-                    const uint64_t da = make_smem_desc(smem_u32(sA + (size_t)stage * A_STAGE_BYTES));
+                    const uint64_t da = make_smem_desc(smem_u32(sA + (size_t)stage * a_stage_bytes));
                     const uint64_t db = make_smem_desc(smem_u32(sB + (size_t)stage * b_stage_bytes));
+                    for (int h = 0; h < p.tpu; ++h) {   // the unit's weight tiles, 16 KiB (1024 x 16 bytes) apart, against the same digit tile
 #pragma unroll
-                    for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
-                        // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
-                        umma_i8(d_tmem, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), p.idesc, (kb > sg.kb0 || k4 > 0) ? 1u : 0u);
+                        for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+                            // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
+                            umma_i8(d_tmem + (uint32_t)(h * p.NB), da + (uint64_t)(h * (A_TILE_BYTES >> 4) + 2 * k4), db + (uint64_t)(2 * k4), p.idesc,
+                                    (kb > sg.kb0 || k4 > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(&empty[stage]);
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -472,70 +460,56 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
         const int r = q * 32 + lane;            // row inside the tile
         YT* y = reinterpret_cast<YT*>(p.y);
-        const int ncol = p.D * p.Mpad;          // accumulator columns in use
         pdl_wait();                             // x, y, the sums and the counters belong to earlier kernels until now
         bool ok = true;
-        const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
+        const int et = threadIdx.x - 64;        // 0..EPI_THREADS-1 among the epilogue threads
+        const int EPI_THREADS = 32 * p.epi_warps;
+        // Two warps share a lane quarter (warps 2-5 and 6-9 see the same quarters): each takes half of the activation
+        // rows, in units of 8.  With 4 epilogue warps every warp takes them all.
+        const int m_split = p.epi_warps == 8 ? ((p.Mpad / 8 + 1) / 2) * 8 : p.Mpad;
+        const int m_lo = (warp - 2) < 4 ? 0 : m_split, m_hi = (warp - 2) < 4 ? m_split : p.Mpad;
         // per-row factors of the pre-pass: once into shared memory (a load from global memory per output costs
         // an L2 round trip each time)
         if (et < p.Mpad) s_rowf[et] = __ldcg(p.row_factor + et);
-        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-        int cut_t[2], cut_j[2], cut_n[2], n_cut = 0;  // shared tiles this CTA added a piece to
-        bool announced = false;
+        asm volatile("bar.sync 1, %0;" ::"r"(EPI_THREADS) : "memory");
+        int cut_t[2], cut_j[2], cut_n[2], cut_f[2], n_cut = 0;  // shared tiles this CTA holds a piece of
         Sched sched(p);
         Segment sg;
         for (int i = 0;; ++i) {
             const bool have = ok && sched.next(sg);
-            // Shared tiles: once all pieces of a tile have been added, each CTA that holds one of them turns an equal share
-            // of the tile's rows into y and leaves zeros behind (the arrival counters are cleared by the next pre-pass).  All pieces are added before anybody waits here, and the
-            // CTAs of the grid are resident together (one wave), so the wait cannot depend on a CTA that has not started.
-            // Announce this CTA's pieces once its last shared segment is behind it (the adds complete about when the
-            // weight stream ends); convert after the CTA's last whole tile, when the other pieces have arrived too.
-            if (ok && n_cut > 0 && !announced && (!have || sg.nseg == 1)) {
-                if (threadIdx.x == 64) {
-                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // this CTA's adds have been performed
-                    __threadfence();
-                    for (int e = 0; e < n_cut; ++e)
-                        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.counters + cut_t[e]) : "memory");
-                }
-                announced = true;
-            }
+            // Shared tiles.  Every CTA that holds a piece of a tile has written it into its own slot, each 64-bit sum
+            // tagged valid in its lowest bit; after its last segment a piece holder gathers an equal share of the tile's
+            // rows from ALL the tile's slots (polling words that are still zero), turns it into y and leaves zeros
+            // behind.  No counters, no fences: a word carries its own arrival.  The CTAs of the grid are resident
+            // together (one wave) and every piece is written before its holder waits here, so a wait cannot depend
+            // on a CTA that has not started.
             for (int e = 0; ok && e < n_cut && !have; ++e) {
-                const int t = cut_t[e], nseg = cut_n[e], j = cut_j[e];
-                if (threadIdx.x == 64) {
-                    const long long t0 = clock64();
-                    while (ld_acquire_gpu_u32(p.counters + t) < (unsigned)nseg) {
-                        if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                            *abort_flag = 1;
-                            if (atomicExch(&p.status->timeout_flag, 1u) == 0u) p.status->timeout_where = 8;
-                            break;
-                        }
-                    }
-                    DBG(10);
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-                if (*abort_flag) { ok = false; break; }
-                int4* tile_sum = reinterpret_cast<int4*>(p.part) + (size_t)(t - p.dp_tiles) * (p.Mpad / 2) * BM;
+                const int t = cut_t[e], nseg = cut_n[e], j = cut_j[e], fcta = cut_f[e];
+                const int lt = t - p.dp_tiles;
+                const size_t slot_items = (size_t)p.tpu * (p.Mpad / 2) * BM;   // a slot: [tile of the unit][m / 2][row] x 16 bytes
                 // this CTA's share of the tile's rows, cut in units of two rows so that a (gate, up) pair stays together
-                const int lo = 2 * (j * (BM / 2) / nseg), rows = 2 * ((j + 1) * (BM / 2) / nseg) - lo;
+                const int lo = 2 * (j * (p.bmu / 2) / nseg), rows = 2 * ((j + 1) * (p.bmu / 2) / nseg) - lo;
                 const int items = rows * (p.Mpad / 2);                         // one item: a row, two activation rows
                 if (rows <= 0) continue;
                 // item -> (row, mp) without a division per item: start at (et % rows, et / rows), step by EPI_THREADS items
                 int row = et % rows, mp = et / rows;
                 const int step_row = EPI_THREADS % rows, step_mp = EPI_THREADS / rows;
+                const long long t_begin = clock64();
                 // the loop bounds are the same for every thread: the pair epilogue needs whole warps
                 for (int base = 0; base < items; base += 4 * EPI_THREADS) {
                     const int it0 = base + et;
-                    int4 v[4];
-                    float sc[4];
+                    long long s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};
+                    size_t off[4];
                     int rw[4], mq[4];
+                    bool in[4];
+                    float wsc[4];   // the rows' weight scales: fetched with the pieces, not behind them
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {  // independent loads: one L2 round trip per batch
+                    for (int u = 0; u < 4; ++u) {
                         rw[u] = lo + row;
                         mq[u] = mp;
-                        const bool in = it0 + u * EPI_THREADS < items && t * BM + rw[u] < p.N;
-                        v[u] = in ? __ldcg(tile_sum + (size_t)mp * BM + rw[u]) : make_int4(0, 0, 0, 0);
-                        sc[u] = in ? __ldg(p.scales + t * BM + rw[u]) : 0.0f;
+                        in[u] = it0 + u * EPI_THREADS < items;
+                        off[u] = ((size_t)(rw[u] >> 7) * (p.Mpad / 2) + mp) * BM + (rw[u] & 127);
+                        wsc[u] = (in[u] && t * p.bmu + rw[u] < p.N) ? __ldg(p.scales + t * p.bmu + rw[u]) : 0.0f;
                         row += step_row;
                         mp += step_mp;
                         if (row >= rows) {
@@ -543,125 +517,155 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                             ++mp;
                         }
                     }
-                    // Park the batch in this thread's slots of the staging tile (free by now) and convert in a rolled
-                    // loop: code that runs once per CTA costs an instruction fetch per line, so it is kept short.
-                    float* stage_sc = reinterpret_cast<float*>(stage_red + 4 * EPI_THREADS);
-                    int* stage_at = reinterpret_cast<int*>(stage_sc + 4 * EPI_THREADS);
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const bool live = it0 + u * EPI_THREADS < items;
-                        if (live) __stcg(tile_sum + (size_t)mq[u] * BM + rw[u], make_int4(0, 0, 0, 0));
-                        stage_red[u * EPI_THREADS + et] = v[u];
-                        stage_sc[u * EPI_THREADS + et] = sc[u];
-                        stage_at[u * EPI_THREADS + et] = (live && t * BM + rw[u] < p.N) ? (rw[u] | (mq[u] << 8)) : -1;
-                    }
 #pragma unroll 1
+                    for (int q0 = 0; q0 < nseg; q0 += 4) {   // four pieces x four items: sixteen loads in flight per trip
+                        ulonglong2* slot[4];
+                        ulonglong2 v[4][4];
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            // piece q of the tile sits with CTA fcta + q: its head piece (even slot) if that CTA's run
+                            // of k-blocks starts inside this tile, else its tail piece (odd slot)
+                            const int c = fcta + min(q0 + w, nseg - 1);
+                            slot[w] = p.part + (size_t)(2 * c + (c * p.sk_per_cta >= lt * p.kb_total ? 0 : 1)) * slot_items;
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                                v[w][u] = (in[u] && q0 + w < nseg) ? __ldcg(slot[w] + off[u]) : make_ulonglong2(1ull, 1ull);
+                        }
+                        // every word carries its own "valid" tag in bit 0: one combined test for the common case ...
+                        unsigned long long allv = 1ull;
+#pragma unroll
+                        for (int w = 0; w < 4; ++w)
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) allv &= v[w][u].x & v[w][u].y;
+                        // ... and a rolled re-poll of the whole batch while some piece has not landed yet
+                        while (!(allv & 1ull)) {
+                            if (*abort_flag || clock64() - t_begin > WAIT_LIMIT_CYCLES) {
+                                *abort_flag = 1;
+                                if (atomicExch(&p.status->timeout_flag, 1u) == 0u) p.status->timeout_where = 8;
+                                ok = false;
+                                break;
+                            }
+                            allv = 1ull;
+#pragma unroll
+                            for (int w = 0; w < 4; ++w)
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    if (in[u] && q0 + w < nseg) v[w][u] = __ldcg(slot[w] + off[u]);
+                                    allv &= v[w][u].x & v[w][u].y;
+                                }
+                        }
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                if (in[u] && q0 + w < nseg) __stcg(slot[w] + off[u], make_ulonglong2(0ull, 0ull));
+                                s0[u] += (long long)v[w][u].x >> 1;   // arithmetic shift: drops the tag, keeps the sign
+                                s1[u] += (long long)v[w][u].y >> 1;
+                            }
+                        }
+                    }
+                    if (__any_sync(0xffffffffu, !ok)) {   // warp-uniform: the conversion below shuffles between lanes
+                        ok = false;
+                        break;
+                    }
+#pragma unroll
                     for (int u = 0; u < 4; u += 2) {  // two items = four outputs per trip
-                        const int at0 = stage_at[u * EPI_THREADS + et], at1 = stage_at[(u + 1) * EPI_THREADS + et];
-                        const bool v0 = at0 >= 0, v1 = at1 >= 0;
-                        const longlong2 t0 = *reinterpret_cast<const longlong2*>(&stage_red[u * EPI_THREADS + et]);
-                        const longlong2 t1 = *reinterpret_cast<const longlong2*>(&stage_red[(u + 1) * EPI_THREADS + et]);
-                        const float s0 = stage_sc[u * EPI_THREADS + et], s1 = stage_sc[(u + 1) * EPI_THREADS + et];
-                        const int n0 = t * BM + (at0 & 0xff), n1 = t * BM + (at1 & 0xff);
-                        const int m0 = v0 ? 2 * (at0 >> 8) : 0, m1 = v1 ? 2 * (at1 >> 8) : 0;
-                        const long long a4[4] = {t0.x, t0.y, t1.x, t1.y};
+                        const bool v0 = in[u] && t * p.bmu + rw[u] < p.N, v1 = in[u + 1] && t * p.bmu + rw[u + 1] < p.N;
+                        const int n0 = t * p.bmu + rw[u], n1 = t * p.bmu + rw[u + 1];
+                        const int m0 = v0 ? 2 * mq[u] : 0, m1 = v1 ? 2 * mq[u + 1] : 0;
+                        const long long a4[4] = {s0[u], s1[u], s0[u + 1], s1[u + 1]};
                         const int n4[4] = {n0, n0, n1, n1}, m4[4] = {m0, m0 + 1, m1, m1 + 1};
-                        const float s4[4] = {s0, s0, s1, s1};
+                        const float s4[4] = {wsc[u], wsc[u], wsc[u + 1], wsc[u + 1]};
                         const bool l4[4] = {v0 && m0 < p.M, v0 && m0 + 1 < p.M, v1 && m1 < p.M, v1 && m1 + 1 < p.M};
                         finalize_store4<YT>(p, y, n4, m4, a4, s4, s_rowf, po, l4);
                     }
                 }
                 if (threadIdx.x == 64) DBG(11);
-                // the batch was parked in the staging tile at slots indexed by thread, the whole tile that may follow
-                // is staged there at slots indexed by row: no warp may start on it while another still reads its batch
-                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
             }
+            if (__any_sync(0xffffffffu, !ok)) ok = false;
             if (!have || !ok) break;
             const int ab = i & 1;
-            const int n = sg.t * BM + r;
-            const bool row_ok = n < p.N;
             if (!mbar_wait(&acc_full[ab], ((uint32_t)i >> 1) & 1u, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             if (threadIdx.x == 64) DBG(6 + 4 * (i & 1));
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * p.NB);
             {
-                // Fold the digit planes into one exact 64-bit integer per output and stage them in shared memory
-                // ([m/2][row] x 16 bytes).  A whole tile is converted from there in a rolled loop (unrolled register
-                // code that runs once per tile costs an instruction fetch per line and was twice as slow); a piece of
-                // a shared tile is added into the tile's sum in global memory with ONE bulk reduce
-                // (cp.reduce.async.bulk ... add.u64: the adds happen in L2 at line rate).
-                for (int m0 = 0; m0 < p.Mpad; m0 += 8) {
-                    int32_t c[4][8];
+                // Fold the digit planes into one exact 64-bit integer per output.  A whole tile is staged in shared
+                // memory ([m/2][row] x 16 bytes) and converted from there in a rolled loop (unrolled register code
+                // that runs once per tile costs an instruction fetch per line and was twice as slow); a piece of a
+                // shared tile goes straight into this CTA's slot in global memory, every word tagged valid.
+                const bool whole = sg.nseg == 1;
+                for (int ht = 0; ht < p.tpu; ++ht) {   // the unit's tiles, one accumulator each
+                    const int n = sg.t * p.bmu + ht * BM + r;
+                    const bool row_ok = n < p.N;
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((ab * p.tpu + ht) * p.NB);
+                    ulonglong2* slot = p.part + ((size_t)sg.slot * p.tpu + ht) * (p.Mpad / 2) * BM;
+                    for (int m0 = m_lo; m0 < m_hi; m0 += 8) {
+                        int32_t c[4][8];
 #pragma unroll
-                    for (int d = 0; d < 4; ++d)
-                        if (d < p.D) tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c[d]);
-                    tmem_ld_wait();
+                        for (int d = 0; d < 4; ++d)
+                            if (d < p.D) tmem_ld8(taddr + (uint32_t)(d * p.Mpad + m0), c[d]);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int h = 0; h < 4; ++h) {
-                        long long a0 = c[0][2 * h], a1 = c[0][2 * h + 1];
+                        for (int h = 0; h < 4; ++h) {
+                            long long a0 = c[0][2 * h], a1 = c[0][2 * h + 1];
 #pragma unroll
-                        for (int d = 1; d < 4; ++d)
-                            if (d < p.D) {
-                                a0 = a0 * 128 + c[d][2 * h];
-                                a1 = a1 * 128 + c[d][2 * h + 1];
+                            for (int d = 1; d < 4; ++d)
+                                if (d < p.D) {
+                                    a0 = a0 * 128 + c[d][2 * h];
+                                    a1 = a1 * 128 + c[d][2 * h + 1];
+                                }
+                            if (!row_ok) a0 = a1 = 0;
+                            if (whole) {
+                                int4 v;
+                                v.x = (int)(a0 & 0xffffffffll);
+                                v.y = (int)(a0 >> 32);
+                                v.z = (int)(a1 & 0xffffffffll);
+                                v.w = (int)(a1 >> 32);
+                                stage_red[(size_t)(m0 / 2 + h) * BM + r] = v;
+                            } else {   // |sum| < 2^46: room for the tag; two 64-bit words, each stored whole
+                                __stcg(slot + (size_t)(m0 / 2 + h) * BM + r,
+                                       make_ulonglong2((unsigned long long)((a0 << 1) | 1), (unsigned long long)((a1 << 1) | 1)));
                             }
-                        if (!row_ok) a0 = a1 = 0;
-                        int4 v;
-                        v.x = (int)(a0 & 0xffffffffll);
-                        v.y = (int)(a0 >> 32);
-                        v.z = (int)(a1 & 0xffffffffll);
-                        v.w = (int)(a1 >> 32);
-                        stage_red[(size_t)(m0 / 2 + h) * BM + r] = v;
+                        }
+                    }
+                    if (ht == p.tpu - 1) {   // the accumulators of this unit have been read
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                        if (threadIdx.x == 64) DBG(7 + 4 * (i & 1));
+                    }
+                    if (whole) {
+                        // every thread reads back only what it staged itself: no barrier needed
+                        const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+#pragma unroll 1
+                        for (int m = m_lo; m < min(m_hi, p.M); m += 4) {  // in units of 8: the staged rows m .. m+3 exist
+                            const longlong2 t0 = *reinterpret_cast<const longlong2*>(&stage_red[(size_t)(m >> 1) * BM + r]);
+                            const longlong2 t1 = *reinterpret_cast<const longlong2*>(&stage_red[(size_t)((m >> 1) + 1) * BM + r]);
+                            const long long a4[4] = {t0.x, t0.y, t1.x, t1.y};
+                            const int n4[4] = {n, n, n, n}, m4[4] = {m, m + 1, m + 2, m + 3};
+                            const float s4[4] = {sc, sc, sc, sc};
+                            const bool l4[4] = {row_ok, row_ok && m + 1 < p.M, row_ok && m + 2 < p.M, row_ok && m + 3 < p.M};
+                            finalize_store4<YT>(p, y, n4, m4, a4, s4, s_rowf, po, l4);
+                        }
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[ab]);
-                if (threadIdx.x == 64) DBG(7 + 4 * (i & 1));
-                if (sg.nseg == 1) {
-                    // every thread reads back only what it staged itself: no barrier needed
-                    const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
-#pragma unroll 1
-                    for (int m = 0; m < p.M; m += 4) {  // Mpad is a multiple of 8: the staged rows m .. m+3 exist
-                        const longlong2 t0 = *reinterpret_cast<const longlong2*>(&stage_red[(size_t)(m >> 1) * BM + r]);
-                        const longlong2 t1 = *reinterpret_cast<const longlong2*>(&stage_red[(size_t)((m >> 1) + 1) * BM + r]);
-                        const long long a4[4] = {t0.x, t0.y, t1.x, t1.y};
-                        const int n4[4] = {n, n, n, n}, m4[4] = {m, m + 1, m + 2, m + 3};
-                        const float s4[4] = {sc, sc, sc, sc};
-                        const bool l4[4] = {row_ok, row_ok && m + 1 < p.M, row_ok && m + 2 < p.M, row_ok && m + 3 < p.M};
-                        finalize_store4<YT>(p, y, n4, m4, a4, s4, s_rowf, po, l4);
-                    }
+                if (whole) {
                     if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
                     continue;
                 }
-                const int lt = sg.t - p.dp_tiles;
-                int4* tile_sum = reinterpret_cast<int4*>(p.part) + (size_t)lt * (p.Mpad / 2) * BM;
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // staged values -> visible to the bulk-copy engine
-                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-                if (threadIdx.x == 64) {
-                    const uint32_t bytes = (uint32_t)(p.Mpad * 8 * BM);
-                    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.u64 [%0], [%1], %2;" ::"l"(tile_sum),
-                                 "r"(smem_u32(stage_red)), "r"(bytes)
-                                 : "memory");
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    // only until the staging tile has been read: the adds themselves complete while the next segment
-                    // is folded, and are waited for (and announced) before the shared conversion below
-                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                }
-                if (threadIdx.x == 64) DBG(8 + 4 * (i & 1));
-                // The conversion of the finished sums is shared between the CTAs that hold the tile's pieces and is
-                // done after the CTA's last segment (below): remember the tile and which piece this was.
+                // The conversion is shared between the CTAs that hold the tile's pieces and is done after the CTA's
+                // last segment (above): remember the tile and which piece this was.
                 if (n_cut < 2) {
                     cut_t[n_cut] = sg.t;
                     cut_j[n_cut] = (int)blockIdx.x - sg.first_cta;
                     cut_n[n_cut] = sg.nseg;
+                    cut_f[n_cut] = sg.first_cta;
                     ++n_cut;
                 } else {
                     ok = false;  // cannot happen: a run of k-blocks starts and ends inside at most two shared tiles
                     if (threadIdx.x == 64 && atomicExch(&p.status->timeout_flag, 1u) == 0u) p.status->timeout_where = 7;
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // the staging tile is free again (the bulk reduce has read it)
-                if (threadIdx.x == 64) DBG(9 + 4 * (i & 1));
+                if (threadIdx.x == 64) DBG(8 + 4 * (i & 1));
             }
         }
     }
@@ -688,29 +692,25 @@ constexpr size_t WS_GUARD = 1024;
 constexpr unsigned char WS_GUARD_BYTE = 0xA5;
 constexpr size_t WS_XQ_BYTES = 24u << 20;      // digit planes: up to 256 rows x K <= 96K
 constexpr size_t WS_INVS_BYTES = 4096;
-constexpr size_t WS_ACC_BYTES = 48u << 20;     // split-K partial sums
-constexpr size_t WS_CNT_BYTES = 64u << 10;     // arrival counters, kept at zero between kernels (small-batch mode, prefill kernels)
-constexpr size_t WS_CNT2_BYTES = 64u << 10;    // arrival counters of the GEMM with a pre-pass, which clears them
+constexpr size_t WS_ACC_BYTES = 48u << 20;     // pieces of K-cut tiles (two slots per CTA), zero between launches
+constexpr size_t WS_CNT_BYTES = 64u << 10;     // arrival counters of the prefill kernels, kept at zero between kernels
 constexpr size_t WS_OFF_XQ = 0;
 constexpr size_t WS_OFF_INVS = WS_OFF_XQ + WS_XQ_BYTES + WS_GUARD;
 constexpr size_t WS_OFF_ACC = WS_OFF_INVS + WS_INVS_BYTES + WS_GUARD;
 constexpr size_t WS_OFF_CNT = WS_OFF_ACC + WS_ACC_BYTES + WS_GUARD;
-constexpr size_t WS_OFF_CNT2 = WS_OFF_CNT + WS_CNT_BYTES + WS_GUARD;
-constexpr size_t WS_TOTAL = WS_OFF_CNT2 + WS_CNT2_BYTES + WS_GUARD;
-constexpr size_t WS_GUARD_AT[5] = {WS_OFF_INVS - WS_GUARD, WS_OFF_ACC - WS_GUARD, WS_OFF_CNT - WS_GUARD, WS_OFF_CNT2 - WS_GUARD,
-                                   WS_TOTAL - WS_GUARD};
+constexpr size_t WS_TOTAL = WS_OFF_CNT + WS_CNT_BYTES + WS_GUARD;
+constexpr int WS_GUARDS = 4;
+constexpr size_t WS_GUARD_AT[WS_GUARDS] = {WS_OFF_INVS - WS_GUARD, WS_OFF_ACC - WS_GUARD, WS_OFF_CNT - WS_GUARD, WS_TOTAL - WS_GUARD};
 
 // The schedule of one launch: how the row tiles are dealt to the CTAs.  One place for the regular entry points and the
 // entry point with built-in scratch, so that their guards cannot drift apart.
 //   whole tiles (tile = cta, cta + grid, ...) for the first dp_tiles tiles; the last sk_tiles tiles are cut along K.
-// `sums_tiles_cap` / `counter_cap`: how many cut tiles the caller's scratch can park / how many arrival counters
-// (indexed by the GLOBAL tile number) it holds.  Returns false when N needs more counters than there are.
+// `slots_cap`: how many piece slots (two per CTA) the caller's scratch holds; a launch that would need more takes
+// whole tiles only.
 struct TcSchedule {
     int grid, dp_tiles, sk_tiles, sk_per_cta, sk_ctas, sk_ways;
 };
-bool plan_tc_schedule(int tiles, int kb_total, int sm_count, int dp_percent, size_t sums_tiles_cap, size_t counter_cap,
-                      TcSchedule* out) {
-    if ((size_t)tiles > counter_cap) return false;
+void plan_tc_schedule(int tiles, int kb_total, int sm_count, int dp_percent, size_t slots_cap, TcSchedule* out) {
     TcSchedule s{};
     // Whole waves of row tiles are taken tile-per-CTA; the remainder (fewer tiles than SMs) is cut stream-K fashion so
     // every SM streams the same number of k-blocks.  A cut needs >= 4 k-blocks per CTA and room for the parked tiles.
@@ -749,7 +749,7 @@ bool plan_tc_schedule(int tiles, int kb_total, int sm_count, int dp_percent, siz
             s.sk_ctas = s.sk_tiles * ways;
             s.sk_per_cta = (kb_total + ways - 1) / ways;
         }
-        if ((size_t)s.sk_tiles > sums_tiles_cap) {
+        if ((size_t)2 * s.sk_ctas > slots_cap) {
             s.dp_tiles = tiles;  // no room to park partial tiles: whole tiles only
             s.sk_tiles = 0;
             s.sk_per_cta = 0;
@@ -761,7 +761,6 @@ bool plan_tc_schedule(int tiles, int kb_total, int sm_count, int dp_percent, siz
     if (s.dp_tiles == 0 && s.sk_ctas > 0) grid = s.sk_ctas;
     s.grid = grid;
     *out = s;
-    return true;
 }
 
 int pick_digits(int x_dtype, uint32_t rows) {
@@ -773,13 +772,15 @@ int pick_digits(int x_dtype, uint32_t rows) {
 }
 
 template <typename XT>
-cudaError_t launch_digitize(rusty_cuda_ctx* ctx, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D,
-                            const PeerPush& push, long long* dbg, unsigned int* counters, int n_counters) {
+cudaError_t launch_digitize(cudaStream_t stream, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D, const PeerPush& push,
+                            long long* dbg) {
+    // Mpad is a multiple of 8 and at most 64: one row per block up to 32 rows, two beyond
+    int R = 1;
+    while (Mpad / R > DIG_MAX_BLOCKS || Mpad % R != 0) R <<= 1;   // R in {1, 2}: the rows' thread groups share a block evenly
+    const int blocks = Mpad / R;
     if (D == 4)
-        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(Mpad), dim3(DIG_THREADS), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg,
-                          counters, n_counters);
-    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(Mpad), dim3(DIG_THREADS), 0, ctx->stream, (const XT*)x, xq, inv_s, M, Mpad, K, push, dbg,
-                      counters, n_counters);
+        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(blocks), dim3(DIG_THREADS), 0, stream, (const XT*)x, xq, inv_s, M, Mpad, K, R, push, dbg);
+    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(blocks), dim3(DIG_THREADS), 0, stream, (const XT*)x, xq, inv_s, M, Mpad, K, R, push, dbg);
 }
 
 }  // namespace
@@ -795,7 +796,7 @@ int tc_workspace_reserve(rusty_cuda_ctx* ctx) {
         return fail(ctx, RUSTY_CUDA_ERR_MEMORY_ALLOCATION, "tensor-core workspace: cudaMalloc(%zu) failed", (size_t)WS_TOTAL);
     }
     e = cudaMemsetAsync(p, 0, WS_TOTAL, ctx->stream);
-    for (size_t g = 0; e == cudaSuccess && g < 5; ++g) e = cudaMemsetAsync((uint8_t*)p + WS_GUARD_AT[g], WS_GUARD_BYTE, WS_GUARD, ctx->stream);
+    for (size_t g = 0; e == cudaSuccess && g < (size_t)WS_GUARDS; ++g) e = cudaMemsetAsync((uint8_t*)p + WS_GUARD_AT[g], WS_GUARD_BYTE, WS_GUARD, ctx->stream);
     if (e != cudaSuccess) {
         cudaFree(p);
         return check_cuda(ctx, e, "tensor-core workspace: memset");
@@ -820,7 +821,7 @@ int tc_workspace_check_guards(rusty_cuda_ctx* ctx, cudaError_t* err) {
     *err = cudaSuccess;
     if (!ctx->tc_ws) return -1;
     std::vector<unsigned char> host(WS_GUARD);
-    for (int g = 0; g < 5; ++g) {
+    for (int g = 0; g < (size_t)WS_GUARDS; ++g) {
         *err = cudaMemcpyAsync(host.data(), (uint8_t*)ctx->tc_ws + WS_GUARD_AT[g], WS_GUARD, cudaMemcpyDeviceToHost, ctx->stream);
         if (*err == cudaSuccess) *err = cudaStreamSynchronize(ctx->stream);
         if (*err != cudaSuccess) return -1;
@@ -828,6 +829,14 @@ int tc_workspace_check_guards(rusty_cuda_ctx* ctx, cudaError_t* err) {
             if (host[i] != WS_GUARD_BYTE) return g;
     }
     return -1;
+}
+
+// After a device-side wait gave up, pieces of K-cut tiles may be left in their slots: clear them, so that the next
+// launch starts from zeros again.
+void tc_workspace_clear_pieces(rusty_cuda_ctx* ctx) {
+    if (!ctx->tc_ws) return;
+    if (cudaMemsetAsync((uint8_t*)ctx->tc_ws + WS_OFF_ACC, 0, WS_ACC_BYTES, ctx->stream) == cudaSuccess) cudaStreamSynchronize(ctx->stream);
+    cudaGetLastError();
 }
 
 void tc_workspace_release(rusty_cuda_ctx* ctx) {
@@ -866,17 +875,12 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     uint8_t* ws = (uint8_t*)ctx->tc_ws;
     int8_t* xq = (int8_t*)ws;
     float* inv_s = (float*)(ws + WS_OFF_INVS);
-    int32_t* acc = (int32_t*)(ws + WS_OFF_ACC);
-    // two sets of arrival counters: one kept at zero by its users, one cleared by the pre-pass of this path
-    unsigned int* counters = (unsigned int*)(ws + WS_OFF_CNT2);   // this set is cleared by the pre-pass
+    ulonglong2* acc = (ulonglong2*)(ws + WS_OFF_ACC);
     if ((size_t)D * Mpad * a.K > WS_XQ_BYTES)
         return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: %d digit rows x K=%u exceed the workspace", D * Mpad, a.K);
 
     cudaError_t le = cudaSuccess;
     int rc = RUSTY_CUDA_OK;
-    const int n_tiles = (int)((a.N + BM - 1) / BM);
-    if ((size_t)n_tiles * 4 > WS_CNT_BYTES)
-        return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: N=%u has more row tiles than arrival counters", a.N);
     // development aid: each launch pair writes its timeline into the next 152 x 16 slots of the attached buffer
     long long* dbg = nullptr;
     if (ctx->tc_dbg) {
@@ -888,8 +892,8 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
         push = *a.push;
     }
     {
-        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr, counters, n_tiles)
-                                          : launch_digitize<float>(ctx, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr, counters, n_tiles);
+        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr)
+                                          : launch_digitize<float>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr);
         if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
         rc = after_launch(ctx, "digitize_x");
         if (rc) return rc;
@@ -899,7 +903,6 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.scales = a.scales;
     p.row_factor = inv_s;
     p.part = acc;
-    p.counters = counters;
     p.y = y;
     p.M = M;
     p.Mpad = Mpad;
@@ -907,14 +910,26 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.NB = NB;
     p.N = (int)a.N;
     p.K = (int)a.K;
-    p.tiles = (p.N + BM - 1) / BM;
-    p.kb_total = (p.K + BK - 1) / BK;
+    // Two row tiles per work unit while both accumulator pairs fit tensor memory (4 * NB <= 512 columns): every
+    // digit tile a CTA loads then multiplies 256 weight rows instead of 128, which takes a quarter off the bytes a
+    // CTA pulls from L2 (the digits are re-read by every row tile; the weights are not).  Only where the units are
+    // then taken whole: a unit's epilogue is twice a tile's, which cut units (whose pieces cross CTAs after the
+    // stream) cannot afford.  Measured on batch 32: gate|up 31.9 -> 29.9 us, LM head 98.1 -> 95.9 us; with cut units
+    // the whole stack loses 6 %.  RUSTY_TC_TWO_TILES = 0 / 1 / 2: never / by that rule / always (tuning aid).
+    static const int two_tiles = getenv("RUSTY_TC_TWO_TILES") ? atoi(getenv("RUSTY_TC_TWO_TILES")) : 1;
     // RUSTY_TC_DP_PERCENT: least share of the SMs that whole tiles must keep streaming (default 72; 101 turns the rule off).
     static const int dp_percent = getenv("RUSTY_TC_DP_PERCENT") ? atoi(getenv("RUSTY_TC_DP_PERCENT")) : 72;
+    p.kb_total = (p.K + BK - 1) / BK;
     TcSchedule sc{};
-    if (!plan_tc_schedule(p.tiles, p.kb_total, ctx->sm_count, dp_percent, WS_ACC_BYTES / ((size_t)Mpad * BM * 8),
-                          WS_CNT_BYTES / 4, &sc))
-        return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: N=%u has more row tiles than arrival counters", a.N);
+    p.tpu = 1;
+    if (two_tiles > 0 && 4 * NB <= 512 && a.N > (uint32_t)BM) {
+        const int units = (p.N + 2 * BM - 1) / (2 * BM);
+        plan_tc_schedule(units, p.kb_total, ctx->sm_count, dp_percent, WS_ACC_BYTES / ((size_t)2 * Mpad * BM * 8), &sc);
+        if (two_tiles >= 2 || sc.sk_tiles == 0) p.tpu = 2;
+    }
+    p.bmu = p.tpu * BM;
+    p.tiles = (p.N + p.bmu - 1) / p.bmu;
+    plan_tc_schedule(p.tiles, p.kb_total, ctx->sm_count, dp_percent, WS_ACC_BYTES / ((size_t)p.tpu * Mpad * BM * 8), &sc);
     int grid = sc.grid;
     p.dp_tiles = sc.dp_tiles;
     p.sk_tiles = sc.sk_tiles;
@@ -924,34 +939,38 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
     p.act = a.act;
+    {
+        // narrow batches keep the small CTA (two of them fit an SM: the next kernel's CTA prefetches beside this one);
+        // from 16 rows on the epilogue is what bounds the kernel and gets eight warps
+        static const bool four = getenv("RUSTY_TC_EPI4") != nullptr;   // tuning aid
+        p.epi_warps = (Mpad >= 16 && !four) ? 8 : 4;
+    }
     p.status = ctx->status_dev;
     p.dbg = dbg;
     p.push = push;
     // int8 x int8 -> int32, both K-major: c_format=S32(2)@4, a_format=INT8(1)@7, b_format=INT8(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     uint32_t cols = 32;
-    while (cols < (uint32_t)(2 * NB)) cols <<= 1;
+    while (cols < (uint32_t)(2 * p.tpu * NB)) cols <<= 1;   // two sets of accumulators: the epilogue of one unit overlaps the next
     p.tmem_cols = cols;
-    const int b_stage = NB * BK;
-    // Half of the SM's shared memory at most, so that the next kernel's CTA can move in beside this one and
-    // prefetch its weights while this one drains (RUSTY_TC_FULL_SMEM=1: take it all, 8 stages).
+    const int a_stage = p.tpu * A_TILE_BYTES, b_stage = NB * BK;
+    // Half of the SM's shared memory at most for narrow batches, so that the next kernel's CTA can move in beside this
+    // one and prefetch its weights while this one drains (RUSTY_TC_FULL_SMEM=1: take it all, 8 stages).
     static const bool full_smem = getenv("RUSTY_TC_FULL_SMEM") != nullptr;
     size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
-    if (!full_smem && NB <= 32 && 4 * A_STAGE_BYTES + 4096 <= budget / 2)
+    if (!full_smem && NB <= 32 && 4 * (size_t)a_stage + 4096 <= budget / 2)
         budget = budget / 2 - 1024;  // narrow batches: leave room for the next kernel's CTA on the SM
-    // epilogue staging of a partial tile; the shared finalize parks 4 x 128 sums, scales and positions there (12 KiB)
-    const size_t red_bytes = (size_t)Mpad * 8 * BM > 12288 ? (size_t)Mpad * 8 * BM : (size_t)12288;
-    int stages = budget > red_bytes + 2048
-                     ? (int)((budget - 1024 - 512 - red_bytes) / (size_t)(A_STAGE_BYTES + b_stage))
-                     : 0;
+    // epilogue staging of one whole 128-row tile (its folded sums); launches without whole tiles need none
+    const size_t red_bytes = p.dp_tiles > 0 ? (size_t)Mpad * 8 * BM : 0;
+    int stages = budget > red_bytes + 2048 ? (int)((budget - 1024 - 512 - red_bytes) / (size_t)(a_stage + b_stage)) : 0;
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "tensor-core path: tile does not fit shared memory");
     p.stages = stages;
     p.red_bytes = (int)red_bytes;
-    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
+    const size_t smem = 1024 + (size_t)stages * (a_stage + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
 
     CUtensorMap map_w, map_x;
-    if (!make_map_u8(&map_w, a.w, a.N, a.K, BM) ||
+    if (!make_map_u8(&map_w, a.w, a.N, a.K, (uint32_t)p.bmu) ||
         !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, a.K, (uint32_t)NB))
         return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "tensor-core path: cuTensorMapEncodeTiled failed");
 
@@ -962,7 +981,7 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
         cudaError_t e = ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_i8_tc: cudaFuncSetAttribute");
     }
-    le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, ctx->stream, map_w, map_x, p);
+    le = launch_pdl(kern, dim3(grid), dim3(64 + 32 * p.epi_warps), smem, ctx->stream, map_w, map_x, p);
     if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_i8_tc");
     return after_launch(ctx, "qlinear_i8_tc");
 }
@@ -1006,16 +1025,14 @@ namespace {
 
 constexpr uint32_t STATIC_MAX_ROWS = 8;       // activation rows per call
 constexpr uint32_t STATIC_MAX_K = 8192;       // input features
-constexpr uint32_t STATIC_MAX_N = 262144;     // output features: one arrival counter per 128-row tile, indexed by tile number
+constexpr uint32_t STATIC_MAX_N = 262144;     // output features (a stated bound; 2048 row tiles)
 constexpr int STATIC_MAX_CTAS = 160;          // CTAs launched at most (one per SM)
 constexpr size_t ST_XQ_BYTES = (size_t)4 * 8 * STATIC_MAX_K;            // 4 digit planes x 8 padded rows
 constexpr size_t ST_FACTOR_BYTES = 256;
-constexpr size_t ST_SUMS_TILES = STATIC_MAX_CTAS;                        // cut tiles parked at most (fewer than CTAs)
-constexpr size_t ST_SUMS_BYTES = ST_SUMS_TILES * 8 * 8 * BM;            // one parked 8-row tile (int64) per cut tile
-constexpr size_t ST_CNT_BYTES = (size_t)(STATIC_MAX_N / BM) * 4;        // 2048 counters
+constexpr size_t ST_SLOTS = 2 * STATIC_MAX_CTAS;                         // pieces of K-cut tiles: a head and a tail slot per CTA
+constexpr size_t ST_SUMS_BYTES = ST_SLOTS * 8 * 8 * BM;                 // one 8-row piece (tagged int64) per slot
 constexpr size_t ST_STATUS_BYTES = 256;
-constexpr size_t ST_TOTAL = ST_XQ_BYTES + ST_FACTOR_BYTES + ST_SUMS_BYTES + ST_CNT_BYTES + ST_STATUS_BYTES;  // ~1.5 MiB
-static_assert(ST_CNT_BYTES / 4 * BM == STATIC_MAX_N, "one arrival counter per row tile up to STATIC_MAX_N");
+constexpr size_t ST_TOTAL = ST_XQ_BYTES + ST_FACTOR_BYTES + ST_SUMS_BYTES + ST_STATUS_BYTES;  // ~2.8 MiB
 static_assert(STATIC_MAX_N % BM == 0, "the N cap is a whole number of row tiles");
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
@@ -1080,22 +1097,20 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     cudaStream_t st = (cudaStream_t)stream;
     int8_t* xq = (int8_t*)sd.base;
     float* factor = (float*)(sd.base + ST_XQ_BYTES);
-    unsigned char* zeroed = sd.base + ST_XQ_BYTES + ST_FACTOR_BYTES;  // sums, counters, status: must start at zero
-    int32_t* sums = (int32_t*)zeroed;
-    unsigned int* counters = (unsigned int*)(zeroed + ST_SUMS_BYTES);
-    rusty_cuda_dev_status* status = (rusty_cuda_dev_status*)(zeroed + ST_SUMS_BYTES + ST_CNT_BYTES);
-    e = cudaMemsetAsync(zeroed, 0, ST_SUMS_BYTES + ST_CNT_BYTES + ST_STATUS_BYTES, st);
+    unsigned char* zeroed = sd.base + ST_XQ_BYTES + ST_FACTOR_BYTES;  // piece slots and status: must start at zero
+    ulonglong2* sums = (ulonglong2*)zeroed;
+    rusty_cuda_dev_status* status = (rusty_cuda_dev_status*)(zeroed + ST_SUMS_BYTES);
+    e = cudaMemsetAsync(zeroed, 0, ST_SUMS_BYTES + ST_STATUS_BYTES, st);
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: clearing the scratch");
 
     const int Mi = (int)M, Mpad = 8, D = 4, NB = 32;
-    e = launch_pdl(digitize_x_kernel<float, 4>, dim3(Mpad), dim3(DIG_THREADS), 0, st, x_f32, xq, factor, Mi, Mpad, (int)K, PeerPush{}, (long long*)nullptr, counters, (int)((N + BM - 1) / BM));
+    e = launch_digitize<float>(st, x_f32, xq, factor, Mi, Mpad, (int)K, D, PeerPush{}, nullptr);
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: digitize_x");
 
     TcParams p{};
     p.scales = scales;
     p.row_factor = factor;
     p.part = sums;
-    p.counters = counters;
     p.y = y_f32;
     p.M = Mi;
     p.Mpad = Mpad;
@@ -1103,13 +1118,13 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     p.NB = NB;
     p.N = (int)N;
     p.K = (int)K;
+    p.tpu = 1;
+    p.bmu = BM;
     p.tiles = (p.N + BM - 1) / BM;
     p.kb_total = (p.K + BK - 1) / BK;
     // the same schedule rules as the regular entry points, with this scratch's capacities
     TcSchedule sc{};
-    if (!plan_tc_schedule(p.tiles, p.kb_total, sd.sm_count < STATIC_MAX_CTAS ? sd.sm_count : STATIC_MAX_CTAS,
-                          /*dp_percent=*/72, ST_SUMS_TILES, ST_CNT_BYTES / 4, &sc))
-        return fail(nullptr, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_i8_forward_static: N=%u has more row tiles than arrival counters", N);
+    plan_tc_schedule(p.tiles, p.kb_total, sd.sm_count < STATIC_MAX_CTAS ? sd.sm_count : STATIC_MAX_CTAS, /*dp_percent=*/72, ST_SLOTS, &sc);
     const int grid = sc.grid;
     p.dp_tiles = sc.dp_tiles;
     p.sk_tiles = sc.sk_tiles;
@@ -1118,6 +1133,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     p.sk_ways = sc.sk_ways;
     p.ldy = (int)N;
     p.y_col0 = 0;
+    p.epi_warps = 4;
     p.status = status;
     p.dbg = nullptr;
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -1125,12 +1141,12 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     const int b_stage = NB * BK;
     const size_t red_bytes = (size_t)Mpad * 8 * BM > 12288 ? (size_t)Mpad * 8 * BM : (size_t)12288;
     const size_t budget = (sd.smem_optin > 4096 ? sd.smem_optin - 4096 : 0) / 2;
-    int stages = budget > red_bytes + 4096 ? (int)((budget - 2048 - red_bytes) / (size_t)(A_STAGE_BYTES + b_stage)) : 0;
+    int stages = budget > red_bytes + 4096 ? (int)((budget - 2048 - red_bytes) / (size_t)(A_TILE_BYTES + b_stage)) : 0;
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(nullptr, RUSTY_CUDA_ERR_UNSUPPORTED, "qlinear_i8_forward_static: shared memory too small");
     p.stages = stages;
     p.red_bytes = (int)red_bytes;
-    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
+    const size_t smem = 1024 + (size_t)stages * (A_TILE_BYTES + b_stage) + red_bytes + (size_t)(2 * stages + 4) * 8 + 256;
     CUtensorMap map_w, map_x;
     if (!make_map_u8(&map_w, w_i8, N, K, BM) || !make_map_u8(&map_x, xq, (uint64_t)D * Mpad, K, (uint32_t)NB))
         return fail(nullptr, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "qlinear_i8_forward_static: cuTensorMapEncodeTiled failed");
@@ -1142,7 +1158,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_forward_static(const void* w
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: cudaFuncGetAttributes");
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sd.smem_optin - fa.sharedSizeBytes));
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: cudaFuncSetAttribute");
-    e = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, st, map_w, map_x, p);
+    e = launch_pdl(kern, dim3(grid), dim3(64 + 32 * p.epi_warps), smem, st, map_w, map_x, p);
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_forward_static: launch");
     return RUSTY_CUDA_OK;
 }
@@ -1166,7 +1182,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_qlinear_i8_static_status(void* stream) 
         return e == cudaSuccess ? RUSTY_CUDA_OK : check_cuda(nullptr, e, "qlinear_i8_static_status: synchronize");
     }
     rusty_cuda_dev_status h{};
-    e = cudaMemcpyAsync(&h, base + ST_XQ_BYTES + ST_FACTOR_BYTES + ST_SUMS_BYTES + ST_CNT_BYTES, sizeof(h), cudaMemcpyDeviceToHost, st);
+    e = cudaMemcpyAsync(&h, base + ST_XQ_BYTES + ST_FACTOR_BYTES + ST_SUMS_BYTES, sizeof(h), cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return check_cuda(nullptr, e, "qlinear_i8_static_status");
     return static_status_to_code(h.timeout_flag, h.timeout_where);

@@ -167,6 +167,7 @@ bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 uint32_t tc_min_rows();
 int tc_workspace_reserve(rusty_cuda_ctx* ctx);
 void tc_workspace_release(rusty_cuda_ctx* ctx);
+void tc_workspace_clear_pieces(rusty_cuda_ctx* ctx);
 int tc_workspace_check_guards(rusty_cuda_ctx* ctx, cudaError_t* err);
 void tc_workspace_sums(rusty_cuda_ctx* ctx, float** sums, size_t* sums_bytes, unsigned int** counters, size_t* cnt_bytes);
 int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a);

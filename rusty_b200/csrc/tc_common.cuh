@@ -54,6 +54,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         }
     }
 }
+// ---- activations -> signed 7-bit digits --------------------------------------
+// One activation times its row scale (|v| <= 127, exact: the scale is a power of two) -> the integer
+// T = round(v * 128^(D-1)) -> D balanced digits, T = ((d_top * 128 + ...) * 128 + d_0) with d_top in [-127, 127] and
+// the others in [-64, 63].  Returned as bytes: byte i = digit i for i < D-1 (least significant first), byte D-1 = top.
+template <int D>
+__device__ __forceinline__ uint32_t digits_of(float v) {
+    const int t = __float2int_rn(v * (D == 4 ? 2097152.0f : 16384.0f));
+    // bias: every low 7-bit field becomes digit + 64; digit = field - 64 as a byte is the field with bit 6 flipped and
+    // copied into bit 7 (three bit operations for all fields at once)
+    if (D == 4) {
+        const uint32_t u = (uint32_t)(t + (64 + 64 * 128 + 64 * 128 * 128));
+        const uint32_t w = (u & 0x7Fu) | ((u << 1) & 0x7F00u) | ((u << 2) & 0x7F0000u) | ((u << 3) & 0xFF000000u);
+        const uint32_t f = w ^ 0x00404040u;
+        return f | ((f & 0x00404040u) << 1);
+    }
+    const uint32_t u = (uint32_t)(t + (64 + 64 * 128));
+    const uint32_t w = (u & 0x7Fu) | ((u << 1) & 0x7F00u) | ((u << 2) & 0xFF0000u);
+    const uint32_t f = w ^ 0x00004040u;
+    return f | ((f & 0x00004040u) << 1);
+}
+
 // ---- exchange by peer stores ------------------------------------------------
 __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
     unsigned int v;
