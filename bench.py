@@ -275,6 +275,129 @@ def bench_single_linear(ctx, eng, M, K, N, x_dtype, y_dtype, iters, warm, l2_byt
             "gbs": alg_bytes / (ms * 1e-3) / 1e9, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "weight_copies": copies}
 
 
+def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, warmup, clocks=False, e2e_logits=True):
+    """One workload on this process group: the device-timed step (inputs resident in HBM), the end-to-end step (host
+    activations in, rank 0 reads the logits back) and the greedy step (the token chosen on the device).  Returns the
+    max-over-ranks figures; builds and frees its own weights."""
+    from rusty_b200 import DType
+    from rusty_b200.backend import Event, PinnedArray, download_async, upload_async
+    from rusty_b200.stack import LinearStack
+    from rusty_b200.workloads import STACKS
+    shape = STACKS[stack_name]
+    stack = LinearStack(ctx, shape, M, DType.FP32, DType.FP32, seed=0, rank=rank, world=world, layers=args.layers,
+                        swiglu=not args.no_swiglu)
+    if world > 1 and args.exchange != "none":
+        from rusty_b200.shard import PushedStack, ShardedStack
+        runner = PushedStack(stack, dist) if args.exchange == "push" else ShardedStack(stack, dist)
+    else:
+        runner = stack    # "none": every rank runs its shard and nothing is exchanged (a lower bound, not a result)
+    runner.capture()
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(v: float) -> float:
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-timed region: inputs resident in HBM ----
+    for _ in range(warmup):
+        runner.replay()
+    barrier()
+    sampler = ClockSampler(local_rank) if (clocks and rank == 0) else None
+    if sampler:
+        sampler.start()
+    l0 = ctx.launch_count()
+    e0, e1 = Event(ctx), Event(ctx)
+    e0.record()
+    for _ in range(steps):
+        runner.replay()
+    e1.record()
+    ms_total = e0.elapsed_ms(e1)
+    barrier()
+    launches = ctx.launch_count() - l0
+    ms_step = max_over_ranks(ms_total / steps)
+    clk = sampler.stop() if sampler else None
+
+    # ---- end-to-end: host activations in on every rank, host logits out on rank 0, every step ----
+    d_in = shape.d
+    x_host = PinnedArray((M, d_in), np.float32)
+    x_host.array[...] = stack.host_inputs[d_in]
+    e2e = None
+    if e2e_logits:
+        logits_t = runner.full_logits() if hasattr(runner, "full_logits") else stack.logits
+        y_host = PinnedArray((M, logits_t.shape[1]), np.float32)
+
+        def one():
+            upload_async(ctx, stack.inputs[d_in], x_host)
+            runner.replay()
+            if rank == 0:
+                download_async(ctx, logits_t, y_host)
+            ctx.sync()
+        for _ in range(2):
+            one()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            one()
+        e2e_s = max_over_ranks((time.perf_counter() - t0) / steps)
+        barrier()
+        finite = bool(np.isfinite(y_host.array).all()) if rank == 0 else True
+        e2e = {"value": M / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": x_host.nbytes,
+               "d2h_bytes_per_step": y_host.nbytes, "ms_per_step": e2e_s * 1e3, "logits_finite": finite,
+               "readback": "rank 0 reads the [M, vocab] f32 logits; every rank uploads the activations"}
+        y_host.free()
+
+    # ---- the same step ending in one greedy token per row chosen on the device (what a greedy decoder reads back):
+    # N > 1 keeps the LM head's logits local and exchanges arg-max candidates instead ----
+    greedy = None
+    if hasattr(runner, "capture_greedy"):
+        runner.capture_greedy()
+        tok_host = PinnedArray((M,), np.uint32)
+        for _ in range(warmup):
+            runner.greedy_graph.launch()
+        barrier()
+        g0, g1 = Event(ctx), Event(ctx)
+        g0.record()
+        for _ in range(steps):
+            runner.greedy_graph.launch()
+        g1.record()
+        g_ms = max_over_ranks(g0.elapsed_ms(g1) / steps)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            upload_async(ctx, stack.inputs[d_in], x_host)
+            runner.greedy_graph.launch()
+            if rank == 0:
+                download_async(ctx, runner.tokens, tok_host)
+            ctx.sync()
+        g_e2e = max_over_ranks((time.perf_counter() - t0) / steps)
+        barrier()
+        greedy = {"value": M / (g_ms * 1e-3), "unit": "tokens/s", "ms_per_step": g_ms,
+                  "e2e": {"value": M / g_e2e, "unit": "tokens/s", "ms_per_step": g_e2e * 1e3,
+                          "h2d_bytes_per_step": x_host.nbytes, "d2h_bytes_per_step": tok_host.nbytes,
+                          "readback": "rank 0 reads the M tokens"},
+                  "tokens_in_range": bool((tok_host.array < shape.vocab).all())}
+        tok_host.free()
+    x_host.free()
+    out = {"ms_step": ms_step, "launches": int(launches), "clocks": clk, "e2e": e2e, "greedy": greedy,
+           "alg_bytes": stack.algorithmic_bytes(), "weight_gb": stack.weight_bytes() / 1e9, "plans": runner.plans(),
+           "swiglu": bool(stack.swiglu)}
+    if hasattr(runner, "close"):
+        runner.close()
+    del runner, stack
+    import gc
+    gc.collect()
+    ctx.pool_clear()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -283,10 +406,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (for profiling captures only)")
-    ap.add_argument("--no-extras", action="store_true", help="skip the single-Linear and CPU legs")
-    ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-Linear, 70B and CPU legs")
+    ap.add_argument("--no-70b", action="store_true", help="skip the llama2-70b-decode64 extra key")
+    ap.add_argument("--exchange", default="push", choices=["push", "nccl", "none"],
                     help="N > 1: how a rank's output columns reach the other ranks: stores from the kernel's epilogue "
-                         "into every rank's memory (push) or an NCCL all-gather after each Linear (nccl)")
+                         "into every rank's memory (push) or an NCCL all-gather after each Linear (nccl); none = no "
+                         "exchange at all, a diagnostic lower bound whose line is not a benchmark result")
     ap.add_argument("--no-swiglu", action="store_true",
                     help="write gate|up as [M, 2*ffn] instead of applying silu(gate)*up in the kernel's epilogue")
     ap.add_argument("--single", default=None, metavar="MxKxN:f32|bf16",
@@ -333,111 +458,23 @@ def main():
     ctx = rusty_b200.CudaContext(local_rank)
     eng = rusty_b200.ComputeEngine(ctx)
     shape = STACKS[stack_name]
-    stack = LinearStack(ctx, shape, M, DType.FP32, DType.FP32, seed=0, rank=rank, world=world, layers=args.layers,
-                        swiglu=not args.no_swiglu)
-    if world > 1:
-        from rusty_b200.shard import PushedStack, ShardedStack
-        runner = PushedStack(stack, dist) if args.exchange == "push" else ShardedStack(stack, dist)
-    else:
-        runner = stack
-    runner.capture()
-
-    def barrier():
-        ctx.sync()
-        if dist is not None:
-            dist.barrier()
-
-    def max_over_ranks(v: float) -> float:
-        if dist is None:
-            return v
-        import torch
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- device-timed region: inputs resident in HBM ----
-    for _ in range(args.warmup):
-        runner.replay()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    l0 = ctx.launch_count()
-    e0, e1 = Event(ctx), Event(ctx)
-    e0.record()
-    for _ in range(args.steps):
-        runner.replay()
-    e1.record()
-    ms_total = e0.elapsed_ms(e1)
-    barrier()
-    launches = ctx.launch_count() - l0
-    ms_step = max_over_ranks(ms_total / args.steps)
-    clocks = sampler.stop() if rank == 0 else None
-
-    # ---- end-to-end: host activations in, host logits out, every step ----
-    d_in = shape.d
-    x_host = PinnedArray((M, d_in), np.float32)
-    x_host.array[...] = stack.host_inputs[d_in]
-    logits_t = runner.full_logits() if world > 1 else stack.logits
-    y_host = PinnedArray((M, logits_t.shape[1]), np.float32)
-    for _ in range(2):
-        upload_async(ctx, stack.inputs[d_in], x_host)
-        runner.replay()
-        download_async(ctx, logits_t, y_host)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        upload_async(ctx, stack.inputs[d_in], x_host)
-        runner.replay()
-        download_async(ctx, logits_t, y_host)
-        ctx.sync()
-    e2e_s = max_over_ranks((time.perf_counter() - t0) / args.steps)
-    barrier()
-    finite = bool(np.isfinite(y_host.array).all())
-
-    # ---- the same step ending in one greedy token per row chosen on the device (what a greedy decoder reads back):
-    # N > 1 keeps the LM head's logits local and exchanges arg-max candidates instead ----
-    greedy = None
-    if hasattr(runner, "capture_greedy"):
-        runner.capture_greedy()
-        tok_host = PinnedArray((M,), np.uint32)
-        for _ in range(args.warmup):
-            runner.greedy_graph.launch()
-        barrier()
-        g0, g1 = Event(ctx), Event(ctx)
-        g0.record()
-        for _ in range(args.steps):
-            runner.greedy_graph.launch()
-        g1.record()
-        g_ms = max_over_ranks(g0.elapsed_ms(g1) / args.steps)
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            upload_async(ctx, stack.inputs[d_in], x_host)
-            runner.greedy_graph.launch()
-            download_async(ctx, runner.tokens, tok_host)
-            ctx.sync()
-        g_e2e = max_over_ranks((time.perf_counter() - t0) / args.steps)
-        barrier()
-        greedy = {"value": M / (g_ms * 1e-3), "unit": "tokens/s", "ms_per_step": g_ms,
-                  "e2e": {"value": M / g_e2e, "unit": "tokens/s", "ms_per_step": g_e2e * 1e3,
-                          "h2d_bytes_per_step": x_host.nbytes, "d2h_bytes_per_step": tok_host.nbytes},
-                  "tokens_in_range": bool((tok_host.array < shape.vocab).all())}
-        tok_host.free()
+    r = run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, args.steps, args.warmup, clocks=True)
+    ms_step, launches, clocks, e2e, greedy = r["ms_step"], r["launches"], r["clocks"], r["e2e"], r["greedy"]
+    alg_bytes, weight_gb, plans, swiglu = r["alg_bytes"], r["weight_gb"], r["plans"], r["swiglu"]
 
     value = M / (ms_step * 1e-3)
-    alg_bytes = stack.algorithmic_bytes()
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
     line = {
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, M, desc),
-        "impl_detail": {"swiglu_epilogue": bool(stack.swiglu),
+        "impl_detail": {"swiglu_epilogue": swiglu,
                         "parallelism": ("1 GPU" if world == 1 else f"output-feature shards x{world}, " + (
                             "outputs stored into every rank's memory by the kernel epilogue (NVLink peer stores)"
-                            if args.exchange == "push" else "NCCL all-gather after each Linear")),
-                        "weight_gb_per_gpu_per_step": stack.weight_bytes() / 1e9, "kernels": runner.plans()},
+                            if args.exchange == "push" else "NCCL all-gather after each Linear" if args.exchange == "nccl"
+                            else "NOTHING EXCHANGED (diagnostic lower bound, not a result)")),
+                        "weight_gb_per_gpu_per_step": weight_gb, "kernels": plans},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"],
                      # DRAM bytes per step: dram__bytes_read+write of the fused linear captured with ncu on one Linear of
@@ -446,12 +483,23 @@ def main():
                      "traffic": alg_bytes * (59.44 / 61.14) if M > 4 else None, "peak_source": peaks["source"],
                      "algorithmic_bytes_per_step_per_gpu": alg_bytes,
                      "note": "whole step (all launches of the fused linear kernel) / device time, per GPU"},
-        "e2e": {"value": M / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": x_host.nbytes,
-                "d2h_bytes_per_step": y_host.nbytes, "ms_per_step": e2e_s * 1e3, "logits_finite": finite},
+        "e2e": e2e,
         "gpu_launches": int(launches),
         "clocks": clocks,
         "greedy": greedy,
     }
+
+    # The 70B stack's Linears are four times larger, so output-feature sharding pays there first: the same measurement
+    # on llama2-70b-decode64 rides along as an extra key (never the headline).
+    if args.workload == DEFAULT_WORKLOAD and not args.no_extras and not args.no_70b and args.layers is None:
+        sn, m70, d70 = WORKLOADS["llama2-70b-decode64"]
+        r70 = run_stack(ctx, dist, args, sn, m70, rank, world, local_rank, max(3, min(args.steps, 10)), 3)
+        line["llama2_70b_decode64"] = {
+            "workload": "llama2-70b-decode64", "desc": d70, "value": m70 / (r70["ms_step"] * 1e-3), "unit": "tokens/s",
+            "ms_per_step": r70["ms_step"], "n_gpus": world,
+            "frac_of_hbm_peak_per_gpu": r70["alg_bytes"] / (r70["ms_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "e2e": r70["e2e"], "greedy": r70["greedy"], "gpu_launches": r70["launches"],
+            "weight_gb_per_gpu_per_step": r70["weight_gb"]}
 
     if rank == 0 and world == 1 and not args.no_extras:
         # single-Linear figures of the metric: GEMV GB/s, prefill GEMM TFLOP/s
@@ -471,10 +519,6 @@ def main():
                                 "fused_int8_value": cs.tokens_per_s(tf), "sample": cs.describe()}
     if rank == 0:
         print(json.dumps(line), flush=True)
-    x_host.free()
-    y_host.free()
-    if hasattr(runner, "close"):
-        runner.close()
     if dist is not None:
         dist.destroy_process_group()
 

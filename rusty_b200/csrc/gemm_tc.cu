@@ -104,8 +104,8 @@ __global__ void __launch_bounds__(DIG_THREADS, 2) digitize_x_kernel(const XT* __
     PDBG(tid == 0 && blockIdx.x == 0, 1);
     if (push.nranks > 1) {
         // x may hold columns pushed by the other ranks, and the GEMM that follows overwrites their copies of y:
-        // wait until every rank has finished (and delivered) all earlier pushes
-        if (tid == 0) peer_wait_all(push, 30);
+        // meet the other ranks (every rank has finished, and delivered, all earlier pushes)
+        if (tid < 32) peer_sync_block(push, (int)blockIdx.x, 30, blockIdx.x == 0 ? dbg : nullptr);
         __syncthreads();
         PDBG(tid == 0 && blockIdx.x == 0, 3);
     }
@@ -677,10 +677,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         tc_fence_after();
         tmem_dealloc(tmem_base, p.tmem_cols);
     }
-    if (threadIdx.x == 0) {
-        peer_signal_cta_done(p.push);  // after the barrier: every store of this CTA is issued
-        DBG(15);
-    }
+    if (threadIdx.x == 0) DBG(15);
 }
 
 // ----------------------------------------------------------------------------
@@ -891,9 +888,17 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     if (a.push && a.push->nranks > 1) {
         push = *a.push;
     }
+    PeerPush push_pre = push;
+#ifdef RUSTY_TIMELINE
+    {   // development aid: take the exchange apart (1: no meeting of the ranks, 2: no stores into the other ranks)
+        static const int exp_mode = getenv("RUSTY_PEER_EXP") ? atoi(getenv("RUSTY_PEER_EXP")) : 0;
+        if (exp_mode & 1) push_pre = PeerPush{};
+        if (exp_mode & 2) push = PeerPush{};
+    }
+#endif
     {
-        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr)
-                                          : launch_digitize<float>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push, dbg ? dbg + 150 * 16 : nullptr);
+        le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push_pre, dbg ? dbg + 150 * 16 : nullptr)
+                                          : launch_digitize<float>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push_pre, dbg ? dbg + 150 * 16 : nullptr);
         if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
         rc = after_launch(ctx, "digitize_x");
         if (rc) return rc;

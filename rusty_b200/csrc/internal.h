@@ -120,14 +120,20 @@ int launch_affine_dequantize_g64(rusty_cuda_ctx* ctx, const uint8_t* w, const fl
                                  float* out, size_t n);
 
 // Exchange by peer stores (peer.cu): what a kernel needs to write its outputs into the other ranks' copies of y and
-// to tell them so.  Every rank owns an arena with the same layout; rank g's arena is mapped here at peer_base[g].
-//   ctl[0..7]  ctl[g] = CTAs of rank g's pushing kernels whose outputs have landed in THIS arena (added to by rank g)
-//   ctl[16]    epoch: CTAs of this rank's pushing kernels that have finished (local)
+// to keep step with them.  Every rank owns an arena with the same layout; rank g's arena is mapped here at peer_base[g].
+// All ranks enqueue the same sequence of operations on an arena, and every operation BEGINS with a kernel whose blocks
+// (at most PEER_SYNC_SLOTS of them, the same number on every rank) meet their namesakes on the other ranks: block b adds
+// one to cell [rank][b] of every other arena, then waits until cells [g][b] of its own arena have all reached its own
+// count.  A block gets there only after griddepcontrol.wait, i.e. after everything this rank enqueued before has
+// finished and its stores have been performed, so "rank g's block b has arrived" means "what rank g pushed in earlier
+// operations has landed here, and rank g no longer reads what this operation overwrites".
+//   ctl[g * PEER_SYNC_SLOTS + b]               arrivals of rank g's block b (written by rank g)
+//   ctl[PEER_MAX_RANKS * PEER_SYNC_SLOTS + b]  this rank's own count for block b (local)
 constexpr int PEER_MAX_RANKS = 8;
-constexpr int PEER_CTL_EPOCH = 16;
+constexpr int PEER_SYNC_SLOTS = 64;
 struct PeerPush {
     int nranks, rank;                            // nranks <= 1: nothing to push, nothing to wait for
-    unsigned int* ctl;                           // this rank's control block
+    unsigned int* ctl;                           // this rank's control block (PEER_MAX_RANKS + 1) * PEER_SYNC_SLOTS words
     unsigned int* peer_ctl[PEER_MAX_RANKS];      // every rank's control block as mapped in this process (own included)
     long long delta[PEER_MAX_RANKS];             // bytes from an address in this arena to the same place in rank g's
     unsigned long long wait_ns;                  // limit of a wait for the other ranks

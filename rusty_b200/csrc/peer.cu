@@ -7,14 +7,10 @@
 // A rank computes its output columns and stores them into its own y AND into
 // the same place of every other rank's y.  Where the tensor-core kernel runs,
 // that happens in its epilogue (gemm_tc.cu); the other kernels are followed by
-// a copy kernel.  Completion travels as one counter per rank per arena:
-//
-//   * every CTA of a pushing kernel, once its stores have been performed
-//     (system-scope fence), adds one to slot `rank` of every other arena and
-//     to the local epoch;
-//   * the next pushing operation, or rusty_cuda_arena_wait, first waits until
-//     the other ranks' slots in the local arena have reached the local epoch
-//     (all ranks run the same grids, so equal counts mean "same kernels done").
+// a copy kernel.  Ranks keep step at the START of every operation: the first kernel of an operation (the digit
+// pre-pass, the wait kernel) runs after everything this rank enqueued before has completed, tells the other ranks so
+// with one add per rank, and waits for theirs (internal.h, peer_sync_block).  No fence stands between a
+// kernel's stores and its exit: the kernel boundary orders them.
 //
 // All ranks must enqueue the same sequence of pushing operations on an arena.
 // Waits are bounded (RUSTY_PEER_WAIT_MS, default 5000): a rank that never
@@ -37,11 +33,11 @@ constexpr size_t ARENA_CTL_BYTES = 4096;  // control block in front of the data 
 __global__ void peer_wait_kernel(const PeerPush pp) {
     pdl_launch_dependents();
     pdl_wait();
-    if (threadIdx.x == 0) peer_wait_all(pp, 31);
+    peer_sync_block(pp, 0, 31);   // one warp
 }
 
 // Copies rows [0,M) x bytes [0,row_bytes) of a local slice (rows ld_bytes apart) to the same addresses of every
-// other arena, then signals.  VEC = bytes per thread access.
+// other arena.  VEC = bytes per thread access.
 template <int VEC>
 __global__ void __launch_bounds__(256) peer_push_kernel(const uint8_t* __restrict__ src, int M, size_t row_bytes, size_t ld_bytes,
                                                         const PeerPush pp) {
@@ -66,8 +62,7 @@ __global__ void __launch_bounds__(256) peer_push_kernel(const uint8_t* __restric
                 if (g != pp.rank) *reinterpret_cast<uint16_t*>(const_cast<uint8_t*>(s) + pp.delta[g]) = val;
         }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) peer_signal_cta_done(pp);
+    // no signal here: the next operation's first kernel meets the other ranks once this kernel has completed
 }
 
 }  // namespace

@@ -100,21 +100,22 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_rows_push_kernel(const floa
                                                                       uint2* __restrict__ table, int M, const PeerPush pp) {
     pdl_launch_dependents();
     pdl_wait();
-    if (threadIdx.x == 0) peer_wait_all(pp, 32);  // the table of the previous step has been consumed everywhere
+    if (threadIdx.x < 32) peer_sync_block(pp, (int)blockIdx.x, 32);  // the table of the previous step has been consumed everywhere
     __syncthreads();
-    Cand best;
-    bool valid;
-    row_argmax(x + (size_t)blockIdx.x * ld, n, col0, best, valid);
-    if (threadIdx.x == 0) {
-        const uint2 e = make_uint2(__float_as_uint(best.v), valid ? best.i + 1u : 0u);
-        uint2* slot = table + (size_t)pp.rank * M + blockIdx.x;
-        *slot = e;
+    for (int m = blockIdx.x; m < M; m += gridDim.x) {
+        Cand best;
+        bool valid;
+        row_argmax(x + (size_t)m * ld, n, col0, best, valid);
+        if (threadIdx.x == 0) {
+            const uint2 e = make_uint2(__float_as_uint(best.v), valid ? best.i + 1u : 0u);
+            uint2* slot = table + (size_t)pp.rank * M + m;
+            *slot = e;
 #pragma unroll
-        for (int g = 0; g < PEER_MAX_RANKS; ++g)
-            if (g < pp.nranks && g != pp.rank) *reinterpret_cast<uint2*>(reinterpret_cast<char*>(slot) + pp.delta[g]) = e;
+            for (int g = 0; g < PEER_MAX_RANKS; ++g)
+                if (g < pp.nranks && g != pp.rank) *reinterpret_cast<uint2*>(reinterpret_cast<char*>(slot) + pp.delta[g]) = e;
+        }
+        __syncthreads();   // row_argmax reuses its shared scratch
     }
-    __syncthreads();
-    if (threadIdx.x == 0) peer_signal_cta_done(pp);
 }
 
 // Second half: once every rank's candidates have landed, the best of the G candidates of each row.
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(256) argmax_finish_kernel(const uint2* __restr
                                                             float* __restrict__ out_val, const PeerPush pp) {
     pdl_launch_dependents();
     pdl_wait();
-    if (threadIdx.x == 0) peer_wait_all(pp, 33);
+    if (threadIdx.x < 32) peer_sync_block(pp, (int)blockIdx.x, 33);
     __syncthreads();
     for (int m = blockIdx.x * blockDim.x + threadIdx.x; m < M; m += gridDim.x * blockDim.x) {
         Cand c{0.0f, 0u};
@@ -140,8 +141,6 @@ __global__ void __launch_bounds__(256) argmax_finish_kernel(const uint2* __restr
         if (out_val) out_val[m] = ok ? c.v : __int_as_float(0xff800000);
     }
     // counted like a pushing kernel: the next table write of any rank waits until every rank has read this one
-    __syncthreads();
-    if (threadIdx.x == 0) peer_signal_cta_done(pp);
 }
 
 }  // namespace
@@ -185,12 +184,13 @@ int rusty_cuda_argmax_rows_sharded(rusty_cuda_ctx* ctx, rusty_cuda_arena* arena,
     if (M == 0) return RUSTY_CUDA_OK;
     DeviceGuard g(ctx->device);
     const unsigned int col0 = (unsigned int)pp->rank * Nl;
-    cudaError_t e = launch_pdl(argmax_rows_push_kernel, dim3(M), dim3(AM_THREADS), 0, ctx->stream, (const float*)logits_shard->ptr, (int)Nl,
+    cudaError_t e = launch_pdl(argmax_rows_push_kernel, dim3(M < (uint32_t)PEER_SYNC_SLOTS ? M : (uint32_t)PEER_SYNC_SLOTS), dim3(AM_THREADS), 0, ctx->stream, (const float*)logits_shard->ptr, (int)Nl,
                                (size_t)Nl, col0, (uint2*)table->ptr, (int)M, *pp);
     if (e != cudaSuccess) return check_cuda(ctx, e, "argmax_rows_push");
     int rc = after_launch(ctx, "argmax_rows_push");
     if (rc) return rc;
     unsigned blocks = (M + 255) / 256;
+    if (blocks > (unsigned)PEER_SYNC_SLOTS) blocks = PEER_SYNC_SLOTS;
     e = launch_pdl(argmax_finish_kernel, dim3(blocks), dim3(256), 0, ctx->stream, (const uint2*)table->ptr, (int)M, G,
                    (unsigned int*)out_idx->ptr, out_val ? (float*)out_val->ptr : (float*)nullptr, *pp);
     if (e != cudaSuccess) return check_cuda(ctx, e, "argmax_finish");

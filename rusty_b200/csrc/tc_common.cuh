@@ -9,7 +9,7 @@
 
 namespace rusty_tc {
 using rusty::PeerPush;
-using rusty::PEER_CTL_EPOCH;
+using rusty::PEER_SYNC_SLOTS;
 using rusty::PEER_MAX_RANKS;
 
 constexpr long long WAIT_LIMIT_CYCLES = 8000000000ll;  // ~4 s of SM clock
@@ -94,42 +94,48 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Called by ONE thread after everything earlier in the stream has finished (so the local epoch is stable): waits
-// until every rank has signalled that epoch, i.e. the outputs all ranks pushed in earlier operations have landed
-// in this rank's arena and every rank is done reading what the next push may overwrite.  Gives up after
-// pp.wait_ns, records site `site` in the status word and returns false; the caller carries on.
-__device__ __forceinline__ bool peer_wait_all(const PeerPush& pp, unsigned site) {
+// Called by the 32 lanes of ONE warp of block b (b < PEER_SYNC_SLOTS) after griddepcontrol.wait: tells the other ranks
+// that this rank has finished everything before this kernel (its pushed stores included) and waits until the same block
+// of every other rank has said so.  Lane g talks to rank g: one add into its arena, one polled cell of ours, all
+// ranks in parallel.  Gives up after pp.wait_ns, records `site` in the status word and returns false; the caller
+// carries on.  The caller follows it with a block-wide barrier.
+__device__ __forceinline__ bool peer_sync_block(const PeerPush& pp, int b, unsigned site, long long* tl = nullptr) {
     if (pp.nranks <= 1) return true;
-    const unsigned int e = *reinterpret_cast<volatile unsigned int*>(pp.ctl + PEER_CTL_EPOCH);
-    const unsigned long long t0 = globaltimer_ns();
-    for (int g = 0; g < pp.nranks; ++g) {
-        if (g == pp.rank) continue;
-        while ((int)(ld_acquire_sys_u32(pp.ctl + g) - e) < 0) {
+    const int lane = threadIdx.x & 31;
+    unsigned int* mine = pp.ctl + PEER_MAX_RANKS * PEER_SYNC_SLOTS + b;
+    unsigned int c = 0;
+    if (lane == 0) {
+        c = *reinterpret_cast<volatile unsigned int*>(mine) + 1u;   // only this block ever touches its cell
+        *reinterpret_cast<volatile unsigned int*>(mine) = c;
+    }
+    c = __shfl_sync(0xffffffffu, c, 0);
+#ifdef RUSTY_TIMELINE
+    if (tl && lane == 0) tl[4] = (long long)globaltimer_ns();
+#endif
+    bool ok = true;
+    if (lane < pp.nranks && lane != pp.rank) {
+        // What this rank stored before (its pushes included) was performed when the kernels that stored it completed,
+        // which is what let this kernel pass griddepcontrol.wait, so a relaxed add is enough.  (A release here is a
+        // system-scope fence: measured at 3-4 us per operation while the next kernel's weight prefetch is in flight.)
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(pp.peer_ctl[lane] + pp.rank * PEER_SYNC_SLOTS + b) : "memory");
+        const unsigned long long t0 = globaltimer_ns();
+#ifdef RUSTY_TIMELINE
+        if (tl) tl[5] = (long long)t0;
+        int polls = 0;
+#endif
+        while ((int)(ld_acquire_sys_u32(pp.ctl + lane * PEER_SYNC_SLOTS + b) - c) < 0) {
+#ifdef RUSTY_TIMELINE
+            if (tl) tl[6] = ++polls;
+#endif
             if (globaltimer_ns() - t0 > pp.wait_ns) {
                 if (atomicExch(&pp.status->timeout_flag, 1u) == 0u) pp.status->timeout_where = site;
-                return false;
+                ok = false;
+                break;
             }
-            __nanosleep(100);
+            __nanosleep(64);
         }
     }
-    return true;
-}
-// Called by ONE thread of every CTA of a pushing kernel, after a CTA-wide barrier that follows the CTA's last
-// store.  Progress is counted in CTAs: the CTA adds one to slot `rank` of every other arena once its stores have
-// been performed there (system-scope fence), and one to the local epoch.  All ranks run the same grids, so a
-// rank's slot in a peer's arena and that peer's own epoch meet when the rank's kernel has finished.
-__device__ __forceinline__ void peer_signal_cta_done(const PeerPush& pp) {
-    if (pp.nranks <= 1) return;
-    // ONE system-scope release fence orders the adds after this CTA's stores (the CTA-wide barrier before the call
-    // makes the other threads' stores part of what is released); it waits for the round trip of the outstanding
-    // stores (~3.7 us).  The adds themselves are relaxed: with a release on each of them, seven peers cost seven such
-    // waits in a row.  (A sequentially consistent fence, __threadfence_system, cost ~7 us.)
-    asm volatile("fence.acq_rel.sys;" ::: "memory");
-#pragma unroll
-    for (int g = 0; g < PEER_MAX_RANKS; ++g)  // static indices: a run-time index would copy the table to local memory
-        if (g < pp.nranks && g != pp.rank)
-            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(pp.peer_ctl[g] + pp.rank) : "memory");
-    asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" ::"l"(pp.ctl + PEER_CTL_EPOCH) : "memory");
+    return __all_sync(0xffffffffu, ok);
 }
 
 // Programmatic dependent launch: let the next kernel in the stream start its
