@@ -50,8 +50,8 @@ def load_peaks():
 
 class ClockSampler:
     """SM clock and throttle reasons sampled DURING the timed region.  Reads only (no setting is changed): NVML from a
-    thread every 2 ms (the timed region is tens of milliseconds, too short for nvidia-smi's own loop, whose first
-    sample arrives after ~100 ms); nvidia-smi is the fall-back when the NVML binding is missing."""
+    thread every 5 ms (the timed region is tens of milliseconds, too short for nvidia-smi's own loop, whose first
+    sample arrives after ~100 ms; a 2 ms period measurably slowed a 2-GPU step whose ranks wait on one another); nvidia-smi is the fall-back when the NVML binding is missing."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -62,6 +62,7 @@ class ClockSampler:
         self.thread = None
         self.stop_flag = False
         self.sm, self.reasons, self.mx = [], set(), None
+        self.period_s = float(os.environ.get("RUSTY_BENCH_SAMPLE_MS", "5")) * 1e-3
 
     def _nvml_loop(self, nv, h):
         bits = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
@@ -78,21 +79,27 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.002)
+            time.sleep(self.period_s)
 
-    def start(self):
+    def prepare(self):
+        """Everything slow (loading and initialising NVML), done ahead of the timed region."""
         try:
-            import threading
-
             import pynvml as nv
             nv.nvmlInit()
             h = nv.nvmlDeviceGetHandleByIndex(self.idx)
             self.mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
-            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self._nv = (nv, h)
+        except Exception:
+            self._nv = None
+
+    def start(self):
+        if getattr(self, "_nv", "unset") == "unset":
+            self.prepare()
+        if self._nv is not None:
+            import threading
+            self.thread = threading.Thread(target=self._nvml_loop, args=self._nv, daemon=True)
             self.thread.start()
             return
-        except Exception:
-            self.thread = None
         try:
             self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -307,10 +314,14 @@ def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, wa
         return float(t.item())
 
     # ---- device-timed region: inputs resident in HBM ----
-    for _ in range(warmup):
+    sampler = ClockSampler(local_rank) if (clocks and rank == 0) else None
+    if sampler:
+        sampler.prepare()   # NVML start-up takes tens of milliseconds: before the barrier, or the other ranks' clocks
+                            # would count the wait for rank 0 in their first step
+    for _ in range(warmup - 1):
         runner.replay()
     barrier()
-    sampler = ClockSampler(local_rank) if (clocks and rank == 0) else None
+    runner.replay()         # the last warm-up step runs after the barrier: its exchanges line the GPUs up
     if sampler:
         sampler.start()
     l0 = ctx.launch_count()
@@ -360,9 +371,10 @@ def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, wa
     if hasattr(runner, "capture_greedy"):
         runner.capture_greedy()
         tok_host = PinnedArray((M,), np.uint32)
-        for _ in range(warmup):
+        for _ in range(warmup - 1):
             runner.greedy_graph.launch()
         barrier()
+        runner.greedy_graph.launch()
         g0, g1 = Event(ctx), Event(ctx)
         g0.record()
         for _ in range(steps):

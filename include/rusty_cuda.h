@@ -311,6 +311,33 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_pushed_batch(rusty_cuda_ctx* ctx, 
                                                            const rusty_cuda_buf* const* xs, int x_dtype, uint32_t M,
                                                            rusty_cuda_buf* const* ys, int y_dtype);
 
+/* ---- the steps in front of a layer's Linears: Embedding gather and RMSNorm --------
+ * Embedding::forward (rusty-graph/src/lib.rs:121-135): out[t, :] = table[ids[t], :], table f32 [vocab, dim], ids
+ * u32[n_ids] in a DEVICE buffer (the reference copies the whole table to the host on every call and slices it there),
+ * dim % 4 == 0.  An id >= vocab panics in the reference; here its row is written as zeros and the next
+ * rusty_cuda_sync returns RUSTY_CUDA_ERR_INVALID_OPERATION naming the id. */
+RUSTY_CUDA_API int rusty_cuda_embedding_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* table, const rusty_cuda_buf* ids,
+                                            rusty_cuda_buf* out, size_t n_ids, uint32_t vocab, uint32_t dim);
+/* WGSL `rms_norm` (kernels.wgsl:81-102) and `rms_norm_residual` (:570-597), as RMSNorm::forward calls them
+ * (rusty-graph/src/lib.rs:148-170), for EVERY row of x[M, K] (the shader stops after row 0; its residual form treats the
+ * whole tensor as one row):  v = x (+ residual);  out = v * (1 / sqrt(mean(v^2) + eps)) * weight,  f32, K % 4 == 0; the
+ * reference uses eps = 1e-5.  residual may be NULL.  sum_out (may be NULL; needs residual) receives v, the new residual
+ * stream.  The sum of squares is a tree sum in f32 (the shader adds sequentially): a few ulp apart, not bit-identical. */
+RUSTY_CUDA_API int rusty_cuda_rms_norm_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* x, const rusty_cuda_buf* residual,
+                                           const rusty_cuda_buf* weight, rusty_cuda_buf* out, rusty_cuda_buf* sum_out,
+                                           uint32_t M, uint32_t K, float eps);
+/* y = Linear(RMSNorm(x (+ residual)) * norm_weight) in one call: norm1 -> q|k|v and norm2 -> gate|up of
+ * TransformerBlock::forward (rusty-graph/src/lib.rs:365-377).  Where the Linear's kernel prepares its activations in
+ * a pass of its own (3 <= M, K <= 8192, or <= 16384 up to 32 rows) that pass applies the norm to the row it already
+ * holds in registers, so the norm costs no launch and no trip through memory; other shapes run the norm kernel above
+ * first.  x, residual, normed_out, sum_out: f32 [M, K] (K = the Linear's in_features).  normed_out (may be NULL)
+ * receives the normalised activations; sum_out as above.  While a stream capture is open pass normed_out for shapes
+ * that are not fused (no scratch can be allocated then). */
+RUSTY_CUDA_API int rusty_cuda_qlinear_forward_normed(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x,
+                                                     const rusty_cuda_buf* residual, const rusty_cuda_buf* norm_weight, float eps,
+                                                     uint32_t M, rusty_cuda_buf* normed_out, rusty_cuda_buf* sum_out,
+                                                     rusty_cuda_buf* y, int y_dtype);
+
 /* ---- the step after the LM head: greedy token choice on the device -------------
  * Sampler::sample with temperature <= 0 (rusty-loader/src/tokenizer.rs:151-158): per activation row the index of
  * the largest logit, the LAST one among equals, 0 for a row without candidates; NaN never wins (the reference panics

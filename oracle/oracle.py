@@ -246,6 +246,33 @@ def swiglu_pairs(s) -> np.ndarray:
     return out
 
 
+def rms_norm(x, weight, residual=None, eps: float = 1e-5, return_sum: bool = False):
+    """`rms_norm` / `rms_norm_residual` shaders applied to every row of x[M, K] (sequential f32 sums)."""
+    a = np.ascontiguousarray(x, np.float32)
+    M, K = a.reshape(-1, a.shape[-1]).shape
+    w, pw = _f32(np.ravel(weight))
+    assert w.size == K
+    r = None if residual is None else np.ascontiguousarray(residual, np.float32)
+    out = np.empty((M, K), np.float32)
+    sm = np.empty((M, K), np.float32) if (return_sum and r is not None) else None
+    lib().oracle_rms_norm_rows(a.ctypes.data_as(_f32p), r.ctypes.data_as(_f32p) if r is not None else None, pw,
+                               out.ctypes.data_as(_f32p), sm.ctypes.data_as(_f32p) if sm is not None else None,
+                               C.c_uint32(M), C.c_uint32(K), C.c_float(eps))
+    out = out.reshape(a.shape)
+    return (out, sm.reshape(a.shape)) if sm is not None else out
+
+
+def embedding(table, ids):
+    """Embedding::forward: rows of table[vocab, dim] picked by ids; returns (out[n, dim], ids outside the table)."""
+    t = np.ascontiguousarray(table, np.float32)
+    i = np.ascontiguousarray(ids, np.uint32)
+    out = np.empty((i.size, t.shape[1]), np.float32)
+    lib().oracle_embedding.restype = C.c_uint32
+    bad = lib().oracle_embedding(t.ctypes.data_as(_f32p), i.ctypes.data_as(C.POINTER(C.c_uint32)), out.ctypes.data_as(_f32p),
+                                 C.c_size_t(i.size), C.c_uint32(t.shape[0]), C.c_uint32(t.shape[1]))
+    return out, int(bad)
+
+
 def greedy_sample(logits) -> int:
     """Sampler::sample with temperature <= 0: index of the maximum, the last one among equals."""
     a, pa = _f32(np.ravel(logits))

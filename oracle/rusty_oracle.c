@@ -326,6 +326,51 @@ ORACLE_API void oracle_swiglu_pairs(const float* s, float* out, uint32_t M, uint
         }
 }
 
+/* ---- the steps in front of a layer's Linears -------------------------------
+ * WGSL `rms_norm` (rusty-backend/src/kernels.wgsl:87-102), the body the shader runs for row 0, applied to one row:
+ *   ss = 0; for i: ss = ss + x[i]*x[i];  ss = ss / f32(size);  inv_rms = 1.0 / sqrt(ss + 1e-5);
+ *   out[i] = x[i] * inv_rms * weight[i]
+ * and WGSL `rms_norm_residual` (kernels.wgsl:579-597): the same over val = x[i] + residual[i].  Sequential f32
+ * accumulation in index order, as the shader text reads (canonical build: no contraction).  eps is a parameter;
+ * the shaders hard-code 1e-5.  residual and sum_out may be NULL; sum_out receives x + residual. */
+ORACLE_API void oracle_rms_norm_row(const float* x, const float* residual, const float* weight, float* out, float* sum_out,
+                                    uint32_t size, float eps) {
+    float ss = 0.0f;
+    for (uint32_t i = 0; i < size; ++i) {
+        float val = residual ? x[i] + residual[i] : x[i];
+        if (sum_out) sum_out[i] = val;
+        out[i] = val; /* temp store, like the residual shader */
+        ss = ss + val * val;
+    }
+    ss = ss / (float)size;
+    float inv_rms = 1.0f / sqrtf(ss + eps);
+    for (uint32_t i = 0; i < size; ++i) out[i] = out[i] * inv_rms * weight[i];
+}
+
+/* Every row of x[M, K] on its own: what RMSNorm::forward (rusty-graph/src/lib.rs:148-170) means to compute; the
+ * shader as written stops after row 0. */
+ORACLE_API void oracle_rms_norm_rows(const float* x, const float* residual, const float* weight, float* out, float* sum_out,
+                                     uint32_t M, uint32_t K, float eps) {
+    for (uint32_t m = 0; m < M; ++m)
+        oracle_rms_norm_row(x + (size_t)m * K, residual ? residual + (size_t)m * K : NULL, weight, out + (size_t)m * K,
+                            sum_out ? sum_out + (size_t)m * K : NULL, K, eps);
+}
+
+/* Embedding::forward (rusty-graph/src/lib.rs:121-135): out[t, :] = table[ids[t], :].  Returns the number of ids
+ * outside the table (the reference panics on the first; their rows are zeroed here). */
+ORACLE_API uint32_t oracle_embedding(const float* table, const uint32_t* ids, float* out, size_t n_ids, uint32_t vocab, uint32_t dim) {
+    uint32_t bad = 0;
+    for (size_t t = 0; t < n_ids; ++t) {
+        if (ids[t] < vocab) {
+            memcpy(out + t * dim, table + (size_t)ids[t] * dim, (size_t)dim * sizeof(float));
+        } else {
+            memset(out + t * dim, 0, (size_t)dim * sizeof(float));
+            ++bad;
+        }
+    }
+    return bad;
+}
+
 /* ---- the step after the LM head -------------------------------------------
  * Greedy sampling (rusty-loader/src/tokenizer.rs:151-158, temperature <= 0): the index of the maximum logit;
  * Iterator::max_by keeps the LAST of several equal maxima; an empty slice gives 0.  (partial_cmp().unwrap()

@@ -316,6 +316,37 @@ class ComputeEngine:
         total = int(np.prod(out.shape, dtype=np.int64))
         check(lib().rusty_cuda_mul_f32(ctx.handle, a.buffer(), b.buffer(), out.buffer(), total), ctx.handle)
 
+    def rms_norm(self, ctx: CudaContext, input: UnifiedTensor, weight: UnifiedTensor, out: UnifiedTensor,
+                 eps: float = 1e-5) -> None:
+        """ComputeEngine::rms_norm (rusty-backend/src/lib.rs:4492): every row of input[..., K] normalised."""
+        K = int(input.shape[-1])
+        M = int(np.prod(input.shape[:-1], dtype=np.int64))
+        check(lib().rusty_cuda_rms_norm_f32(ctx.handle, input.buffer(), None, weight.buffer(), out.buffer(), None, M, K, eps),
+              ctx.handle)
+
+    def rms_norm_residual(self, ctx: CudaContext, x: UnifiedTensor, residual: UnifiedTensor, weight: UnifiedTensor,
+                          out: UnifiedTensor, sum_out: Optional[UnifiedTensor] = None, eps: float = 1e-5) -> None:
+        """ComputeEngine::rms_norm_residual (rusty-backend/src/lib.rs:5320), row by row; sum_out receives x + residual."""
+        K = int(x.shape[-1])
+        M = int(np.prod(x.shape[:-1], dtype=np.int64))
+        check(lib().rusty_cuda_rms_norm_f32(ctx.handle, x.buffer(), residual.buffer(), weight.buffer(), out.buffer(),
+                                            sum_out.buffer() if sum_out is not None else None, M, K, eps), ctx.handle)
+
+    def embedding(self, ctx: CudaContext, table: UnifiedTensor, ids: UnifiedTensor, out: UnifiedTensor) -> None:
+        """Embedding::forward (rusty-graph/src/lib.rs:121-135) with the ids (u32) already on the device."""
+        vocab, dim = int(table.shape[0]), int(table.shape[1])
+        n = ids.size_in_bytes() // 4
+        check(lib().rusty_cuda_embedding_f32(ctx.handle, table.buffer(), ids.buffer(), out.buffer(), n, vocab, dim), ctx.handle)
+
+    def qlinear_normed(self, ctx: CudaContext, x: UnifiedTensor, norm_weight: UnifiedTensor, w: "QLinear", out: UnifiedTensor,
+                       residual: Optional[UnifiedTensor] = None, normed_out: Optional[UnifiedTensor] = None,
+                       sum_out: Optional[UnifiedTensor] = None, eps: float = 1e-5) -> None:
+        """out = w(RMSNorm(x [+ residual]) * norm_weight): norm1 -> q|k|v, norm2 -> gate|up of a transformer block."""
+        M = int(np.prod(x.shape[:-1], dtype=np.int64))
+        b = lambda t: t.buffer() if t is not None else None
+        check(lib().rusty_cuda_qlinear_forward_normed(ctx.handle, w._h, x.buffer(), b(residual), norm_weight.buffer(), eps, M,
+                                                      b(normed_out), b(sum_out), out.buffer(), int(out.dtype)), ctx.handle)
+
     def argmax_rows(self, ctx: CudaContext, logits: UnifiedTensor, out_idx: UnifiedTensor,
                     out_val: Optional[UnifiedTensor] = None) -> None:
         """Greedy token per row (Sampler::sample with temperature <= 0, rusty-loader/src/tokenizer.rs:151-158):

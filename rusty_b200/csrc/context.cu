@@ -190,6 +190,12 @@ int rusty_cuda_sync(rusty_cuda_ctx* ctx) {
         tc_workspace_clear_pieces(ctx);   // a kernel that gave up may have left pieces of K-cut tiles behind
         return fail(ctx, RUSTY_CUDA_ERR_TIMEOUT, "a bounded device-side wait gave up (site %u)", where);
     }
+    if (ctx->status_host->bad_index_flag) {
+        unsigned id = ctx->status_host->bad_index_value;
+        ctx->status_host->bad_index_flag = 0;
+        ctx->status_host->bad_index_value = 0;
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "embedding: token id %u lies outside the table (its row was written as zeros)", id);
+    }
     return RUSTY_CUDA_OK;
 }
 
@@ -223,6 +229,8 @@ int rusty_cuda_buf_alloc(rusty_cuda_ctx* ctx, size_t bytes, int pooled, rusty_cu
             it->second.pop_back();
         }
     }
+    if (!p && ctx->capturing)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "buf_alloc: no idle pool buffer of %zu bytes, and device memory cannot be allocated while a capture is open", bytes);
     if (!p) {
         // A zero-byte tensor still gets a distinct, valid allocation.
         cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);

@@ -89,11 +89,16 @@ constexpr int DIG_MAXV = 8;   // passes of a row held in registers between the m
 // registers a thread fit beside a GEMM CTA on any SM and cannot fill more than eight.  Rows M..Mpad-1 are written as
 // zeros.  A row of up to 16384 activations (one row per block) stays in registers between its maximum and its digits:
 // one round trip to memory, all loads in flight together.
-template <typename XT, int D>
+//
+// NORM: the activations are RMSNorm(x [+ residual]) * weight (norm_embed.cu gives the formula and its lines in the
+// reference); the row is normalised in registers between the load and the maximum, so it must fit there
+// (K <= DIG_MAXV * 4 * threads of the row), and the normalised row and the sum are written out where asked for.
+template <typename XT, int D, bool NORM>
 __global__ void __launch_bounds__(DIG_THREADS, 2) digitize_x_kernel(const XT* __restrict__ x, int8_t* __restrict__ xq,
                                                                     float* __restrict__ inv_s, int M, int Mpad, int K, int R,
-                                                                    const PeerPush push, long long* dbg) {
+                                                                    const PeerPush push, const NormArgs nrm, long long* dbg) {
     __shared__ float red[DIG_THREADS / 32];
+    __shared__ float red_ss[DIG_THREADS / 32];
     const int tid = threadIdx.x;
     const int tpr = DIG_THREADS / R;               // threads per row (512 or 256)
     const int grp = tid / tpr, tg = tid - grp * tpr;
@@ -122,6 +127,41 @@ __global__ void __launch_bounds__(DIG_THREADS, 2) digitize_x_kernel(const XT* __
     for (int j = 0; j < DIG_MAXV; ++j) {
         const int k = tg * 4 + j * step;
         v[j] = k < K ? load_row4<XT>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if constexpr (NORM) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < DIG_MAXV; ++j) {
+            const int k = tg * 4 + j * step;
+            if (k < K) {
+                if (nrm.residual) {
+                    const float4 r = *reinterpret_cast<const float4*>(nrm.residual + (size_t)m * K + k);
+                    v[j].x += r.x; v[j].y += r.y; v[j].z += r.z; v[j].w += r.w;
+                    if (nrm.sum) *reinterpret_cast<float4*>(nrm.sum + (size_t)m * K + k) = v[j];
+                }
+                ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if ((tid & 31) == 0) red_ss[tid >> 5] = ss;
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(tpr) : "memory");
+        const int wpr_n = tpr / 32;
+        float tot = red_ss[grp * wpr_n + (tid & (wpr_n - 1))];
+        if (wpr_n == 16) tot += __shfl_xor_sync(0xffffffffu, tot, 8);
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, off);
+        const float inv_rms = 1.0f / sqrtf(tot / (float)K + nrm.eps);
+#pragma unroll
+        for (int j = 0; j < DIG_MAXV; ++j) {
+            const int k = tg * 4 + j * step;
+            if (k < K) {
+                const float4 w = __ldg(reinterpret_cast<const float4*>(nrm.weight + k));
+                v[j].x = v[j].x * inv_rms * w.x; v[j].y = v[j].y * inv_rms * w.y;
+                v[j].z = v[j].z * inv_rms * w.z; v[j].w = v[j].w * inv_rms * w.w;
+                if (nrm.normed) *reinterpret_cast<float4*>(nrm.normed + (size_t)m * K + k) = v[j];
+            }
+        }
     }
     float mx = 0.0f;
     auto fold = [&](const float4& f) {
@@ -770,14 +810,21 @@ int pick_digits(int x_dtype, uint32_t rows) {
 
 template <typename XT>
 cudaError_t launch_digitize(cudaStream_t stream, const void* x, int8_t* xq, float* inv_s, int M, int Mpad, int K, int D, const PeerPush& push,
-                            long long* dbg) {
+                            long long* dbg, const NormArgs* norm = nullptr) {
     // Mpad is a multiple of 8 and at most 64: one row per block up to 32 rows, two beyond
     int R = 1;
     while (Mpad / R > DIG_MAX_BLOCKS || Mpad % R != 0) R <<= 1;   // R in {1, 2}: the rows' thread groups share a block evenly
     const int blocks = Mpad / R;
+    if constexpr (std::is_same<XT, float>::value) {
+        if (norm) {
+            if (D == 4)
+                return launch_pdl(digitize_x_kernel<XT, 4, true>, dim3(blocks), dim3(DIG_THREADS), 0, stream, (const XT*)x, xq, inv_s, M, Mpad, K, R, push, *norm, dbg);
+            return launch_pdl(digitize_x_kernel<XT, 3, true>, dim3(blocks), dim3(DIG_THREADS), 0, stream, (const XT*)x, xq, inv_s, M, Mpad, K, R, push, *norm, dbg);
+        }
+    }
     if (D == 4)
-        return launch_pdl(digitize_x_kernel<XT, 4>, dim3(blocks), dim3(DIG_THREADS), 0, stream, (const XT*)x, xq, inv_s, M, Mpad, K, R, push, dbg);
-    return launch_pdl(digitize_x_kernel<XT, 3>, dim3(blocks), dim3(DIG_THREADS), 0, stream, (const XT*)x, xq, inv_s, M, Mpad, K, R, push, dbg);
+        return launch_pdl(digitize_x_kernel<XT, 4, false>, dim3(blocks), dim3(DIG_THREADS), 0, stream, (const XT*)x, xq, inv_s, M, Mpad, K, R, push, NormArgs{}, dbg);
+    return launch_pdl(digitize_x_kernel<XT, 3, false>, dim3(blocks), dim3(DIG_THREADS), 0, stream, (const XT*)x, xq, inv_s, M, Mpad, K, R, push, NormArgs{}, dbg);
 }
 
 }  // namespace
@@ -864,8 +911,17 @@ bool tc_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a) {
 // The kernel pair below stores into the peers' arenas itself, except in the small-batch mode that has no pre-pass.
 bool tc_pushes_fused(uint32_t M) { return M >= tc_min_rows(); }
 
+// The pre-pass normalises a row held in registers: 8 x 4 activations per thread, 512 threads a row up to 32 rows and
+// 256 beyond (two rows share a block).
+bool tc_norm_fused(uint32_t M, uint32_t K) {
+    if (M < (uint32_t)tc_min_rows()) return false;
+    const uint32_t Mpad = (M + 7u) & ~7u;
+    const uint32_t threads_per_row = Mpad > (uint32_t)DIG_MAX_BLOCKS ? DIG_THREADS / 2 : DIG_THREADS;
+    return K % 4 == 0 && K <= (uint32_t)DIG_MAXV * 4u * threads_per_row;
+}
+
 // One launch pair (digitise + GEMM) for up to 64 activation rows.
-static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void* x, void* y, uint32_t rows) {
+static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void* x, void* y, uint32_t rows, const NormArgs* norm) {
     const int M = (int)rows, Mpad = (M + 7) / 8 * 8;
     const int D = pick_digits(a.x_dtype, rows);
     const int NB = (D * Mpad + 15) / 16 * 16;
@@ -897,8 +953,10 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     }
 #endif
     {
+        if (norm && (a.x_dtype != RUSTY_CUDA_F32 || !tc_norm_fused(a.M, a.K)))
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: the norm cannot be applied by this call's pre-pass");
         le = a.x_dtype == RUSTY_CUDA_BF16 ? launch_digitize<__nv_bfloat16>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push_pre, dbg ? dbg + 150 * 16 : nullptr)
-                                          : launch_digitize<float>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push_pre, dbg ? dbg + 150 * 16 : nullptr);
+                                          : launch_digitize<float>(ctx->stream, x, xq, inv_s, M, Mpad, (int)a.K, D, push_pre, dbg ? dbg + 150 * 16 : nullptr, norm);
         if (le != cudaSuccess) return check_cuda(ctx, le, "digitize_x");
         rc = after_launch(ctx, "digitize_x");
         if (rc) return rc;
@@ -995,7 +1053,15 @@ int launch_tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     const size_t xs = a.x_dtype == RUSTY_CUDA_BF16 ? 2 : 4, ys = a.y_dtype == RUSTY_CUDA_BF16 ? 2 : 4;
     for (uint32_t m0 = 0; m0 < a.M; m0 += 64) {
         uint32_t rows = a.M - m0 < 64 ? a.M - m0 : 64;
-        int rc = launch_tc_rows(ctx, a, (const char*)a.x + (size_t)m0 * a.K * xs, (char*)a.y + (size_t)m0 * a.ldy * ys, rows);
+        NormArgs nrm{};
+        if (a.norm) {   // this pass's rows of the norm's operands
+            nrm = *a.norm;
+            const size_t off = (size_t)m0 * a.K;
+            if (nrm.residual) nrm.residual += off;
+            if (nrm.normed) nrm.normed += off;
+            if (nrm.sum) nrm.sum += off;
+        }
+        int rc = launch_tc_rows(ctx, a, (const char*)a.x + (size_t)m0 * a.K * xs, (char*)a.y + (size_t)m0 * a.ldy * ys, rows, a.norm ? &nrm : nullptr);
         if (rc) return rc;
     }
     return RUSTY_CUDA_OK;

@@ -22,6 +22,8 @@
 struct rusty_cuda_dev_status {
     unsigned int timeout_flag;   // != 0: some bounded wait ran out
     unsigned int timeout_where;  // kernel-defined site id of the first give-up
+    unsigned int bad_index_flag; // != 0: a gather met an index outside its table (the row was written as zeros)
+    unsigned int bad_index_value;  // the first such index
 };
 
 struct rusty_cuda_ctx {
@@ -159,7 +161,24 @@ struct QLinearArgs {
     // Non-null: y lies in a peer arena; the kernel also stores every output into the other ranks' arenas and
     // signals them (honoured by the kernels for which qlinear_pushes_fused() is true).
     const PeerPush* push = nullptr;
+    // Non-null: the activations are RMSNorm(x [+ residual]) * weight, computed by the kernel that prepares them for
+    // the tensor cores (honoured where qlinear_norm_fused() is true; x, residual and the outputs are f32 [M, K]).
+    const struct NormArgs* norm = nullptr;
 };
+
+// RMSNorm in front of a Linear (norm_embed.cu has the formula and its reference lines).
+struct NormArgs {
+    const float* residual;  // null: plain RMSNorm of x
+    const float* weight;    // [K]
+    float eps;
+    float* normed;          // null, or where the normalised activations are also written
+    float* sum;             // null, or where x + residual is also written (needs residual)
+};
+int launch_rms_norm(rusty_cuda_ctx* ctx, const float* x, const float* residual, const float* weight, float* out, float* sum_out,
+                    uint32_t M, uint32_t K, float eps);
+// whether the Linear's own activation pre-pass can apply the norm for this call
+bool qlinear_norm_fused(const rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
+bool tc_norm_fused(uint32_t M, uint32_t K);
 
 bool gemv_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 int launch_gemv(rusty_cuda_ctx* ctx, const QLinearArgs& a);
@@ -190,7 +209,7 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
 // Forward into columns [y_col0, y_col0 + N) of a y whose rows are ldy elements apart.
 int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
                          uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0,
-                         const PeerPush* push = nullptr);
+                         const PeerPush* push = nullptr, const NormArgs* norm = nullptr);
 
 }  // namespace rusty
 

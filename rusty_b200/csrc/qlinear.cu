@@ -54,8 +54,13 @@ bool qlinear_pushes_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M,
     return strcmp(qlinear_plan(ql, x_dtype, M, y_dtype), "tcgen05") == 0 && tc_pushes_fused(M);
 }
 
+bool qlinear_norm_fused(const rusty_cuda_ctx*, const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype) {
+    return x_dtype == RUSTY_CUDA_F32 && strcmp(qlinear_plan(ql, x_dtype, M, y_dtype), "tcgen05") == 0 && tc_norm_fused(M, ql->K);
+}
+
 int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
-                         uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0, const PeerPush* push) {
+                         uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0, const PeerPush* push,
+                         const NormArgs* norm) {
     if (!ql || !x || !y) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: null argument");
     if (ql->ctx != ctx) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: object belongs to another context");
     size_t xs = dtype_size(x_dtype), ys = dtype_size(y_dtype);
@@ -95,6 +100,11 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
         if (!qlinear_pushes_fused(ql, x_dtype, M, y_dtype))
             return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: the kernel for this shape does not push to peers");
         a.push = push;
+    }
+    if (norm) {
+        if (!qlinear_norm_fused(ctx, ql, x_dtype, M, y_dtype))
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: the kernel for this shape does not apply a norm");
+        a.norm = norm;
     }
     DeviceGuard g(ctx->device);
     if (!a.act && f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
@@ -189,6 +199,49 @@ int rusty_cuda_qlinear_forward(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql
     RUSTY_REQUIRE_CTX(ctx);
     if (!ql) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: null qlinear");
     return qlinear_forward_cols(ctx, ql, x, x_dtype, M, y, y_dtype, ql->act ? ql->N / 2 : ql->N, 0);
+}
+
+int rusty_cuda_qlinear_forward_normed(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, const rusty_cuda_buf* residual,
+                                      const rusty_cuda_buf* norm_weight, float eps, uint32_t M, rusty_cuda_buf* normed_out, rusty_cuda_buf* sum_out,
+                                      rusty_cuda_buf* y, int y_dtype) {
+    RUSTY_REQUIRE_CTX(ctx);
+    if (!ql || !x || !norm_weight || !y) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_normed: null argument");
+    if (sum_out && !residual) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_normed: sum_out without a residual");
+    if (!(eps >= 0.0f)) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_normed: eps must be >= 0");
+    const uint32_t K = ql->K;
+    if (K % 4 != 0) return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward_normed: K=%u must be a multiple of 4", K);
+    const size_t rows_b = (size_t)M * K * 4;
+    if (x->bytes < rows_b || (residual && residual->bytes < rows_b) || (normed_out && normed_out->bytes < rows_b) || (sum_out && sum_out->bytes < rows_b))
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward_normed: a buffer is smaller than [%u,%u] f32 (%zu bytes)", M, K, rows_b);
+    if (norm_weight->bytes < (size_t)K * 4)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward_normed: norm weight holds %zu bytes, [%u] needs %zu", norm_weight->bytes, K, (size_t)K * 4);
+    if ((normed_out && (normed_out == x || normed_out == residual)) || (sum_out && (sum_out == x || sum_out == normed_out)))
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_normed: normed_out must not alias an input, sum_out must not alias x or normed_out");
+    const uint32_t ldy = ql->act ? ql->N / 2 : ql->N;
+    if (M == 0) return RUSTY_CUDA_OK;
+    if (qlinear_norm_fused(ctx, ql, RUSTY_CUDA_F32, M, y_dtype)) {
+        NormArgs n{residual ? (const float*)residual->ptr : nullptr, (const float*)norm_weight->ptr, eps,
+                   normed_out ? (float*)normed_out->ptr : nullptr, sum_out ? (float*)sum_out->ptr : nullptr};
+        return qlinear_forward_cols(ctx, ql, x, RUSTY_CUDA_F32, M, y, y_dtype, ldy, 0, nullptr, &n);
+    }
+    // Other kernels: the norm as a kernel of its own, into normed_out or into a buffer borrowed from the pool.  The
+    // pool hands a buffer back to later calls on the same stream only, so it can be released as soon as the Linear
+    // that reads it has been enqueued.
+    rusty_cuda_buf* tmp = nullptr;
+    if (!normed_out) {
+        int rc = rusty_cuda_buf_alloc(ctx, rows_b, 1, &tmp);
+        if (rc) return rc;   // (under a stream capture this needs an idle pool buffer of that size: pass normed_out there)
+        normed_out = tmp;
+    }
+    int rc;
+    {
+        DeviceGuard g(ctx->device);
+        rc = launch_rms_norm(ctx, (const float*)x->ptr, residual ? (const float*)residual->ptr : nullptr, (const float*)norm_weight->ptr,
+                             (float*)normed_out->ptr, sum_out ? (float*)sum_out->ptr : nullptr, M, K, eps);
+    }
+    if (!rc) rc = qlinear_forward_cols(ctx, ql, normed_out, RUSTY_CUDA_F32, M, y, y_dtype, ldy, 0);
+    if (tmp) rusty_cuda_buf_release(tmp);
+    return rc;
 }
 
 int rusty_cuda_qlinear_forward_batch(rusty_cuda_ctx* ctx, size_t n, const rusty_cuda_qlinear* const* qls,

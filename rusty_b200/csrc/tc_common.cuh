@@ -10,6 +10,7 @@
 namespace rusty_tc {
 using rusty::PeerPush;
 using rusty::PEER_SYNC_SLOTS;
+using rusty::NormArgs;
 using rusty::PEER_MAX_RANKS;
 
 constexpr long long WAIT_LIMIT_CYCLES = 8000000000ll;  // ~4 s of SM clock

@@ -162,3 +162,37 @@ def test_greedy_sample_and_top_k_tie_rules(oracle):
     assert oracle.greedy_sample(np.array([], np.float32)) == 0
     assert oracle.greedy_sample(np.array([np.nan, -1.0, np.nan], np.float32)) == 1
     assert oracle.top_k(np.array([-2e9, -3e9], np.float32), 1).tolist() == [0]   # nothing beats the -1e9 start: index 0
+
+
+# ---- the steps in front of a layer's Linears (kernels.wgsl:81-102, :570-597; rusty-graph/src/lib.rs:121-135) ----
+def test_rms_norm_follows_the_shader_formula(oracle):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((5, 256)).astype(np.float32)
+    x[2] *= 1e-4
+    x[3, 17] = 500.0
+    r = rng.standard_normal((5, 256)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, 256).astype(np.float32)
+    got = oracle.rms_norm(x, w)
+    exact = x.astype(np.float64) / np.sqrt((x.astype(np.float64) ** 2).mean(-1, keepdims=True) + 1e-5) * w
+    assert np.max(np.abs(got - exact) / np.max(np.abs(exact), axis=1, keepdims=True)) < 1e-6
+    # the shader's own sequence of f32 operations, restated with numpy scalars for one row
+    ss = np.float32(0)
+    for v in x[1]:
+        ss = np.float32(ss + np.float32(v * v))
+    inv = np.float32(1.0) / np.sqrt(np.float32(np.float32(ss / np.float32(256)) + np.float32(1e-5)))
+    assert np.array_equal(got[1], (x[1] * inv) * w)
+    got_r, s = oracle.rms_norm(x, w, residual=r, return_sum=True)
+    assert np.array_equal(s, x + r)
+    assert np.array_equal(got_r, oracle.rms_norm(x + r, w))
+    # a row of zeros stays zero (eps keeps the root away from 0)
+    assert np.array_equal(oracle.rms_norm(np.zeros((1, 8), np.float32), np.ones(8, np.float32)), np.zeros((1, 8), np.float32))
+
+
+def test_embedding_picks_rows(oracle):
+    table = np.arange(40, dtype=np.float32).reshape(10, 4)
+    out, bad = oracle.embedding(table, [9, 0, 3, 3])
+    assert bad == 0 and np.array_equal(out, table[[9, 0, 3, 3]])
+    out, bad = oracle.embedding(table, [10, 2])
+    assert bad == 1 and np.array_equal(out[0], np.zeros(4, np.float32)) and np.array_equal(out[1], table[2])
+    out, bad = oracle.embedding(table, [])
+    assert out.shape == (0, 4) and bad == 0
