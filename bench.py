@@ -31,11 +31,20 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (stack, batch rows M, description)
+    # name: (stack, activation rows M, description[, activation dtype: "f32" (default) or "bf16"])
     "llama3-8b-decode32": ("llama3-8b", 32, "Llama-3-8B-shaped GQA linear stack, random int8 weights, batch-32 decode"),
     "llama7b-decode1": ("llama7b", 1, "Llama-7B-shaped linear stack, random int8 weights, batch-1 decode"),
     "llama2-70b-decode64": ("llama2-70b", 64, "Llama-2-70B-shaped linear stack, random int8 weights, batch-64 decode"),
+    # prefill: every Linear at M = all prompt tokens, bf16 activations in and out, fp32 accumulate (tensor-core bound)
+    "llama3-8b-prefill2048": ("llama3-8b", 2048, "Llama-3-8B-shaped GQA linear stack, random int8 weights, 2048-token prefill", "bf16"),
+    "llama2-70b-prefill8192": ("llama2-70b", 8192, "Llama-2-70B-shaped linear stack, random int8 weights, batch 4 x 2048-token prefill", "bf16"),
 }
+
+
+def workload(name):
+    """(stack, M, description, activation dtype) of a workload."""
+    w = WORKLOADS[name]
+    return w[0], w[1], w[2], (w[3] if len(w) > 3 else "f32")
 DEFAULT_WORKLOAD = "llama3-8b-decode32"
 
 
@@ -157,10 +166,14 @@ class CpuSample:
     dequantised beforehand (untimed, as at its load time); fused = int8 read +
     dequant inside the dot product."""
 
+    MAX_ROWS = 128   # a prefill workload is sampled on this many of its rows (time is linear in rows)
+
     def __init__(self, stack_name: str, M: int):
         from oracle import oracle as O
         from rusty_b200.workloads import STACKS
         self.O = O
+        self.M_full = M
+        M = min(M, self.MAX_ROWS)
         self.M = M
         shape = STACKS[stack_name]
         rng = np.random.default_rng(0)
@@ -197,23 +210,28 @@ class CpuSample:
         return self.M / (seconds_per_sample * self.total_weights / self.sample_weights)
 
     def describe(self) -> str:
-        return ("one layer (q,k,v,o,gate,up,down) at batch %d per step, scaled to the whole stack by weight bytes "
+        rows = "" if self.M == self.M_full else " (%d of the workload's %d rows; time is linear in rows)" % (self.M, self.M_full)
+        return ("one layer (q,k,v,o,gate,up,down) at batch %d%s per step, scaled to the whole stack by weight bytes "
                 "(%d / %d); f32 matmul over pre-dequantised weights = the reference's per-forward work"
-                % (self.M, self.total_weights, self.sample_weights))
+                % (self.M, rows, self.total_weights, self.sample_weights))
 
 
 def workload_config(args, M: int, desc: str) -> dict:
     """The `config` object both arms print: what is computed, not how."""
-    stack_name = WORKLOADS[args.workload][0]
+    stack_name, _m, _d, act = workload(args.workload)
     from rusty_b200.workloads import STACKS
     shape = STACKS[stack_name]
     layers = shape.layers if args.layers is None else args.layers
     return {"workload": args.workload, "desc": desc, "batch_rows": M, "layers": layers,
             "linears_per_step": 4 * layers + 1,
             "weights": "int8 [out,in], f32 scale per output row; q|k|v and gate|up run as one Linear each",
-            "activations": "f32 in, f32 out, fp32 accumulate",
+            "activations": "%s in, %s out, fp32 accumulate" % (act, act),
             "l2": "inputs larger than L2: every step streams all %.2f GB of weights, each layer from its own buffer"
                   % (sum(n * k for _p, n, k in shape.per_layer()) * layers / 1e9 + shape.vocab * shape.d / 1e9)}
+
+
+def metric_name(M: int) -> str:
+    return "decode_tokens_per_s" if M <= 64 else "prefill_tokens_per_s"
 
 
 def run_reference(args, rank: int):
@@ -224,7 +242,7 @@ def run_reference(args, rank: int):
     sample scaled by weight bytes, and both are printed."""
     if rank != 0:
         return
-    stack_name, M, desc = WORKLOADS[args.workload]
+    stack_name, M, desc, act = workload(args.workload)
     cs = CpuSample(stack_name, M)
     for _ in range(args.warmup):
         cs.two_step()
@@ -233,7 +251,7 @@ def run_reference(args, rank: int):
     val = cs.tokens_per_s(t_sample)
     step_s = M / val
     line = {
-        "impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric_name(M), "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, M, desc),
@@ -282,17 +300,20 @@ def bench_single_linear(ctx, eng, M, K, N, x_dtype, y_dtype, iters, warm, l2_byt
             "gbs": alg_bytes / (ms * 1e-3) / 1e9, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "weight_copies": copies}
 
 
-def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, warmup, clocks=False, e2e_logits=True):
+def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, warmup, clocks=False, e2e_logits=True,
+              norms=False, act="f32"):
     """One workload on this process group: the device-timed step (inputs resident in HBM), the end-to-end step (host
     activations in, rank 0 reads the logits back) and the greedy step (the token chosen on the device).  Returns the
     max-over-ranks figures; builds and frees its own weights."""
     from rusty_b200 import DType
-    from rusty_b200.backend import Event, PinnedArray, download_async, upload_async
+    from rusty_b200.backend import Event, PinnedArray, bf16_bits_to_f32, download_async, f32_to_bf16_bits, upload_async
     from rusty_b200.stack import LinearStack
     from rusty_b200.workloads import STACKS
     shape = STACKS[stack_name]
-    stack = LinearStack(ctx, shape, M, DType.FP32, DType.FP32, seed=0, rank=rank, world=world, layers=args.layers,
-                        swiglu=not args.no_swiglu)
+    dt = DType.BF16 if act == "bf16" else DType.FP32
+    npdt = np.uint16 if act == "bf16" else np.float32
+    stack = LinearStack(ctx, shape, M, dt, dt, seed=0, rank=rank, world=world, layers=args.layers,
+                        swiglu=not args.no_swiglu, norms=norms)
     if world > 1 and args.exchange != "none":
         from rusty_b200.shard import PushedStack, ShardedStack
         runner = PushedStack(stack, dist) if args.exchange == "push" else ShardedStack(stack, dist)
@@ -338,18 +359,21 @@ def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, wa
 
     # ---- end-to-end: host activations in on every rank, host logits out on rank 0, every step ----
     d_in = shape.d
-    x_host = PinnedArray((M, d_in), np.float32)
-    x_host.array[...] = stack.host_inputs[d_in]
+    x_host = PinnedArray((M, d_in), npdt)
+    x_host.array[...] = f32_to_bf16_bits(stack.host_inputs[d_in]) if act == "bf16" else stack.host_inputs[d_in]
     e2e = None
     if e2e_logits:
         logits_t = runner.full_logits() if hasattr(runner, "full_logits") else stack.logits
-        y_host = PinnedArray((M, logits_t.shape[1]), np.float32)
+        # decode reads every row's logits back; prefill only the last token's (the one that is sampled from)
+        rows_back = M if M <= 64 else 1
+        y_host = PinnedArray((rows_back, logits_t.shape[1]), npdt)
+        y_off = (M - rows_back) * int(logits_t.shape[1]) * dt.size_bytes()
 
         def one():
             upload_async(ctx, stack.inputs[d_in], x_host)
             runner.replay()
             if rank == 0:
-                download_async(ctx, logits_t, y_host)
+                download_async(ctx, logits_t, y_host, y_off)
             ctx.sync()
         for _ in range(2):
             one()
@@ -359,16 +383,18 @@ def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, wa
             one()
         e2e_s = max_over_ranks((time.perf_counter() - t0) / steps)
         barrier()
-        finite = bool(np.isfinite(y_host.array).all()) if rank == 0 else True
+        yh = bf16_bits_to_f32(y_host.array) if act == "bf16" else y_host.array
+        finite = bool(np.isfinite(yh).all()) if rank == 0 else True
         e2e = {"value": M / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": x_host.nbytes,
                "d2h_bytes_per_step": y_host.nbytes, "ms_per_step": e2e_s * 1e3, "logits_finite": finite,
-               "readback": "rank 0 reads the [M, vocab] f32 logits; every rank uploads the activations"}
+               "readback": "rank 0 reads the [%d, vocab] %s logits%s; every rank uploads the [M, d] activations"
+                           % (rows_back, act, "" if rows_back == M else " of the last token")}
         y_host.free()
 
     # ---- the same step ending in one greedy token per row chosen on the device (what a greedy decoder reads back):
     # N > 1 keeps the LM head's logits local and exchanges arg-max candidates instead ----
     greedy = None
-    if hasattr(runner, "capture_greedy"):
+    if hasattr(runner, "capture_greedy") and act == "f32":
         runner.capture_greedy()
         tok_host = PinnedArray((M,), np.uint32)
         for _ in range(warmup - 1):
@@ -400,6 +426,7 @@ def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, wa
     x_host.free()
     out = {"ms_step": ms_step, "launches": int(launches), "clocks": clk, "e2e": e2e, "greedy": greedy,
            "alg_bytes": stack.algorithmic_bytes(), "weight_gb": stack.weight_bytes() / 1e9, "plans": runner.plans(),
+           "flops": stack.flops(),
            "swiglu": bool(stack.swiglu)}
     if hasattr(runner, "close"):
         runner.close()
@@ -451,8 +478,11 @@ def main():
         print(json.dumps({"single": args.single, **r}), flush=True)
         return
 
-    stack_name, M, desc = WORKLOADS[args.workload]
+    stack_name, M, desc, act = workload(args.workload)
     peaks = load_peaks()
+    prefill = M > 64
+    if prefill and args.steps > 5 and "--steps" not in sys.argv:
+        args.steps = 5   # a prefill step is hundreds of milliseconds
 
     dist = None
     if world > 1:
@@ -470,16 +500,33 @@ def main():
     ctx = rusty_b200.CudaContext(local_rank)
     eng = rusty_b200.ComputeEngine(ctx)
     shape = STACKS[stack_name]
-    r = run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, args.steps, args.warmup, clocks=True)
+    r = run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, args.steps, args.warmup, clocks=True, act=act)
     ms_step, launches, clocks, e2e, greedy = r["ms_step"], r["launches"], r["clocks"], r["e2e"], r["greedy"]
     alg_bytes, weight_gb, plans, swiglu = r["alg_bytes"], r["weight_gb"], r["plans"], r["swiglu"]
 
     value = M / (ms_step * 1e-3)
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    if prefill:
+        # tensor-core bound: 2*M*N*K flops per Linear over the whole step's device time, against the cuBLAS bf16
+        # throughput measured in a seconds-long loop (the step is hundreds of milliseconds of back-to-back GEMMs)
+        tfl = r["flops"] / (ms_step * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": tfl, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                    "frac": tfl / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["source"] + " (sustained)",
+                    "frac_of_burst_peak": tfl / peaks["bf16_tflops"], "flops_per_step_per_gpu": r["flops"],
+                    "note": "whole step (all launches of the bf16 tensor-core linear) / device time, per GPU"}
+    else:
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"],
+                    # DRAM bytes per step: dram__bytes_read+write of the fused linear captured with ncu on one Linear of
+                    # this stack (32 x 4096 x 14336: 59.44 MB for 61.14 MB algorithmic), scaled to the step by
+                    # algorithmic bytes (traffic grows with the weight bytes streamed)
+                    "traffic": alg_bytes * (59.44 / 61.14) if M > 4 else None, "peak_source": peaks["source"],
+                    "algorithmic_bytes_per_step_per_gpu": alg_bytes,
+                    "note": "whole step (all launches of the fused linear kernel) / device time, per GPU"}
     line = {
-        "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": metric_name(M), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "vs_baseline": None, "dtype": act, "data": "synthetic",
         "config": workload_config(args, M, desc),
         "impl_detail": {"swiglu_epilogue": swiglu,
                         "parallelism": ("1 GPU" if world == 1 else f"output-feature shards x{world}, " + (
@@ -487,24 +534,26 @@ def main():
                             if args.exchange == "push" else "NCCL all-gather after each Linear" if args.exchange == "nccl"
                             else "NOTHING EXCHANGED (diagnostic lower bound, not a result)")),
                         "weight_gb_per_gpu_per_step": weight_gb, "kernels": plans},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"],
-                     # DRAM bytes per step: dram__bytes_read+write of the fused linear captured with ncu on one Linear of
-                     # this stack (32 x 4096 x 14336: 59.44 MB for 61.14 MB algorithmic), scaled to the step by
-                     # algorithmic bytes (traffic grows with the weight bytes streamed)
-                     "traffic": alg_bytes * (59.44 / 61.14) if M > 4 else None, "peak_source": peaks["source"],
-                     "algorithmic_bytes_per_step_per_gpu": alg_bytes,
-                     "note": "whole step (all launches of the fused linear kernel) / device time, per GPU"},
+        "roofline": roofline,
         "e2e": e2e,
         "gpu_launches": int(launches),
         "clocks": clocks,
         "greedy": greedy,
     }
 
+    # The block's RMSNorms riding in the Linears that follow them (norm1 -> q|k|v, norm2 + residual -> gate|up, final
+    # norm -> lm_head): the same step with 65 norms added, as an extra key.
+    if world == 1 and not args.no_extras and args.layers is None and not prefill:
+        rn = run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, args.steps, args.warmup, e2e_logits=False, norms=True)
+        line["with_rms_norms"] = {"value": M / (rn["ms_step"] * 1e-3), "unit": "tokens/s", "ms_per_step": rn["ms_step"],
+                                  "gpu_launches": rn["launches"],
+                                  "note": "RMSNorm applied by the pre-pass of q|k|v, gate|up (with residual add) and lm_head; "
+                                          "no norm kernel is launched"}
+
     # The 70B stack's Linears are four times larger, so output-feature sharding pays there first: the same measurement
     # on llama2-70b-decode64 rides along as an extra key (never the headline).
     if args.workload == DEFAULT_WORKLOAD and not args.no_extras and not args.no_70b and args.layers is None:
-        sn, m70, d70 = WORKLOADS["llama2-70b-decode64"]
+        sn, m70, d70, _a = workload("llama2-70b-decode64")
         r70 = run_stack(ctx, dist, args, sn, m70, rank, world, local_rank, max(3, min(args.steps, 10)), 3)
         line["llama2_70b_decode64"] = {
             "workload": "llama2-70b-decode64", "desc": d70, "value": m70 / (r70["ms_step"] * 1e-3), "unit": "tokens/s",
@@ -513,7 +562,7 @@ def main():
             "e2e": r70["e2e"], "greedy": r70["greedy"], "gpu_launches": r70["launches"],
             "weight_gb_per_gpu_per_step": r70["weight_gb"]}
 
-    if rank == 0 and world == 1 and not args.no_extras:
+    if rank == 0 and world == 1 and not args.no_extras and not prefill:
         # single-Linear figures of the metric: GEMV GB/s, prefill GEMM TFLOP/s
         g1 = bench_single_linear(ctx, eng, 1, 4096, 4096, DType.FP32, DType.FP32, 200, 20)
         g2 = bench_single_linear(ctx, eng, 1, 4096, 11008, DType.BF16, DType.BF16, 200, 20)

@@ -54,6 +54,7 @@ struct F16Params {
     float* sums;              // [sk_units][BN/4][128] x float4: f32 sums of cut tiles (zero between uses)
     unsigned int* counters;   // [sk_units] arrivals per cut tile (zero between uses)
     int ldy, y_col0;
+    int act;                  // RUSTY_CUDA_ACT_*: the pair epilogue writes N/2 columns
     uint32_t idesc;
     rusty_cuda_dev_status* status;
 };
@@ -64,6 +65,21 @@ template <>
 __device__ __forceinline__ void store_y<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// One output of activation row m and weight row n (this lane's), already scaled.  Every lane of the warp calls this
+// together.  With the pair activation rows 2j / 2j+1 of the weight are gate_j / up_j (MLP::forward,
+// rusty-graph/src/lib.rs:317-323): the even lane takes its neighbour's value and writes silu(gate) * up into column
+// (y_col0 + n) / 2; silu as kernels.wgsl:104-113.
+template <typename YT>
+__device__ __forceinline__ void store_out(const F16Params& p, YT* y, int m, int n, float v, bool row_ok) {
+    if (p.act) {
+        const float up = __shfl_down_sync(0xffffffffu, v, 1);
+        v = __fdividef(v, 1.0f + __expf(-v)) * up;
+        if (row_ok && m < p.Mx && !(n & 1)) store_y<YT>(y + (size_t)m * p.ldy + ((p.y_col0 + n) >> 1), v);
+    } else if (row_ok && m < p.Mx) {
+        store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, v);
+    }
+}
 
 // 16 int8 (one 128-bit word) -> 8 registers of packed bf16 pairs (low half = even k).
 // u = q ^ 0x80 is q + 128; dropping u into the low mantissa byte of 2^23 and subtracting 2^23 + 128 leaves q
@@ -297,13 +313,8 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     uint32_t v[16];
                     tmem_ld16(taddr + (uint32_t)c0, v);
                     tmem_ld_wait();
-                    if (row_ok) {
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            const int m = j * p.BN + c0 + e;
-                            if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, __uint_as_float(v[e]) * sc);
-                        }
-                    }
+                    for (int e = 0; e < 16; ++e) store_out<YT>(p, y, j * p.BN + c0 + e, n, __uint_as_float(v[e]) * sc, row_ok);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -340,16 +351,11 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
                         for (int e = 0; e < 4; ++e)
                             __stcg(reinterpret_cast<float4*>(tile) + (size_t)(c0 / 4 + e) * BM + r, make_float4(0.f, 0.f, 0.f, 0.f));
-                        if (row_ok) {
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float vals[4] = {f[e].x, f[e].y, f[e].z, f[e].w};
+                        for (int e = 0; e < 4; ++e) {
+                            const float vals[4] = {f[e].x, f[e].y, f[e].z, f[e].w};
 #pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    const int m = j * p.BN + c0 + e * 4 + k;
-                                    if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, vals[k] * sc);
-                                }
-                            }
+                            for (int k = 0; k < 4; ++k) store_out<YT>(p, y, j * p.BN + c0 + e * 4 + k, n, vals[k] * sc, row_ok);
                         }
                     }
                     if (threadIdx.x == 32 * (2 + CONV_WARPS)) p.counters[pc.lu] = 0u;
@@ -393,6 +399,7 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.nws = (p.K + WK - 1) / WK;
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
+    p.act = a.act;
     p.status = ctx->status_dev;
     // bf16 A x bf16 B -> f32: c_format=F32(1)@4, a_format=BF16(1)@7, b_format=BF16(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);

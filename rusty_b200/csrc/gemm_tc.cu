@@ -992,7 +992,14 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     }
     p.bmu = p.tpu * BM;
     p.tiles = (p.N + p.bmu - 1) / p.bmu;
-    plan_tc_schedule(p.tiles, p.kb_total, ctx->sm_count, dp_percent, WS_ACC_BYTES / ((size_t)p.tpu * Mpad * BM * 8), &sc);
+    int sched_sms = ctx->sm_count;
+#ifdef RUSTY_TIMELINE
+    {   // development aid: schedule as if the GPU had fewer SMs (what one SM can stream on its own)
+        static const int sms_env = getenv("RUSTY_TC_SMS") ? atoi(getenv("RUSTY_TC_SMS")) : 0;
+        if (sms_env > 0 && sms_env < sched_sms) sched_sms = sms_env;
+    }
+#endif
+    plan_tc_schedule(p.tiles, p.kb_total, sched_sms, dp_percent, WS_ACC_BYTES / ((size_t)p.tpu * Mpad * BM * 8), &sc);
     int grid = sc.grid;
     p.dp_tiles = sc.dp_tiles;
     p.sk_tiles = sc.sk_tiles;

@@ -42,8 +42,7 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
     a.y_dtype = y_dtype;
     a.M = M;
     a.act = ql->act;
-    // the bf16 prefill kernels have no activation epilogue: batches of pairs go through the int8 kernel in 64-row passes
-    if (!a.act && f16tc_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16";
+    if (f16tc_supported(ql->ctx, a) && M >= f16tc_min_rows()) return "tcgen05_f16";
     if (tc_supported(ql->ctx, a) && M >= tc_min_rows() && (!a.act || tc_pushes_fused(M))) return "tcgen05";
     if (gemv_mma_supported(ql->ctx, a)) return "gemv_mma";
     if (gemv_supported(ql->ctx, a)) return "gemv";
@@ -107,7 +106,7 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
         a.norm = norm;
     }
     DeviceGuard g(ctx->device);
-    if (!a.act && f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
+    if (f16tc_supported(ctx, a) && M >= f16tc_min_rows()) return launch_f16tc(ctx, a);
     if (tc_supported(ctx, a) && M >= tc_min_rows() && (!a.act || tc_pushes_fused(M))) return launch_tc(ctx, a);
     if (gemv_mma_supported(ctx, a)) return launch_gemv_mma(ctx, a);
     if (gemv_supported(ctx, a)) return launch_gemv(ctx, a);

@@ -29,7 +29,7 @@ from .workloads import StackShape
 class LinearStack:
     def __init__(self, ctx: CudaContext, shape: StackShape, M: int, x_dtype: DType = DType.FP32,
                  y_dtype: DType = DType.FP32, seed: int = 0, rank: int = 0, world: int = 1,
-                 layers: Optional[int] = None, fuse: bool = True, swiglu: bool = False):
+                 layers: Optional[int] = None, fuse: bool = True, swiglu: bool = False, norms: bool = False):
         self.ctx, self.shape, self.M = ctx, shape, M
         self.x_dtype, self.y_dtype = x_dtype, y_dtype
         self.rank, self.world = rank, world
@@ -105,6 +105,22 @@ class LinearStack:
         self._xs = [self.inputs[k] for _, k in self.dims]
         self._ys = [self.outputs[-1 if nm == "lm_head" else nl] for nl, nm in zip(self.out_n, self.names)]
         self.graph: Optional[Graph] = None
+        # norms: the RMSNorms of a transformer block ride in the Linears that follow them (TransformerBlock::forward,
+        # rusty-graph/src/lib.rs:365-377; LlamaModel::forward :433-435): norm1 -> q|k|v, norm2 of (x + attention
+        # output) -> gate|up with the sum written back as the new residual stream, the final norm -> lm_head.
+        # One weight vector per norm; the residual is a fixed buffer like the other inputs.
+        self.norms = bool(norms) and fuse and world == 1 and x_dtype == DType.FP32
+        self.norm_w: List[Optional[UnifiedTensor]] = [None] * len(self.qls)
+        self.norm_res: List[Optional[UnifiedTensor]] = [None] * len(self.qls)
+        self.norm_sum: Optional[UnifiedTensor] = None
+        if self.norms:
+            res = UnifiedTensor.new(ctx, (rng.standard_normal((M, shape.d)) * 0.5).astype(np.float32), [M, shape.d])
+            self.norm_sum = UnifiedTensor.empty(ctx, [M, shape.d])
+            for i, name in enumerate(self.names):
+                if name.endswith(".qkv") or name.endswith(".gate_up") or name == "lm_head":
+                    self.norm_w[i] = UnifiedTensor.new(ctx, rng.uniform(0.5, 1.5, size=shape.d).astype(np.float32), [shape.d])
+                    if name.endswith(".gate_up"):
+                        self.norm_res[i] = res
 
     # ---- accounting (algorithmic bytes / flops of ONE step on this rank) ----
     def weight_bytes(self) -> int:
@@ -112,7 +128,11 @@ class LinearStack:
 
     def algorithmic_bytes(self) -> int:
         xs, ys = self.x_dtype.size_bytes(), self.y_dtype.size_bytes()
-        return sum(n * k + n * 4 + self.M * k * xs + self.M * no * ys for (n, k), no in zip(self.dims, self.out_n))
+        b = sum(n * k + n * 4 + self.M * k * xs + self.M * no * ys for (n, k), no in zip(self.dims, self.out_n))
+        for (n, k), w, r in zip(self.dims, self.norm_w, self.norm_res):
+            if w is not None:   # norm weight, and for the residual form the residual read and the sum written
+                b += k * 4 + (2 * self.M * k * 4 if r is not None else 0)
+        return b
 
     def flops(self) -> int:
         return sum(2 * self.M * n * k for n, k in self.dims)
@@ -122,8 +142,16 @@ class LinearStack:
 
     # ---- execution ----
     def step(self) -> None:
-        """Enqueue every Linear of the stack once (one host call)."""
-        qlinear_forward_batch(self.ctx, self.qls, self._xs, self._ys, self.M, self.x_dtype, self.y_dtype)
+        """Enqueue every Linear of the stack once (one host call; one call per Linear when norms ride along)."""
+        if not self.norms:
+            qlinear_forward_batch(self.ctx, self.qls, self._xs, self._ys, self.M, self.x_dtype, self.y_dtype)
+            return
+        eng = ComputeEngine(self.ctx)
+        for ql, x, y, w, r in zip(self.qls, self._xs, self._ys, self.norm_w, self.norm_res):
+            if w is None:
+                eng.qlinear(self.ctx, x, ql, y)
+            else:
+                eng.qlinear_normed(self.ctx, x, w, ql, y, residual=r, sum_out=self.norm_sum if r is not None else None)
 
     def capture(self) -> Graph:
         g = Graph(self.ctx)

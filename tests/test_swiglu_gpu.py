@@ -83,6 +83,29 @@ def test_bf16_in_and_out(ctx, engine, oracle):
     assert rel_err(y.to_vec(ctx).reshape(M, F), _reference(oracle, xr, gq, gs, uq, us)) <= TOL_BF16
 
 
+@pytest.mark.parametrize("M,K,F,ydt", [(128, 1024, 256, DType.BF16), (200, 4096, 192, DType.BF16), (512, 2048, 1000, DType.FP32),
+                                       (65, 512, 64, DType.BF16), (2048, 1024, 7168, DType.BF16)])
+def test_prefill_pairs_on_the_bf16_tensor_core_kernel(ctx, engine, oracle, M, K, F, ydt):
+    """M >= 65 with bf16 activations: the bf16 MMA kernel applies silu(gate) * up in its epilogue (whole tiles and
+    tiles cut along K alike)."""
+    from canary import GuardedOutput
+    from parity import rel_err_rows
+    from rusty_b200.backend import bf16_bits_to_f32, f32_to_bf16_bits
+    x, gq, gs, uq, us = _pairs_case(M + F, M, K, F)
+    xr = bf16_bits_to_f32(f32_to_bf16_bits(x)).reshape(M, K)
+    ql = QLinear.from_gate_up(ctx, gq, gs, uq, us)
+    assert ql.plan(M, DType.BF16, ydt) == "tcgen05_f16"
+    xt = UnifiedTensor.from_bf16(ctx, x, [M, K])
+    g = GuardedOutput(ctx, [M, F], ydt)
+    engine.qlinear(ctx, xt, ql, g.tensor)
+    got = g.read()
+    assert np.isfinite(got).all()
+    # sampled rows at the large shape keep the oracle's share of the run short
+    rows = np.arange(M) if M * F * K <= 2 ** 31 else np.unique(np.concatenate([np.arange(0, M, 37), [M - 1]]))
+    want = _reference(oracle, xr[rows], gq, gs, uq, us)
+    assert rel_err_rows(got[rows], want) <= (TOL_BF16 if ydt == DType.BF16 else 1e-4)
+
+
 def test_shards_of_pairs_give_the_columns_of_the_whole(ctx, engine):
     M, K, F = 32, 1024, 512
     x, gq, gs, uq, us = _pairs_case(5, M, K, F)
