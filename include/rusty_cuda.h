@@ -338,6 +338,16 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_forward_normed(rusty_cuda_ctx* ctx, const 
                                                      uint32_t M, rusty_cuda_buf* normed_out, rusty_cuda_buf* sum_out,
                                                      rusty_cuda_buf* y, int y_dtype);
 
+/* y = residual + Linear(x): `x = x + attn_out` and `x = x + mlp_out` of TransformerBlock::forward
+ * (rusty-graph/src/lib.rs:365-377, ComputeEngine::add after o_proj / down_proj) applied where the Linear's outputs are
+ * rounded (the tensor-core kernels, M >= 3: for f32 outputs fl(residual + fl(out)), bit-identical to Linear followed by
+ * `add`; bf16 outputs are rounded once, after the add); other
+ * shapes run the Linear and one add kernel.  residual: [M, N] of y's type; it may be y itself (the residual stream
+ * updated in place).  Not for a weight that carries the pair activation. */
+RUSTY_CUDA_API int rusty_cuda_qlinear_forward_residual(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x,
+                                                       int x_dtype, uint32_t M, const rusty_cuda_buf* residual,
+                                                       rusty_cuda_buf* y, int y_dtype);
+
 /* ---- the step after the LM head: greedy token choice on the device -------------
  * Sampler::sample with temperature <= 0 (rusty-loader/src/tokenizer.rs:151-158): per activation row the index of
  * the largest logit, the LAST one among equals, 0 for a row without candidates; NaN never wins (the reference panics
@@ -352,6 +362,18 @@ RUSTY_CUDA_API int rusty_cuda_argmax_rows_f32(rusty_cuda_ctx* ctx, const rusty_c
 RUSTY_CUDA_API int rusty_cuda_argmax_rows_sharded(rusty_cuda_ctx* ctx, rusty_cuda_arena* arena,
                                                   const rusty_cuda_buf* logits_shard, uint32_t M, uint32_t Nl,
                                                   rusty_cuda_buf* table, rusty_cuda_buf* out_idx, rusty_cuda_buf* out_val);
+/* The k largest logits of every row: WGSL `top_k` (kernels.wgsl:168-188) for each row of logits[M, N] — descending
+ * values, equal values in ascending index order, values that are not > -1e9 (NaN included) never taken, and slots for
+ * which nothing is left report index 0 (value -inf) as the shader's exhausted rounds do.  1 <= k <= 1024.
+ * out_idx: u32 [M, k]; out_val (may be NULL): f32 [M, k]. */
+RUSTY_CUDA_API int rusty_cuda_top_k_rows_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* logits, uint32_t M, uint32_t N, uint32_t k,
+                                             rusty_cuda_buf* out_idx, rusty_cuda_buf* out_val);
+/* The same over output-feature shards: every rank passes its own columns [M, Nl] (global index = rank * Nl + column);
+ * only k (value, index) pairs per row and rank cross NVLink, every rank ends with the k global winners.
+ * table: a buffer of the arena, nranks * M * k * 8 bytes, at the same offset on every rank.  k * nranks <= 2048. */
+RUSTY_CUDA_API int rusty_cuda_top_k_rows_sharded(rusty_cuda_ctx* ctx, rusty_cuda_arena* arena, const rusty_cuda_buf* logits_shard,
+                                                 uint32_t M, uint32_t Nl, uint32_t k, rusty_cuda_buf* table,
+                                                 rusty_cuda_buf* out_idx, rusty_cuda_buf* out_val);
 
 /* ---- stream capture and timing ---------------------------------------------
  * rusty submits one command buffer per op (lib.rs:4452); a decode step here is

@@ -347,6 +347,14 @@ class ComputeEngine:
         check(lib().rusty_cuda_qlinear_forward_normed(ctx.handle, w._h, x.buffer(), b(residual), norm_weight.buffer(), eps, M,
                                                       b(normed_out), b(sum_out), out.buffer(), int(out.dtype)), ctx.handle)
 
+    def qlinear_residual(self, ctx: CudaContext, x: UnifiedTensor, w: "QLinear", residual: UnifiedTensor,
+                         out: UnifiedTensor) -> None:
+        """out = residual + w(x): the residual add after o_proj / down_proj inside the Linear's epilogue (out may be
+        the residual tensor itself)."""
+        M = int(np.prod(x.shape[:-1], dtype=np.int64))
+        check(lib().rusty_cuda_qlinear_forward_residual(ctx.handle, w._h, x.buffer(), int(x.dtype), M, residual.buffer(),
+                                                        out.buffer(), int(out.dtype)), ctx.handle)
+
     def argmax_rows(self, ctx: CudaContext, logits: UnifiedTensor, out_idx: UnifiedTensor,
                     out_val: Optional[UnifiedTensor] = None) -> None:
         """Greedy token per row (Sampler::sample with temperature <= 0, rusty-loader/src/tokenizer.rs:151-158):
@@ -354,6 +362,14 @@ class ComputeEngine:
         m = int(np.prod(logits.shape[:-1], dtype=np.int64))
         check(lib().rusty_cuda_argmax_rows_f32(ctx.handle, logits.buffer(), m, int(logits.shape[-1]), out_idx.buffer(),
                                                out_val.buffer() if out_val is not None else None), ctx.handle)
+
+    def top_k(self, ctx: CudaContext, input: UnifiedTensor, out_idx: UnifiedTensor, k: int,
+              out_val: Optional[UnifiedTensor] = None) -> None:
+        """ComputeEngine::top_k (rusty-backend/src/lib.rs:4901) for every row of input[..., N]: out_idx u32 [M, k]."""
+        N = int(input.shape[-1])
+        M = int(np.prod(input.shape[:-1], dtype=np.int64))
+        check(lib().rusty_cuda_top_k_rows_f32(ctx.handle, input.buffer(), M, N, k, out_idx.buffer(),
+                                              out_val.buffer() if out_val is not None else None), ctx.handle)
 
     def qlinear(self, ctx: CudaContext, x: UnifiedTensor, w: QLinear, out: UnifiedTensor) -> None:
         """out[M,N] = x[M,K] (.) w, fused dequantise + multiply."""

@@ -100,8 +100,11 @@ SIGNATURES = {
     "rusty_cuda_embedding_f32": ([_vp, _vp, _vp, _vp, _sz, _u32, _u32], _int),
     "rusty_cuda_rms_norm_f32": ([_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float], _int),
     "rusty_cuda_qlinear_forward_normed": ([_vp, _vp, _vp, _vp, _vp, C.c_float, _u32, _vp, _vp, _vp, _int], _int),
+    "rusty_cuda_qlinear_forward_residual": ([_vp, _vp, _vp, _int, _u32, _vp, _vp, _int], _int),
     "rusty_cuda_argmax_rows_f32": ([_vp, _vp, _u32, _u32, _vp, _vp], _int),
     "rusty_cuda_argmax_rows_sharded": ([_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp], _int),
+    "rusty_cuda_top_k_rows_f32": ([_vp, _vp, _u32, _u32, _u32, _vp, _vp], _int),
+    "rusty_cuda_top_k_rows_sharded": ([_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp], _int),
     "rusty_cuda_graph_begin": ([_vp], _int),
     "rusty_cuda_graph_end": ([_vp, _vpp], _int),
     "rusty_cuda_graph_launch": ([_vp, _vp], _int),

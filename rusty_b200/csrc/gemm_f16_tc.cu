@@ -55,6 +55,7 @@ struct F16Params {
     unsigned int* counters;   // [sk_units] arrivals per cut tile (zero between uses)
     int ldy, y_col0;
     int act;                  // RUSTY_CUDA_ACT_*: the pair epilogue writes N/2 columns
+    const void* residual;     // null, or added to every output (same layout as y)
     uint32_t idesc;
     rusty_cuda_dev_status* status;
 };
@@ -65,6 +66,13 @@ template <>
 __device__ __forceinline__ void store_y<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename T>
+__device__ __forceinline__ float load_y(const T* p);
+template <>
+__device__ __forceinline__ float load_y<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load_y<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
 // One output of activation row m and weight row n (this lane's), already scaled.  Every lane of the warp calls this
 // together.  With the pair activation rows 2j / 2j+1 of the weight are gate_j / up_j (MLP::forward,
@@ -77,7 +85,9 @@ __device__ __forceinline__ void store_out(const F16Params& p, YT* y, int m, int 
         v = __fdividef(v, 1.0f + __expf(-v)) * up;
         if (row_ok && m < p.Mx && !(n & 1)) store_y<YT>(y + (size_t)m * p.ldy + ((p.y_col0 + n) >> 1), v);
     } else if (row_ok && m < p.Mx) {
-        store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, v);
+        const size_t at = (size_t)m * p.ldy + p.y_col0 + n;
+        if (p.residual) v += load_y<YT>(reinterpret_cast<const YT*>(p.residual) + at);
+        store_y<YT>(y + at, v);
     }
 }
 
@@ -400,6 +410,7 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
     p.act = a.act;
+    p.residual = a.residual;
     p.status = ctx->status_dev;
     // bf16 A x bf16 B -> f32: c_format=F32(1)@4, a_format=BF16(1)@7, b_format=BF16(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);

@@ -60,6 +60,12 @@ template <>
 __device__ __forceinline__ void store_y<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+template <typename T>
+__device__ __forceinline__ float load_y(const T* p);
+template <>
+__device__ __forceinline__ float load_y<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load_y<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
 // ----------------------------------------------------------------------------
 // Pre-pass: activations -> digit planes.
@@ -222,6 +228,7 @@ struct TcParams {
     ulonglong2* part;        // pieces of tiles cut across CTAs: slot (2*cta + head/tail) x [Mpad/2][128] x 16 bytes = two tagged
                              // int64 (value << 1 | 1: a word is valid as soon as it is not zero); all zero between launches
     void* y;
+    const void* residual;    // null, or added to every output (same layout as y)
     int M, Mpad, D, NB;      // NB = UMMA N = roundup16(D*Mpad)
     int N, K;
     int tpu, bmu;            // row tiles of 128 per work unit (1 or 2: two tiles share every digit tile they multiply), rows per unit
@@ -337,6 +344,7 @@ __device__ __forceinline__ void finalize_store4(const TcParams& p, YT* y, const 
         if (live[k] && !(p.act && (n[k] & 1))) {
             const int col = p.act ? (p.y_col0 + n[k]) >> 1 : p.y_col0 + n[k];
             YT* dst = y + (size_t)m[k] * p.ldy + col;
+            if (p.residual) v[k] += load_y<YT>(reinterpret_cast<const YT*>(p.residual) + ((size_t)m[k] * p.ldy + col));
             store_y<YT>(dst, v[k]);
             // exchange fused into the epilogue: the same element of every other rank's y, over NVLink
             for (int g = 0; g < po.n; ++g) store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<char*>(dst) + po.delta[g]), v[k]);
@@ -1008,6 +1016,7 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.sk_ways = sc.sk_ways;
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
+    p.residual = a.residual ? (const char*)a.residual + ((const char*)y - (const char*)a.y) : nullptr;   // this pass's rows
     p.act = a.act;
     {
         // narrow batches keep the small CTA (two of them fit an SM: the next kernel's CTA prefetches beside this one);

@@ -164,6 +164,9 @@ struct QLinearArgs {
     // Non-null: the activations are RMSNorm(x [+ residual]) * weight, computed by the kernel that prepares them for
     // the tensor cores (honoured where qlinear_norm_fused() is true; x, residual and the outputs are f32 [M, K]).
     const struct NormArgs* norm = nullptr;
+    // Non-null: y = residual + Linear(x); same element type, row stride and column window as y (may be y itself).
+    // Honoured by the tensor-core kernels (qlinear_residual_fused()); never together with the pair activation.
+    const void* residual = nullptr;
 };
 
 // RMSNorm in front of a Linear (norm_embed.cu has the formula and its reference lines).
@@ -179,6 +182,8 @@ int launch_rms_norm(rusty_cuda_ctx* ctx, const float* x, const float* residual, 
 // whether the Linear's own activation pre-pass can apply the norm for this call
 bool qlinear_norm_fused(const rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 bool tc_norm_fused(uint32_t M, uint32_t K);
+int launch_residual_add(rusty_cuda_ctx* ctx, const void* a, const void* b, void* out, size_t n, int y_dtype);
+bool qlinear_residual_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 
 bool gemv_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a);
 int launch_gemv(rusty_cuda_ctx* ctx, const QLinearArgs& a);
@@ -209,7 +214,7 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
 // Forward into columns [y_col0, y_col0 + N) of a y whose rows are ldy elements apart.
 int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
                          uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0,
-                         const PeerPush* push = nullptr, const NormArgs* norm = nullptr);
+                         const PeerPush* push = nullptr, const NormArgs* norm = nullptr, const rusty_cuda_buf* residual = nullptr);
 
 }  // namespace rusty
 

@@ -53,13 +53,18 @@ bool qlinear_pushes_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M,
     return strcmp(qlinear_plan(ql, x_dtype, M, y_dtype), "tcgen05") == 0 && tc_pushes_fused(M);
 }
 
+bool qlinear_residual_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype) {
+    const char* plan = qlinear_plan(ql, x_dtype, M, y_dtype);
+    return !ql->act && (strcmp(plan, "tcgen05") == 0 || strcmp(plan, "tcgen05_f16") == 0);
+}
+
 bool qlinear_norm_fused(const rusty_cuda_ctx*, const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype) {
     return x_dtype == RUSTY_CUDA_F32 && strcmp(qlinear_plan(ql, x_dtype, M, y_dtype), "tcgen05") == 0 && tc_norm_fused(M, ql->K);
 }
 
 int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,
                          uint32_t M, rusty_cuda_buf* y, int y_dtype, uint32_t ldy, uint32_t y_col0, const PeerPush* push,
-                         const NormArgs* norm) {
+                         const NormArgs* norm, const rusty_cuda_buf* residual) {
     if (!ql || !x || !y) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: null argument");
     if (ql->ctx != ctx) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: object belongs to another context");
     size_t xs = dtype_size(x_dtype), ys = dtype_size(y_dtype);
@@ -99,6 +104,13 @@ int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, cons
         if (!qlinear_pushes_fused(ql, x_dtype, M, y_dtype))
             return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: the kernel for this shape does not push to peers");
         a.push = push;
+    }
+    if (residual) {
+        if (!qlinear_residual_fused(ql, x_dtype, M, y_dtype))
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: the kernel for this shape does not add a residual");
+        if (residual->bytes < (size_t)M * ldy * ys)
+            return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward: residual holds %zu bytes, [%u,%u] needs %zu", residual->bytes, M, ldy, (size_t)M * ldy * ys);
+        a.residual = residual->ptr;
     }
     if (norm) {
         if (!qlinear_norm_fused(ctx, ql, x_dtype, M, y_dtype))
@@ -198,6 +210,36 @@ int rusty_cuda_qlinear_forward(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql
     RUSTY_REQUIRE_CTX(ctx);
     if (!ql) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward: null qlinear");
     return qlinear_forward_cols(ctx, ql, x, x_dtype, M, y, y_dtype, ql->act ? ql->N / 2 : ql->N, 0);
+}
+
+int rusty_cuda_qlinear_forward_residual(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype, uint32_t M,
+                                        const rusty_cuda_buf* residual, rusty_cuda_buf* y, int y_dtype) {
+    RUSTY_REQUIRE_CTX(ctx);
+    if (!ql || !x || !residual || !y) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_residual: null argument");
+    if (ql->act) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_forward_residual: not for a weight with the pair activation");
+    const size_t ys = y_dtype == RUSTY_CUDA_BF16 ? 2 : y_dtype == RUSTY_CUDA_F32 ? 4 : 0;
+    if (!ys) return fail(ctx, RUSTY_CUDA_ERR_INVALID_DATA_TYPE, "qlinear_forward_residual: y must be f32 or bf16");
+    const size_t out_b = (size_t)M * ql->N * ys;
+    if (residual->bytes < out_b || y->bytes < out_b)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_forward_residual: residual / y smaller than [%u,%u] (%zu bytes)", M, ql->N, out_b);
+    if (M == 0 || ql->N == 0) return RUSTY_CUDA_OK;
+    if (qlinear_residual_fused(ql, x_dtype, M, y_dtype))
+        return qlinear_forward_cols(ctx, ql, x, x_dtype, M, y, y_dtype, ql->N, 0, nullptr, nullptr, residual);
+    // Other kernels: the Linear into y (or, when the residual IS y, into a buffer borrowed from the pool), then one add.
+    rusty_cuda_buf* tmp = nullptr;
+    rusty_cuda_buf* lin = y;
+    if (residual->ptr == y->ptr) {
+        int rc = rusty_cuda_buf_alloc(ctx, out_b, 1, &tmp);
+        if (rc) return rc;
+        lin = tmp;
+    }
+    int rc = qlinear_forward_cols(ctx, ql, x, x_dtype, M, lin, y_dtype, ql->N, 0);
+    if (!rc) {
+        DeviceGuard g(ctx->device);
+        rc = launch_residual_add(ctx, lin->ptr, residual->ptr, y->ptr, (size_t)M * ql->N, y_dtype);
+    }
+    if (tmp) rusty_cuda_buf_release(tmp);
+    return rc;
 }
 
 int rusty_cuda_qlinear_forward_normed(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, const rusty_cuda_buf* residual,

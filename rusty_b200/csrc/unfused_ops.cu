@@ -14,6 +14,8 @@
 //   * affine_dequantize rounds the multiply and the add separately
 //     (__fmul_rn / __fadd_rn), bit-identical to the uncontracted shader text.
 //   * dequantize is exact integer unpacking.
+#include <cuda_bf16.h>
+
 #include "internal.h"
 
 namespace {
@@ -157,6 +159,18 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ 
     for (; i < n; i += stride) out[i] = __fadd_rn(a[i], b[i]);
 }
 
+// out = a + b with a and out of the output type of a Linear (f32 or bf16): the residual add behind a Linear whose
+// kernel has no epilogue for it.
+template <typename YT>
+__global__ void __launch_bounds__(256) residual_add_kernel(const YT* __restrict__ a, const YT* b, YT* out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        if constexpr (sizeof(YT) == 4) out[i] = __fadd_rn(a[i], b[i]);
+        else out[i] = __float2bfloat16_rn(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+    }
+}
+
 // WGSL `silu` (kernels.wgsl:104-113) and `mul` (kernels.wgsl:146-151), one element per thread as there.
 __global__ void __launch_bounds__(256) silu_f32_kernel(const float* __restrict__ x, float* __restrict__ out, size_t n) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -213,6 +227,17 @@ int launch_affine_dequantize_g64(rusty_cuda_ctx* ctx, const uint8_t* w, const fl
     if (blocks > cap) blocks = cap;
     affine_dequantize_g64_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(w, scales, biases, out, n);
     return after_launch(ctx, "affine_dequantize_g64");
+}
+
+int launch_residual_add(rusty_cuda_ctx* ctx, const void* a, const void* b, void* out, size_t n, int y_dtype) {
+    size_t blocks = (n + 255) / 256, cap = (size_t)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    if (y_dtype == RUSTY_CUDA_BF16)
+        residual_add_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, n);
+    else
+        residual_add_kernel<float><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float*)a, (const float*)b, (float*)out, n);
+    return after_launch(ctx, "residual_add");
 }
 
 }  // namespace rusty

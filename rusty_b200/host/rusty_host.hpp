@@ -200,6 +200,41 @@ public:
         check(rusty_cuda_qlinear_forward(ctx.raw(), w.raw(), x.buffer(), (int)x.dtype, (uint32_t)rows, out.buffer(), (int)out.dtype),
               ctx.raw());
     }
+    // ComputeEngine::rms_norm (rusty-backend/src/lib.rs:4492) for every row of input[..., K]
+    void rms_norm(const CudaContext& ctx, const UnifiedTensor& input, const UnifiedTensor& weight, const UnifiedTensor& out,
+                  float eps = 1e-5f) const {
+        const size_t K = input.shape.back(), rows = numel(input.shape) / K;
+        check(rusty_cuda_rms_norm_f32(ctx.raw(), input.buffer(), nullptr, weight.buffer(), out.buffer(), nullptr, (uint32_t)rows, (uint32_t)K, eps),
+              ctx.raw());
+    }
+    // ComputeEngine::rms_norm_residual (rusty-backend/src/lib.rs:5320), row by row; sum_out (optional) receives x + residual
+    void rms_norm_residual(const CudaContext& ctx, const UnifiedTensor& x, const UnifiedTensor& residual, const UnifiedTensor& weight,
+                           const UnifiedTensor& out, const UnifiedTensor* sum_out = nullptr, float eps = 1e-5f) const {
+        const size_t K = x.shape.back(), rows = numel(x.shape) / K;
+        check(rusty_cuda_rms_norm_f32(ctx.raw(), x.buffer(), residual.buffer(), weight.buffer(), out.buffer(),
+                                      sum_out ? sum_out->buffer() : nullptr, (uint32_t)rows, (uint32_t)K, eps), ctx.raw());
+    }
+    // Embedding::forward (rusty-graph/src/lib.rs:121-135) with the ids (u32) in a device tensor
+    void embedding(const CudaContext& ctx, const UnifiedTensor& table, const UnifiedTensor& ids, size_t n_ids, const UnifiedTensor& out) const {
+        check(rusty_cuda_embedding_f32(ctx.raw(), table.buffer(), ids.buffer(), out.buffer(), n_ids, (uint32_t)table.shape[0],
+                                       (uint32_t)table.shape[1]), ctx.raw());
+    }
+    // out = w(RMSNorm(x [+ residual]) * norm_weight): the norm rides in the Linear's activation pre-pass where it can
+    void qlinear_normed(const CudaContext& ctx, const UnifiedTensor& x, const UnifiedTensor& norm_weight, const QWeight& w,
+                        const UnifiedTensor& out, const UnifiedTensor* residual = nullptr, const UnifiedTensor* normed_out = nullptr,
+                        const UnifiedTensor* sum_out = nullptr, float eps = 1e-5f) const {
+        const size_t rows = numel(x.shape) / x.shape.back();
+        check(rusty_cuda_qlinear_forward_normed(ctx.raw(), w.raw(), x.buffer(), residual ? residual->buffer() : nullptr, norm_weight.buffer(),
+                                                eps, (uint32_t)rows, normed_out ? normed_out->buffer() : nullptr,
+                                                sum_out ? sum_out->buffer() : nullptr, out.buffer(), (int)out.dtype), ctx.raw());
+    }
+    // out = residual + w(x): the residual add after o_proj / down_proj in the Linear's epilogue (out may be residual)
+    void qlinear_residual(const CudaContext& ctx, const UnifiedTensor& x, const QWeight& w, const UnifiedTensor& residual,
+                          const UnifiedTensor& out) const {
+        const size_t rows = numel(x.shape) / x.shape.back();
+        check(rusty_cuda_qlinear_forward_residual(ctx.raw(), w.raw(), x.buffer(), (int)x.dtype, (uint32_t)rows, residual.buffer(),
+                                                  out.buffer(), (int)out.dtype), ctx.raw());
+    }
 };
 
 struct LoRAAdapter {

@@ -208,6 +208,16 @@ def argmax_rows_sharded(ctx: CudaContext, arena: Arena, logits_shard: UnifiedTen
           ctx.handle)
 
 
+def top_k_rows_sharded(ctx: CudaContext, arena: Arena, logits_shard: UnifiedTensor, k: int, table: UnifiedTensor,
+                       out_idx: UnifiedTensor, out_val=None) -> None:
+    """The k largest logits per row over column shards: k (value, index) pairs per row and rank cross NVLink.
+    `table` is an arena buffer of world * M * k * 8 bytes at the same offset on every rank; out_idx is u32[M, k]."""
+    M, Nl = int(np.prod(logits_shard.shape[:-1], dtype=np.int64)), int(logits_shard.shape[-1])
+    check(lib().rusty_cuda_top_k_rows_sharded(ctx.handle, arena._h, logits_shard.buffer(), M, Nl, k, table.buffer(),
+                                              out_idx.buffer(), out_val.buffer() if out_val is not None else None),
+          ctx.handle)
+
+
 class PushedStack:
     """Runs a LinearStack built with (rank, world): every Linear computes this rank's output columns and stores them
     into every rank's copy of the full output (no collective call).  Outputs of equal width share one arena buffer;

@@ -181,3 +181,52 @@ def test_normed_linear_into_pairs_and_bf16_and_a_graph(ctx, engine, oracle):
     engine.qlinear_normed(ctx, tx, tw, ql2, yb)
     got = bf16_bits_to_f32(yb.to_bytes(ctx).view(np.uint16)).reshape(M, 256)
     assert rel_err_rows(got, oracle.qlinear_rowscale(oracle.rms_norm(x, w), q, s)) <= TOL_BF16
+
+
+# ---- residual add in the Linear's epilogue (x = x + o_proj(...), x = x + down_proj(...)) ----
+@pytest.mark.parametrize("M,K,N", [(1, 1024, 256), (2, 4096, 512), (4, 512, 200), (32, 4096, 4096), (64, 2048, 1000), (100, 512, 192)])
+@pytest.mark.parametrize("in_place", [False, True])
+def test_residual_epilogue_equals_linear_then_add_bit_for_bit(ctx, engine, oracle, M, K, N, in_place):
+    rng = np.random.default_rng(M + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    q, s = _linear_case(K + N, M, K, N)
+    res = (rng.standard_normal((M, N)) * 3).astype(np.float32)
+    ql = QLinear.from_host(ctx, q, s)
+    tx = UnifiedTensor.new(ctx, x, [M, K])
+    lin = UnifiedTensor.empty(ctx, [M, N])
+    engine.qlinear(ctx, tx, ql, lin)
+    tr = UnifiedTensor.new(ctx, res, [M, N])
+    want = UnifiedTensor.empty(ctx, [M, N])
+    engine.add(ctx, lin, tr, want)
+    if in_place:
+        engine.qlinear_residual(ctx, tx, ql, tr, tr)
+        got = tr.to_vec(ctx)
+    else:
+        g = GuardedOutput(ctx, [M, N])
+        engine.qlinear_residual(ctx, tx, ql, tr, g.tensor)
+        got = g.read()
+        assert_bits_equal(tr.to_vec(ctx).reshape(M, N), res)       # the residual itself is untouched
+    assert_bits_equal(np.asarray(got).reshape(M, N), want.to_vec(ctx).reshape(M, N))
+    assert rel_err_rows(np.asarray(got).reshape(M, N), res + oracle.qlinear_rowscale(x, q, s)) <= TOL_FP32
+
+
+def test_residual_epilogue_of_the_bf16_prefill_kernel(ctx, engine, oracle):
+    from rusty_b200.backend import f32_to_bf16_bits
+    M, K, N = 300, 1024, 640
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    q, s = _linear_case(4, M, K, N)
+    res = (rng.standard_normal((M, N)) * 3).astype(np.float32)
+    xr = bf16_bits_to_f32(f32_to_bf16_bits(x)).reshape(M, K)
+    rr = bf16_bits_to_f32(f32_to_bf16_bits(res)).reshape(M, N)
+    ql = QLinear.from_host(ctx, q, s)
+    assert ql.plan(M, DType.BF16, DType.BF16) == "tcgen05_f16"
+    tx = UnifiedTensor.from_bf16(ctx, x, [M, K])
+    tr = UnifiedTensor.from_bf16(ctx, res, [M, N])
+    g = GuardedOutput(ctx, [M, N], DType.BF16)
+    engine.qlinear_residual(ctx, tx, ql, tr, g.tensor)
+    assert rel_err_rows(g.read(), rr + oracle.qlinear_rowscale(xr, q, s)) <= TOL_BF16
+    with pytest.raises(BackendError) as e:                         # not together with the pair activation
+        from rusty_b200 import capi
+        engine.qlinear_residual(ctx, tx, QLinear.from_host(ctx, q, s).set_activation(capi.ACT_SWIGLU_PAIRS), tr, g.tensor)
+    assert e.value.kind == "InvalidOperation"

@@ -54,3 +54,67 @@ def test_top_k_shader_differs_only_in_the_tie_rule(oracle):
     """k = 1 of the WGSL top_k takes the FIRST of equal maxima; the sampler takes the last (documented in the header)."""
     x = np.array([1.0, 5.0, 3.0, 5.0, 2.0], np.float32)
     assert oracle.top_k(x, 3).tolist() == [1, 3, 2] and oracle.greedy_sample(x) == 3
+
+
+# ---- k > 1: WGSL `top_k` (rusty-backend/src/kernels.wgsl:168-188) for every row ----
+def _topk(ctx, engine, logits, k):
+    M, N = logits.shape
+    t = UnifiedTensor.new(ctx, logits, [M, N])
+    idx = UnifiedTensor.from_bytes_with_dtype(ctx, np.full(M * k, 0xFFFFFFFF, np.uint32), [M * k * 4], DType.U8)
+    val = UnifiedTensor.new(ctx, np.full(M * k, np.nan, np.float32), [M, k])
+    engine.top_k(ctx, t, idx, k, out_val=val)
+    return idx.to_bytes(ctx).view(np.uint32).reshape(M, k), val.to_vec(ctx).reshape(M, k)
+
+
+@pytest.mark.parametrize("M,N,k", [(1, 10, 3), (3, 1000, 50), (5, 1025, 1), (32, 128256, 50), (2, 2000, 1024), (4, 40, 64),
+                                   (150, 333, 8)])
+def test_top_k_random_rows_match_the_shader(ctx, engine, oracle, M, N, k):
+    logits = np.random.default_rng(M * 31 + N + k).standard_normal((M, N)).astype(np.float32)
+    idx, val = _topk(ctx, engine, logits, k)
+    for m in range(M):
+        want = oracle.top_k(logits[m], k)
+        assert np.array_equal(idx[m], want), (m, idx[m][:8], want[:8])
+        kk = min(k, N)
+        assert np.array_equal(val[m, :kk], logits[m, want[:kk]])
+        assert np.all(np.isneginf(val[m, kk:]))
+
+
+def test_top_k_ties_nan_and_thresholds(ctx, engine, oracle):
+    N, k = 6000, 40
+    rng = np.random.default_rng(1)
+    rows = []
+    rows.append(np.round(rng.standard_normal(N) * 4).astype(np.float32))      # heavy ties: integers in about -16..16
+    rows.append(np.full(N, 2.5, np.float32))                                  # all equal: the first k indices
+    r = rng.standard_normal(N).astype(np.float32)
+    r[::3] = np.nan
+    r[5] = np.inf
+    r[77] = -np.inf
+    rows.append(r)
+    r = np.full(N, -2e9, np.float32)                                          # nothing above the shader's -1e9 start value ...
+    r[[10, 4000, 4001]] = [1.0, -5e8, 1.0]                                    # ... but three
+    rows.append(r)
+    r = rng.standard_normal(N).astype(np.float32)
+    r[[3, 9]] = [0.0, -0.0]                                                   # the two zeros compare equal
+    r[r > 0] = -r[r > 0]
+    rows.append(r)
+    rows.append(np.full(N, np.nan, np.float32))                               # no candidate at all
+    logits = np.stack(rows)
+    idx, val = _topk(ctx, engine, logits, k)
+    for m in range(logits.shape[0]):
+        assert np.array_equal(idx[m], oracle.top_k(logits[m], k)), m
+    assert np.array_equal(idx[1], np.arange(k, dtype=np.uint32))
+    assert np.array_equal(idx[3][:4], np.array([10, 4001, 4000, 0], np.uint32))
+    assert np.all(idx[5] == 0) and np.all(np.isneginf(val[5]))
+
+
+def test_top_k_argument_errors(ctx, engine):
+    from rusty_b200 import BackendError
+    t = UnifiedTensor.zeros(ctx, [2, 16])
+    idx = UnifiedTensor.from_bytes_with_dtype(ctx, np.zeros(8, np.uint32), [32], DType.U8)
+    for k in (0, 1025):
+        with pytest.raises(BackendError) as e:
+            engine.top_k(ctx, t, idx, k)
+        assert e.value.kind == "InvalidDimensions"
+    with pytest.raises(BackendError) as e:
+        engine.top_k(ctx, t, idx, 8)          # 2 x 8 indices do not fit 32 bytes
+    assert e.value.kind == "InvalidDimensions"

@@ -194,6 +194,49 @@ sys.exit(0 if ok else 1)
 '''
 
 
+# The k largest logits over column shards: k (value, index) pairs per row and rank travel; every rank ends with the
+# winners of the whole row, which must equal the single-device kernel's answer on the whole logits.
+_TOPK_SCRIPT = r'''
+import os, sys
+import numpy as np
+sys.path.insert(0, {root!r})
+import torch, torch.distributed as dist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+import rusty_b200
+from rusty_b200 import DType, UnifiedTensor
+from rusty_b200.shard import Arena, top_k_rows_sharded
+ctx = rusty_b200.CudaContext(rank)
+eng = rusty_b200.ComputeEngine(ctx)
+M, N, k = 40, 4096 * world, 50
+Nl = N // world
+arena = Arena(ctx, world * M * k * 8, world, rank)
+arena.connect(dist)
+table = arena.tensor(0, [world * M * k * 8], DType.U8)
+ok = True
+for step in range(3):
+    logits = np.random.default_rng(200 + step).standard_normal((M, N)).astype(np.float32)
+    logits[0] = np.round(logits[0] * 3)      # ties across the shards: ascending index among equals
+    logits[1, :] = np.nan                    # no candidate anywhere
+    logits[2, Nl:] = -2e9                    # every winner lives in rank 0's columns
+    shard = UnifiedTensor.new(ctx, np.ascontiguousarray(logits[:, rank * Nl:(rank + 1) * Nl]), [M, Nl])
+    idx = UnifiedTensor.from_bytes_with_dtype(ctx, np.full(M * k, 0xFFFFFFFF, np.uint32), [M * k * 4], DType.U8)
+    val = UnifiedTensor.new(ctx, np.full(M * k, np.nan, np.float32), [M, k])
+    top_k_rows_sharded(ctx, arena, shard, k, table, idx, val)
+    whole = UnifiedTensor.new(ctx, logits, [M, N])
+    idx1 = UnifiedTensor.from_bytes_with_dtype(ctx, np.full(M * k, 0xFFFFFFFF, np.uint32), [M * k * 4], DType.U8)
+    val1 = UnifiedTensor.new(ctx, np.full(M * k, np.nan, np.float32), [M, k])
+    eng.top_k(ctx, whole, idx1, k, out_val=val1)
+    a, b = idx.to_bytes(ctx).view(np.uint32), idx1.to_bytes(ctx).view(np.uint32)
+    ok = ok and np.array_equal(a, b) and np.array_equal(val.to_vec(ctx).view(np.uint32), val1.to_vec(ctx).view(np.uint32))
+    ok = ok and bool(np.all(a.reshape(M, k)[1] == 0)) and bool(np.all(a.reshape(M, k)[2] < Nl))
+sys.stdout.write("rank %d %s\n" % (rank, "ok" if ok else "MISMATCH")); sys.stdout.flush()
+ctx.sync(); dist.barrier()
+arena.destroy(); ctx.destroy(); dist.destroy_process_group()
+sys.exit(0 if ok else 1)
+'''
+
+
 def _run(world: int, tmp_path, script_text: str = None, extra_env=None):
     script = tmp_path / "rank.py"
     script.write_text((script_text or _RANK_SCRIPT).format(root=ROOT))
@@ -252,3 +295,14 @@ def test_sharded_argmax_two_ranks(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _run(2, tmp_path, _ARGMAX_SCRIPT)
+
+
+def test_sharded_top_k_single_rank(tmp_path):
+    _run(1, tmp_path, _TOPK_SCRIPT)
+
+
+def test_sharded_top_k_two_ranks(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(2, tmp_path, _TOPK_SCRIPT)
