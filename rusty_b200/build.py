@@ -52,6 +52,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
     # RUSTY_TIMELINE=1 in the environment: a development build whose kernels can write %globaltimer stamps
     extra = ["-DRUSTY_TIMELINE"] if os.environ.get("RUSTY_TIMELINE") == "1" else []
     os.makedirs(OBJ, exist_ok=True)
+    # objects built with other flags (a development build before a regular one, or the reverse) are all stale
+    stamp = os.path.join(OBJ, "flags.txt")
+    flags_now = " ".join(NVCC_FLAGS + extra)
+    if not os.path.exists(stamp) or open(stamp).read() != flags_now:
+        force = True
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     hdr_t = _deps_mtime()
     jobs = []
@@ -73,6 +78,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
             if r.returncode:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
+    with open(stamp, "w") as f:
+        f.write(flags_now)
     need_link = force or jobs or not os.path.exists(SO) or not os.path.exists(AR)
     if need_link:
         subprocess.check_call([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", SO] + objs
