@@ -37,11 +37,14 @@ constexpr int A_BUFS = 3;        // converted-weight buffers in tensor memory, 6
 constexpr int A_COLS = WK / 2;   // two 16-bit values per 32-bit column
 constexpr int D_COLS = 256;      // accumulator columns reserved
 constexpr int CONV_WARPS = 8;     // two per TMEM lane quarter, each takes half of a stage's k range
-constexpr int F16_THREADS = 32 * (2 + CONV_WARPS + 4);  // producer, MMA, converter and 4 epilogue warps
+constexpr int EPI_WARPS = 8;      // two per TMEM lane quarter, each drains half of the accumulator's columns: the
+                                  // accumulator is single-buffered, so the drain holds up the next tile's first MMA
+constexpr int F16_THREADS = 32 * (2 + CONV_WARPS + EPI_WARPS);  // producer, MMA, converter and epilogue warps
 constexpr int W_STAGE_BYTES = BM * WK;
 
 struct F16Params {
-    const float* scales;  // [N]
+    const float* scales;  // SYM_ROW: [N], applied to the sums; AFFINE_G64: [N*K/64], applied to the weights as they are converted
+    const float* biases;  // AFFINE_G64: [N*K/64]; null selects SYM_ROW
     void* y;
     int Mx, N, K;
     int BN;               // activation rows per tile (multiple of 16, <= 256)
@@ -110,6 +113,25 @@ __device__ __forceinline__ void int8x16_to_bf16x2(const uint4& w, uint32_t* out)
     }
 }
 
+// The reference's affine layout (WGSL `affine_dequantize`, rusty-backend/src/kernels.wgsl:385-400): w = f32(u8) * scale +
+// bias, one (scale, bias) per 64 consecutive elements.  The product is rounded to bf16 for the tensor core (2^-9
+// relative per weight: inside the 1e-2 tolerance of the bf16 path, not the 1e-5 of the f32 paths).
+__device__ __forceinline__ void u8x16_affine_to_bf16x2(const uint4& w, float sc, float bi, uint32_t* out) {
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t u = words[i];
+        const float f0 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388608.0f, sc, bi);
+        const float f1 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388608.0f, sc, bi);
+        const float f2 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388608.0f, sc, bi);
+        const float f3 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388608.0f, sc, bi);
+        __nv_bfloat162 a = __floats2bfloat162_rn(f0, f1);
+        __nv_bfloat162 b = __floats2bfloat162_rn(f2, f3);
+        out[2 * i] = *reinterpret_cast<uint32_t*>(&a);
+        out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
+    }
+}
+
 // One piece of work: weight stages [s0, s1) of output tile `u`.  nseg > 1: the tile is shared with other CTAs.
 struct Piece {
     int u, s0, s1, nseg, lu;
@@ -154,7 +176,7 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-template <typename YT>
+template <typename YT, bool AFFINE>
 __global__ void __launch_bounds__(F16_THREADS, 1)
 qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const F16Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -188,7 +210,7 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             mbar_init(&a_empty[s], 1);
         }
         mbar_init(d_full, 1);
-        mbar_init(d_empty, 4);
+        mbar_init(d_empty, EPI_WARPS);
         for (int s = 0; s < p.x_stages; ++s) {
             mbar_init(&x_full[s], 1);
             mbar_init(&x_empty[s], 1);
@@ -277,7 +299,18 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         PieceSched sched(p);
         Piece pc;
         while (ok && sched.next(pc)) {
+            const int n_row = (pc.u % p.tiles_w) * BM + r;   // this thread's weight row
             for (int s = pc.s0; s < pc.s1 && ok; ++s) {
+                // affine: this thread's 64 k-elements of the stage are exactly one group of its row (K % 64 == 0)
+                float g_sc = 0.0f, g_bi = 0.0f;
+                if constexpr (AFFINE) {
+                    const int k0 = s * WK + half * 64;
+                    if (n_row < p.N && k0 < p.K) {
+                        const size_t g = ((size_t)n_row * p.K + k0) >> 6;
+                        g_sc = __ldg(p.scales + g);
+                        g_bi = __ldg(p.biases + g);
+                    }
+                }
                 if (!mbar_wait(&w_full[ws], wph, abort_flag, p.status, 16)) { ok = false; break; }
                 // row r of the swizzled tile: logical 16-byte chunk c sits at physical chunk c ^ (r & 7)
                 const uint4* row = reinterpret_cast<const uint4*>(sW + (size_t)ws * W_STAGE_BYTES + (size_t)r * WK);
@@ -288,8 +321,13 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 if (lane == 0) mbar_arrive(&w_empty[ws]);  // this warp's share is in registers
                 if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
                 uint32_t cv[32];
+                if constexpr (AFFINE) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[c], cv + 8 * c);
+                    for (int c = 0; c < 4; ++c) u8x16_affine_to_bf16x2(raw[c], g_sc, g_bi, cv + 8 * c);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) int8x16_to_bf16x2(raw[c], cv + 8 * c);
+                }
                 if (!mbar_wait(&a_empty[ab], aph ^ 1u, abort_flag, p.status, 17)) { ok = false; break; }
                 tc_fence_after();
                 tmem_st32(tmem_a0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * A_COLS + half * 32), cv);
@@ -304,7 +342,12 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         // ------------------------------ epilogue ----------------------------------
         const int q = warp & 3;
         const int r = q * 32 + lane;
+        // this warp's share of the accumulator's columns (activation rows of the tile), in chunks of 16
+        const int c_split = ((p.BN / 2 + 15) / 16) * 16;
+        const int c_lo = (warp - (2 + CONV_WARPS)) >= 4 ? c_split : 0;
+        const int c_hi = (warp - (2 + CONV_WARPS)) >= 4 ? p.BN : c_split;
         YT* y = reinterpret_cast<YT*>(p.y);
+        const bool plain = !p.act && !p.residual;
         pdl_wait();
         bool ok = true;
         int i = 0;
@@ -314,17 +357,27 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const int t = pc.u % p.tiles_w, j = pc.u / p.tiles_w;
             const int n = t * BM + r;
             const bool row_ok = n < p.N;
-            const float sc = row_ok ? __ldg(p.scales + n) : 0.0f;
+            const float sc = !row_ok ? 0.0f : AFFINE ? 1.0f : __ldg(p.scales + n);
             if (!mbar_wait(d_full, (uint32_t)i & 1u, abort_flag, p.status, 18)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
             if (pc.nseg == 1) {
-                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                for (int c0 = c_lo; c0 < c_hi; c0 += 16) {
                     uint32_t v[16];
                     tmem_ld16(taddr + (uint32_t)c0, v);
                     tmem_ld_wait();
+                    if (plain) {   // the common case keeps the shortest code: this loop holds up the next tile's MMAs
+                        if (row_ok) {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) store_out<YT>(p, y, j * p.BN + c0 + e, n, __uint_as_float(v[e]) * sc, row_ok);
+                            for (int e = 0; e < 16; ++e) {
+                                const int m = j * p.BN + c0 + e;
+                                if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, __uint_as_float(v[e]) * sc);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) store_out<YT>(p, y, j * p.BN + c0 + e, n, __uint_as_float(v[e]) * sc, row_ok);
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -333,7 +386,7 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 // a K-slice of a shared tile: add it into the tile's f32 sums ([col/4][row] x float4, so a warp's
                 // vector reductions cover 512 contiguous bytes); the last CTA to arrive writes y.
                 float* tile = p.sums + (size_t)pc.lu * p.BN * BM;
-                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                for (int c0 = c_lo; c0 < c_hi; c0 += 16) {
                     uint32_t v[16];
                     tmem_ld16(taddr + (uint32_t)c0, v);
                     tmem_ld_wait();
@@ -346,31 +399,45 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 __syncwarp();
                 if (lane == 0) mbar_arrive(d_empty);
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
                 if (threadIdx.x == 32 * (2 + CONV_WARPS)) {
                     const unsigned prev = atomicAdd(p.counters + pc.lu, 1u);
                     *last_flag = (prev == (unsigned)(pc.nseg - 1)) ? 1 : 0;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
                 if (*last_flag) {
                     __threadfence();
-                    for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                    for (int c0 = c_lo; c0 < c_hi; c0 += 16) {
                         float4 f[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) f[e] = __ldcg(reinterpret_cast<const float4*>(tile) + (size_t)(c0 / 4 + e) * BM + r);
 #pragma unroll
                         for (int e = 0; e < 4; ++e)
                             __stcg(reinterpret_cast<float4*>(tile) + (size_t)(c0 / 4 + e) * BM + r, make_float4(0.f, 0.f, 0.f, 0.f));
+                        if (plain) {
+                            if (row_ok) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float vals[4] = {f[e].x, f[e].y, f[e].z, f[e].w};
+                                for (int e = 0; e < 4; ++e) {
+                                    const float vals[4] = {f[e].x, f[e].y, f[e].z, f[e].w};
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) store_out<YT>(p, y, j * p.BN + c0 + e * 4 + k, n, vals[k] * sc, row_ok);
+                                    for (int k = 0; k < 4; ++k) {
+                                        const int m = j * p.BN + c0 + e * 4 + k;
+                                        if (m < p.Mx) store_y<YT>(y + (size_t)m * p.ldy + p.y_col0 + n, vals[k] * sc);
+                                    }
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float vals[4] = {f[e].x, f[e].y, f[e].z, f[e].w};
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) store_out<YT>(p, y, j * p.BN + c0 + e * 4 + k, n, vals[k] * sc, row_ok);
+                            }
                         }
                     }
                     if (threadIdx.x == 32 * (2 + CONV_WARPS)) p.counters[pc.lu] = 0u;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
             }
         }
     }
@@ -389,7 +456,8 @@ namespace rusty {
 
 bool f16tc_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
     if (!encode_tiled_fn()) return false;
-    if (a.layout != RUSTY_CUDA_LAYOUT_NK || a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
+    if (a.layout != RUSTY_CUDA_LAYOUT_NK) return false;
+    if (a.qmode == RUSTY_CUDA_QMODE_AFFINE_G64 ? (a.K % 64 != 0 || a.act) : a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
     if (a.x_dtype != RUSTY_CUDA_BF16) return false;
     if (a.K % 16 != 0) return false;
     if ((reinterpret_cast<uintptr_t>(a.w) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return false;
@@ -399,6 +467,7 @@ bool f16tc_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
 int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     F16Params p{};
     p.scales = a.scales;
+    p.biases = a.qmode == RUSTY_CUDA_QMODE_AFFINE_G64 ? a.biases : nullptr;
     p.y = a.y;
     p.Mx = (int)a.M;
     p.N = (int)a.N;
@@ -453,11 +522,19 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
         }
     }
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
-    auto kern = yb ? qlinear_f16_tc_kernel<__nv_bfloat16> : qlinear_f16_tc_kernel<float>;
+    const bool affine = p.biases != nullptr;
+    auto kern = affine ? (yb ? qlinear_f16_tc_kernel<__nv_bfloat16, true> : qlinear_f16_tc_kernel<float, true>)
+                       : (yb ? qlinear_f16_tc_kernel<__nv_bfloat16, false> : qlinear_f16_tc_kernel<float, false>);
     {
         cudaError_t e = ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_f16_tc: cudaFuncSetAttribute");
     }
+#ifdef RUSTY_TIMELINE
+    {   // development aid: what the launch would take if the epilogue stored nothing (results are then invalid)
+        static const bool nostore = getenv("RUSTY_F16_NOSTORE") != nullptr;
+        if (nostore) p.Mx = 0;
+    }
+#endif
     cudaError_t le = launch_pdl(kern, dim3(grid), dim3(F16_THREADS), smem, ctx->stream, map_w, map_x, p);
     if (le != cudaSuccess) return check_cuda(ctx, le, "qlinear_f16_tc");
     return after_launch(ctx, "qlinear_f16_tc");

@@ -374,6 +374,33 @@ def test_tc_nonfinite_activation_poisons_its_row_only(ctx, engine):
 
 # ---- prefill path: fp16 weights in tensor memory x bf16 activations ----
 
+@pytest.mark.parametrize("M,K,N", [(128, 512, 256), (300, 4096, 1000), (96, 192, 24), (2048, 4096, 512), (65, 64, 8)])
+def test_prefill_affine_g64_on_the_bf16_kernel(ctx, engine, oracle, M, K, N):
+    """The reference's own layout (u8, scale and bias per 64 elements) with bf16 activations at M >= 65: the converter
+    warps of the tensor-core kernel apply scale and bias while converting, the product rounded to bf16 (tolerance
+    1e-2, as for every path that rounds to bf16; the f32 paths keep 1e-5 on the CUDA-core kernel)."""
+    x, q, _ = sym_row_linear(3 * K + N + M, M, K, N)
+    rng = np.random.default_rng(K + N)
+    u = (q.astype(np.int16) + 128).astype(np.uint8)
+    sg = rng.uniform(0.001, 0.02, size=N * K // 64).astype(np.float32)
+    bg = (np.float32(-128.0) * sg * rng.uniform(0.9, 1.1, size=N * K // 64)).astype(np.float32)   # zero point near 128, not on it
+    ql = QLinear.from_host(ctx, u, sg, bg)
+    assert ql.plan(M, DType.BF16, DType.BF16) == "tcgen05_f16"
+    xb = bf16_bits_to_f32(f32_to_bf16_bits(x))
+    got32 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.FP32)
+    got16 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.BF16)
+    wf = oracle.affine_dequantize(u, sg, bg, mt=True).reshape(N, K)
+    rows = slice(None) if M * N * K < 3e9 else [0, 1, M // 2, M - 1]
+    ref = oracle.matmul_bt(xb[rows], wf, mt=True)
+    assert np.isfinite(got32).all()
+    assert rel_err_rows(got32[rows], ref) <= TOL_BF16
+    assert rel_err_rows(got16[rows], ref) <= TOL_BF16
+    # the weights really are rounded to bf16 and nothing else: against that model the f32 output is tight
+    wb = bf16_bits_to_f32(f32_to_bf16_bits(wf)).reshape(N, K)
+    assert rel_err(got32[rows], xb[rows].astype(np.float64) @ wb.astype(np.float64).T) <= 5e-4   # (fused multiply-add on the device, separate multiply and add in the oracle: a few bf16 roundings differ)
+    # f32 activations keep the exact CUDA-core kernel
+    assert ql.plan(M, DType.FP32, DType.FP32) == "gemv"
+
 @pytest.mark.parametrize("M,K,N", [(128, 512, 256), (512, 4096, 1024), (200, 1024, 130), (96, 4096, 4096), (300, 80, 24),
                                    (512, 4096, 11008)])
 def test_prefill_f16_shapes(ctx, engine, oracle, M, K, N):
