@@ -280,14 +280,19 @@ RUSTY_CUDA_API int rusty_cuda_qlinear_set_activation(rusty_cuda_qlinear* ql, int
  * allocation with the same layout on every rank (one process per GPU, one node);
  * ranks swap the 64-byte handles over any host channel and attach.
  *
- * Protocol: every rank enqueues the same sequence of pushed forwards on an
- * arena.  y_full of a pushed forward is complete on this rank once the next
- * pushed forward on the arena, or rusty_cuda_arena_wait, has run; it may be
+ * Protocol: every rank enqueues the same sequence of pushed operations on an
+ * arena (pushed forwards, rusty_cuda_arena_wait, the sharded arg-max / top-k);
+ * the ranks meet at the START of each one: its first kernel tells the other
+ * ranks that everything this rank enqueued before has completed and waits for
+ * the same word from them.  y_full of a pushed forward is therefore complete on
+ * this rank once the next pushed operation on the arena has run; it may be
  * read until the following pushed forward is enqueued and may be the output of
  * a pushed forward again from the second-next on.  Waits for other ranks are
  * bounded (environment RUSTY_PEER_WAIT_MS, default 5000): when one runs out,
  * the next rusty_cuda_sync returns RUSTY_CUDA_ERR_TIMEOUT and the context stays
- * usable.  Keep an arena alive until every rank has stopped pushing to it. */
+ * usable; the arena's ranks are then out of step, so destroy it on every rank
+ * and build a new one before pushing again.  Keep an arena alive until every
+ * rank has stopped pushing to it. */
 #define RUSTY_CUDA_IPC_HANDLE_BYTES 64
 typedef struct rusty_cuda_arena rusty_cuda_arena;
 RUSTY_CUDA_API int rusty_cuda_arena_create(rusty_cuda_ctx* ctx, size_t bytes, int nranks, int rank, rusty_cuda_arena** out);
