@@ -25,6 +25,7 @@
 #include <cerrno>
 #include <cstdint>
 #include <cstring>
+#include <algorithm>
 #include <map>
 #include <memory>
 #include <stdexcept>
@@ -266,6 +267,13 @@ public:
             if (t.begin > t.end || t.end > data_len_ || t.end - t.begin != nbytes)
                 throw LoaderError("Safetensors", path + ": " + kv.first + ": data_offsets do not match shape and dtype");
         }
+        // no two tensors may share bytes (the reference's safetensors crate validates the same)
+        std::vector<std::pair<size_t, size_t>> ranges;
+        for (const auto& kv : entries_)
+            if (kv.second.end > kv.second.begin) ranges.emplace_back(kv.second.begin, kv.second.end);
+        std::sort(ranges.begin(), ranges.end());
+        for (size_t i = 1; i < ranges.size(); ++i)
+            if (ranges[i].first < ranges[i - 1].second) throw LoaderError("Safetensors", path + ": tensor byte ranges overlap");
     }
     ~MappedFile() {
         if (base_) ::munmap(const_cast<unsigned char*>(base_), size_);

@@ -114,6 +114,11 @@ class _File:
             if not (0 <= b <= e <= self.data_len) or e - b != want:
                 raise LoaderError("Safetensors", f"{path}: {name}: data_offsets [{b},{e}) do not match shape {list(shape)} {tag}")
             self.entries[name] = (tag, shape, int(b), int(e))
+        # no two tensors may share bytes (the reference's safetensors crate validates the same)
+        spans = sorted((b, e) for _t, _s, b, e in self.entries.values() if e > b)
+        for (b0, e0), (b1, _e1) in zip(spans, spans[1:]):
+            if b1 < e0:
+                raise LoaderError("Safetensors", f"{path}: tensor byte ranges overlap")
         self.mmap = np.memmap(path, dtype=np.uint8, mode="r") if size > 0 else np.zeros(0, np.uint8)
 
     def view(self, name: str) -> Tuple[np.ndarray, Tuple[int, ...], str]:

@@ -77,6 +77,13 @@ def test_error_variants(exe, checkpoint, tmp_path):
     wrap.write_bytes(len(hdr).to_bytes(8, "little") + hdr)
     r = subprocess.run([exe, "info", str(wrap), "w.weight"], capture_output=True, text=True, timeout=60)
     assert r.returncode == 3 and r.stdout.strip() == "LoaderError Safetensors", r.stdout + r.stderr
+    # two tensors over the same bytes
+    hdr = json.dumps({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]},
+                      "b": {"dtype": "F32", "shape": [1], "data_offsets": [4, 8]}}).encode()
+    lap = tmp_path / "overlap.safetensors"
+    lap.write_bytes(len(hdr).to_bytes(8, "little") + hdr + b"\0" * 8)
+    r = subprocess.run([exe, "info", str(lap), "a"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 3 and r.stdout.strip() == "LoaderError Safetensors", r.stdout + r.stderr
     r = subprocess.run([exe, "shard", checkpoint, "norm", "0", "1"], capture_output=True, text=True, timeout=60)
     assert r.returncode == 3 and r.stdout.strip() == "LoaderError MissingWeight"   # norm has no quantised parts
     r = subprocess.run([exe, "shard", checkpoint, "layers.0.q_proj", "0", "3"], capture_output=True, text=True, timeout=60)

@@ -60,7 +60,7 @@ def test_header_is_the_published_layout(tmp_path):
     assert blob[8 + n:] == a.tobytes() and (8 + n) % 8 == 0
 
 
-@pytest.mark.parametrize("damage", ["short", "length", "json", "offsets", "dtype"])
+@pytest.mark.parametrize("damage", ["short", "length", "json", "offsets", "dtype", "overlap"])
 def test_malformed_files_are_rejected(tmp_path, damage):
     path = str(tmp_path / "bad.safetensors")
     good = {"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}
@@ -73,6 +73,8 @@ def test_malformed_files_are_rejected(tmp_path, damage):
     else:
         if damage == "offsets":
             good["a"]["data_offsets"] = [0, 12]
+        elif damage == "overlap":
+            good["b"] = {"dtype": "F32", "shape": [1], "data_offsets": [4, 8]}
         else:
             good["a"]["dtype"] = "Q4"
         hj = json.dumps(good).encode()
