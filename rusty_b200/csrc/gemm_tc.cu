@@ -23,11 +23,13 @@
 //             128-byte swizzle, mbarrier complete_tx;
 //   warp 1  : allocates TMEM, issues tcgen05.mma (M=128, N=NB, K=32) from one
 //             elected lane, frees ring slots with tcgen05.commit;
-//   warps 2-5: epilogue — tcgen05.ld the int32 accumulators (double-buffered in
-//             TMEM), fold the digits into int64 in a shared-memory staging tile,
-//             scale, store y; or, when K is split over several CTAs, add the
-//             staged piece into the tile's sum in L2 with one bulk reduce and
-//             convert an equal share of the rows once all pieces have arrived.
+//   warps 2-9: epilogue (four or eight warps) — tcgen05.ld the int32
+//             accumulators (double-buffered in TMEM), fold the digits into
+//             int64, scale, store y (whole tiles through a shared-memory
+//             staging tile); or, when K is split over several CTAs, store the
+//             piece as tagged 64-bit words (sum << 1 | 1) into this CTA's slot,
+//             poll the other pieces' words until they are non-zero, and convert
+//             an equal share of the rows (readers zero the words they used).
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the kernel
 // raises the context's timeout flag, drains and frees its TMEM.
 #include <cstdlib>
@@ -363,7 +365,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     const int a_stage_bytes = p.tpu * A_TILE_BYTES;
     uint8_t* sA = smem;
     uint8_t* sB = smem + (size_t)p.stages * a_stage_bytes;
-    // epilogue staging for the bulk reduce-add of a partial tile: [Mpad/2][128] x 16 bytes
+    // epilogue staging of a whole tile's folded sums: [Mpad/2][128] x 16 bytes
     int4* stage_red = reinterpret_cast<int4*>(sB + (size_t)p.stages * b_stage_bytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stage_red) + (size_t)p.red_bytes);
     uint64_t* full = bars;                      // [stages]
@@ -508,7 +510,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
         const int r = q * 32 + lane;            // row inside the tile
         YT* y = reinterpret_cast<YT*>(p.y);
-        pdl_wait();                             // x, y, the sums and the counters belong to earlier kernels until now
+        pdl_wait();                             // x, y and the piece slots belong to earlier kernels until now
         bool ok = true;
         const int et = threadIdx.x - 64;        // 0..EPI_THREADS-1 among the epilogue threads
         const int EPI_THREADS = 32 * p.epi_warps;
@@ -1104,7 +1106,7 @@ extern "C" RUSTY_CUDA_API int rusty_cuda_debug_set_timeline(rusty_cuda_ctx* ctx,
 // latency-critical serving loop whose memory was carved up front, or under an
 // allocator that owns every byte of the device and treats a foreign allocation
 // as a leak.  For them the tensor-core kernel's scratch (digit planes of the
-// activations, per-row factors, sums of K-cut tiles, arrival counters, status
+// activations, per-row factors, slots for the pieces of K-cut tiles, status
 // word) lives in the fixed array below, which every GPU that loads this library
 // holds until the process exits.
 // ----------------------------------------------------------------------------
