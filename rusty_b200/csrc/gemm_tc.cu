@@ -442,6 +442,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     }
                     if (!waited) {
                         pdl_wait();
+                        DBG(1);
                         for (int e = 0; e < early; ++e)
                             tma_load_2d(sB + (size_t)e * b_stage_bytes, &map_x, early_kb[e] * BK, 0, &full[e], pol_x);
                         waited = true;
@@ -456,6 +457,7 @@ qlinear_i8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             }
             if (!waited) {  // fewer k-blocks than ring slots
                 pdl_wait();
+                DBG(1);
                 for (int e = 0; e < early; ++e)
                     tma_load_2d(sB + (size_t)e * b_stage_bytes, &map_x, early_kb[e] * BK, 0, &full[e], pol_x);
             }

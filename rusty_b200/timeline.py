@@ -101,7 +101,7 @@ def main() -> None:
             return (us(v.min()) + "," + us(v.max())) if v.size else "-"
         sync = f" arrived={us(d[4])} told_peers={us(d[5])} polls={int(d[6])} met={us(d[3])}" if world > 1 else ""
         out.append(f"L{i}: pre-pass launched={us(d[0])} released={us(d[1])}{sync} end={us(d[2])} | GEMM ctas={int(act.sum())} "
-                   f"start[{mm(0)}] first_mma[{mm(4)}] last_mma[{mm(5)}] folded[{mm(7)}] pieces_done[{mm(11)}] exit[{mm(15)}]")
+                   f"start[{mm(0)}] released[{mm(1)}] first_mma[{mm(4)}] last_mma[{mm(5)}] folded[{mm(7)}] pieces_done[{mm(11)}] exit[{mm(15)}]")
     out.append("period per Linear: %.2f us" % ((t[9, 150, 1] - t[5, 150, 1]) / 4000.0))
     for r in range(world):
         if r == rank:
