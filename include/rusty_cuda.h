@@ -373,6 +373,12 @@ RUSTY_CUDA_API int rusty_cuda_argmax_rows_sharded(rusty_cuda_ctx* ctx, rusty_cud
  * out_idx: u32 [M, k]; out_val (may be NULL): f32 [M, k]. */
 RUSTY_CUDA_API int rusty_cuda_top_k_rows_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* logits, uint32_t M, uint32_t N, uint32_t k,
                                              rusty_cuda_buf* out_idx, rusty_cuda_buf* out_val);
+/* Soft-max statistics of every row at a temperature (> 0): out_max[m] = the largest logit, out_sum[m] = sum_j
+ * exp((x[m,j] - max) / temperature): what Sampler::sample computes before sorting (rusty-loader/src/tokenizer.rs:161-170),
+ * NaN skipped, f32 tree sum.  With the row's top-k pairs the host walks the nucleus without reading the logits back
+ * (probability of a candidate = exp((value - max) / temperature) / sum). */
+RUSTY_CUDA_API int rusty_cuda_softmax_stats_rows_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* logits, uint32_t M, uint32_t N,
+                                                     float temperature, rusty_cuda_buf* out_max, rusty_cuda_buf* out_sum);
 /* The same over output-feature shards: every rank passes its own columns [M, Nl] (global index = rank * Nl + column);
  * only k (value, index) pairs per row and rank cross NVLink, every rank ends with the k global winners.
  * table: a buffer of the arena, nranks * M * k * 8 bytes, at the same offset on every rank.  k * nranks <= 2048. */

@@ -371,6 +371,15 @@ class ComputeEngine:
         check(lib().rusty_cuda_top_k_rows_f32(ctx.handle, input.buffer(), M, N, k, out_idx.buffer(),
                                               out_val.buffer() if out_val is not None else None), ctx.handle)
 
+    def softmax_stats(self, ctx: CudaContext, input: UnifiedTensor, temperature: float, out_max: UnifiedTensor,
+                      out_sum: UnifiedTensor) -> None:
+        """Per row of input[..., N]: the largest logit and sum exp((x - max) / temperature) (the first half of
+        Sampler::sample, rusty-loader/src/tokenizer.rs:161-170)."""
+        N = int(input.shape[-1])
+        M = int(np.prod(input.shape[:-1], dtype=np.int64))
+        check(lib().rusty_cuda_softmax_stats_rows_f32(ctx.handle, input.buffer(), M, N, float(temperature), out_max.buffer(),
+                                                      out_sum.buffer()), ctx.handle)
+
     def qlinear(self, ctx: CudaContext, x: UnifiedTensor, w: QLinear, out: UnifiedTensor) -> None:
         """out[M,N] = x[M,K] (.) w, fused dequantise + multiply."""
         m = int(np.prod(x.shape[:-1], dtype=np.int64))

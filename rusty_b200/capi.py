@@ -104,6 +104,7 @@ SIGNATURES = {
     "rusty_cuda_argmax_rows_f32": ([_vp, _vp, _u32, _u32, _vp, _vp], _int),
     "rusty_cuda_argmax_rows_sharded": ([_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp], _int),
     "rusty_cuda_top_k_rows_f32": ([_vp, _vp, _u32, _u32, _u32, _vp, _vp], _int),
+    "rusty_cuda_softmax_stats_rows_f32": ([_vp, _vp, _u32, _u32, C.c_float, _vp, _vp], _int),
     "rusty_cuda_top_k_rows_sharded": ([_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp], _int),
     "rusty_cuda_graph_begin": ([_vp], _int),
     "rusty_cuda_graph_end": ([_vp, _vpp], _int),

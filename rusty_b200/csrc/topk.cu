@@ -220,6 +220,51 @@ __global__ void __launch_bounds__(TK_THREADS) topk_merge_kernel(const unsigned l
     // like the arg-max table: the next table write of any rank waits until every rank has merged this one
 }
 
+// Soft-max statistics of every row at a temperature: the largest logit and sum_j exp((x_j - max) / T), what
+// Sampler::sample (rusty-loader/src/tokenizer.rs:161-170) computes before it sorts.  With these two numbers and the
+// row's top-k pairs the host can walk the nucleus without ever seeing the other logits.  Tree sum in f32 (the
+// reference adds sequentially); NaN logits are skipped.
+__global__ void __launch_bounds__(TK_THREADS) softmax_stats_rows_kernel(const float* __restrict__ x, int n, size_t ld, int M, float inv_t,
+                                                                        float* __restrict__ out_max, float* __restrict__ out_sum) {
+    __shared__ float red[TK_THREADS / 32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int m = blockIdx.x; m < M; m += gridDim.x) {
+        const float* row = x + (size_t)m * ld;
+        float mx = __int_as_float(0xff800000);
+        for (int j = tid; j < n; j += TK_THREADS) {
+            const float v = row[j];
+            if (v == v) mx = fmaxf(mx, v);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        if (lane == 0) red[warp] = mx;
+        __syncthreads();
+        mx = red[lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        __syncthreads();
+        float sum = 0.0f;
+        for (int j = tid; j < n; j += TK_THREADS) {
+            const float v = row[j];
+            if (v == v) sum += expf((v - mx) * inv_t);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (lane == 0) red[warp] = sum;
+        __syncthreads();
+        sum = red[lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (tid == 0) {
+            out_max[m] = mx;
+            out_sum[m] = sum;
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace
 
 namespace rusty {
@@ -247,6 +292,24 @@ int rusty_cuda_top_k_rows_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* logits,
                                (unsigned long long*)nullptr, PeerPush{});
     if (e != cudaSuccess) return check_cuda(ctx, e, "top_k_rows");
     return after_launch(ctx, "top_k_rows");
+}
+
+int rusty_cuda_softmax_stats_rows_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf* logits, uint32_t M, uint32_t N, float temperature,
+                                      rusty_cuda_buf* out_max, rusty_cuda_buf* out_sum) {
+    RUSTY_REQUIRE_CTX(ctx);
+    if (!logits || !out_max || !out_sum) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "softmax_stats_rows: null buffer");
+    if (!(temperature > 0.0f)) return fail(ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "softmax_stats_rows: temperature must be > 0 (greedy choice is argmax_rows)");
+    if (N > 0x7fffffffu) return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "softmax_stats_rows: N=%u too large", N);
+    if (logits->bytes < (size_t)M * N * 4 || out_max->bytes < (size_t)M * 4 || out_sum->bytes < (size_t)M * 4)
+        return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "softmax_stats_rows: [%u,%u] logits need %zu bytes, the outputs %zu each", M, N,
+                    (size_t)M * N * 4, (size_t)M * 4);
+    if (M == 0) return RUSTY_CUDA_OK;
+    DeviceGuard g(ctx->device);
+    const unsigned blocks = M < (uint32_t)ctx->sm_count ? M : (unsigned)ctx->sm_count;
+    cudaError_t e = launch_pdl(softmax_stats_rows_kernel, dim3(blocks), dim3(TK_THREADS), 0, ctx->stream, (const float*)logits->ptr, (int)N, (size_t)N,
+                               (int)M, 1.0f / temperature, (float*)out_max->ptr, (float*)out_sum->ptr);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "softmax_stats_rows");
+    return after_launch(ctx, "softmax_stats_rows");
 }
 
 int rusty_cuda_top_k_rows_sharded(rusty_cuda_ctx* ctx, rusty_cuda_arena* arena, const rusty_cuda_buf* logits_shard, uint32_t M, uint32_t Nl,

@@ -3,7 +3,10 @@
 Greedy choice (temperature <= 0) also exists on the device (`ComputeEngine.argmax_rows`, sharded form in
 `rusty_b200.shard`); temperature / top-p sampling stays on the host, as in the reference, in f32 arithmetic and in the
 reference's order of operations: scale by 1/temperature, soft-max with the maximum subtracted, sort by probability
-(descending, stable), take the shortest prefix whose sum reaches top_p, renormalise, draw.
+(descending, stable), take the shortest prefix whose sum reaches top_p, renormalise, draw.  `sample_rows_from_device`
+does the same walk over the k largest logits of each row and the row's soft-max statistics, both computed on the
+device, so that k pairs and two floats per row cross PCIe instead of the whole vocabulary; a row whose nucleus does not
+fit into k falls back to reading its logits.
 """
 from __future__ import annotations
 
@@ -52,3 +55,60 @@ class Sampler:
             if r < cumsum:
                 return i
         return nucleus[0] if nucleus else 0
+
+    def sample_from_candidates(self, idx, val, row_max: float, exp_sum: float):
+        """The nucleus walk over candidates sorted by value (descending; equal values by ascending index), given the
+        row's largest logit and sum exp((x - max) / T) over ALL logits.  Returns the token, or None when the
+        candidates' probability mass does not reach top_p (the nucleus is longer than the list)."""
+        t = self.temperature
+        scaled = (np.asarray(val, np.float32) / t).astype(np.float32)            # the reference's order: scale, then subtract
+        max_val = np.float32(np.float32(row_max) / t)
+        probs = (np.exp((scaled - max_val).astype(np.float32)).astype(np.float32) / np.float32(exp_sum)).astype(np.float32)
+        cumsum = np.float32(0.0)
+        n = 0
+        for p in probs:
+            cumsum = np.float32(cumsum + p)
+            n += 1
+            if cumsum >= self.top_p:
+                break
+        else:
+            return None
+        nucleus_sum = np.float32(0.0)
+        for p in probs[:n]:
+            nucleus_sum = np.float32(nucleus_sum + p)
+        r = np.float32(self._rand())
+        cumsum = np.float32(0.0)
+        for i in range(n):
+            cumsum = np.float32(cumsum + np.float32(probs[i] / nucleus_sum))
+            if r < cumsum:
+                return int(idx[i])
+        return int(idx[0])
+
+    def sample_rows_from_device(self, ctx, engine, logits, k: int = 64):
+        """One token per row of a device tensor logits[M, N] (f32).  temperature <= 0: the device arg-max.  Otherwise
+        the device's top-k and soft-max statistics, then the reference's nucleus walk on the host."""
+        from .backend import DType, UnifiedTensor
+        M, N = int(np.prod(logits.shape[:-1], dtype=np.int64)), int(logits.shape[-1])
+        if self.temperature <= 0.0:
+            tok = UnifiedTensor.from_bytes_with_dtype(ctx, np.zeros(M, np.uint32), [M * 4], DType.U8)
+            engine.argmax_rows(ctx, logits, tok)
+            return [int(t) for t in tok.to_bytes(ctx).view(np.uint32)]
+        k = max(1, min(int(k), N, 1024))
+        idx_t = UnifiedTensor.from_bytes_with_dtype(ctx, np.zeros(M * k, np.uint32), [M * k * 4], DType.U8)
+        val_t = UnifiedTensor.empty(ctx, [M, k])
+        mx_t, sm_t = UnifiedTensor.empty(ctx, [M]), UnifiedTensor.empty(ctx, [M])
+        engine.top_k(ctx, logits, idx_t, k, out_val=val_t)
+        engine.softmax_stats(ctx, logits, float(self.temperature), mx_t, sm_t)
+        idx = idx_t.to_bytes(ctx).view(np.uint32).reshape(M, k)
+        val = val_t.to_vec(ctx).reshape(M, k)
+        mx, sm = mx_t.to_vec(ctx), sm_t.to_vec(ctx)
+        out = []
+        host_rows = None
+        for m in range(M):
+            tok = self.sample_from_candidates(idx[m], val[m], mx[m], sm[m])
+            if tok is None:   # the nucleus is longer than k: the reference's own path over the whole row
+                if host_rows is None:
+                    host_rows = logits.to_vec(ctx).reshape(M, N)
+                tok = self.sample(host_rows[m])
+            out.append(tok)
+        return out

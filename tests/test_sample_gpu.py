@@ -118,3 +118,44 @@ def test_top_k_argument_errors(ctx, engine):
     with pytest.raises(BackendError) as e:
         engine.top_k(ctx, t, idx, 8)          # 2 x 8 indices do not fit 32 bytes
     assert e.value.kind == "InvalidDimensions"
+
+
+# ---- temperature / top-p with the device's top-k and soft-max statistics ----
+def test_softmax_stats_rows(ctx, engine):
+    rng = np.random.default_rng(5)
+    M, N = 6, 50000
+    logits = (rng.standard_normal((M, N)) * 3).astype(np.float32)
+    logits[1, ::7] = np.nan
+    logits[2, 100] = 40.0
+    t = UnifiedTensor.new(ctx, logits, [M, N])
+    mx, sm = UnifiedTensor.empty(ctx, [M]), UnifiedTensor.empty(ctx, [M])
+    for temp in (0.7, 1.0, 2.5):
+        engine.softmax_stats(ctx, t, temp, mx, sm)
+        got_mx, got_sm = mx.to_vec(ctx), sm.to_vec(ctx)
+        want_mx = np.nanmax(logits, axis=1)
+        want_sm = np.nansum(np.exp((logits.astype(np.float64) - want_mx[:, None]) / temp), axis=1)
+        assert np.array_equal(got_mx, want_mx)
+        assert np.max(np.abs(got_sm - want_sm) / want_sm) < 2e-6
+    from rusty_b200 import BackendError
+    with pytest.raises(BackendError) as e:
+        engine.softmax_stats(ctx, t, 0.0, mx, sm)
+    assert e.value.kind == "InvalidOperation"
+
+
+def test_device_assisted_nucleus_sampling_matches_the_host_sampler(ctx, engine):
+    """Same draws, same tokens: k pairs and two floats per row leave the device instead of the whole vocabulary; a row
+    whose nucleus is longer than k takes the host path over its logits."""
+    from rusty_b200.sampler import Sampler
+    rng = np.random.default_rng(9)
+    M, N = 8, 32000
+    logits = (rng.standard_normal((M, N)) * 4).astype(np.float32)
+    logits[3] *= 0.02                       # nearly flat row: the nucleus holds thousands of tokens -> host path
+    t = UnifiedTensor.new(ctx, logits, [M, N])
+    for temp, top_p in ((0.7, 0.9), (1.0, 0.5), (0.0, 0.9)):
+        draws = [float(v) for v in rng.random(M)]
+        it = iter(draws)
+        got = Sampler(temp, top_p, rand=lambda: next(it)).sample_rows_from_device(ctx, engine, t, k=64)
+        it2 = iter(draws)
+        host = Sampler(temp, top_p, rand=lambda: next(it2))
+        want = [host.sample(logits[m]) for m in range(M)]
+        assert got == want, (temp, top_p, got, want)

@@ -44,3 +44,30 @@ def test_temperature_sharpens():
 def test_defaults_are_the_reference_defaults():
     s = Sampler()
     assert abs(float(s.temperature) - 0.7) < 1e-7 and abs(float(s.top_p) - 0.9) < 1e-7
+
+
+def test_nucleus_walk_over_candidates_equals_the_walk_over_the_whole_row():
+    """The device hands the host the k largest logits (sorted as the shader sorts them) and the row's soft-max
+    statistics; the walk over those candidates must choose what Sampler.sample chooses on the whole row."""
+    import numpy as np
+    from rusty_b200.sampler import Sampler
+    rng = np.random.default_rng(7)
+    for trial in range(40):
+        n = int(rng.integers(50, 3000))
+        logits = (rng.standard_normal(n) * rng.uniform(0.5, 6.0)).astype(np.float32)
+        t, top_p = float(rng.uniform(0.3, 1.5)), float(rng.uniform(0.3, 0.98))
+        r = float(rng.random())
+        whole = Sampler(t, top_p, rand=lambda: r).sample(logits)
+        order = np.lexsort((np.arange(n), -logits))            # value descending, index ascending among equals
+        scaled_max = np.float32(logits.max())
+        e = np.exp(((logits - scaled_max) / np.float32(t)).astype(np.float32)).astype(np.float32)
+        exp_sum = np.float32(0.0)
+        for v in e:
+            exp_sum = np.float32(exp_sum + v)
+        for k in (n, 256, 8):
+            k = min(k, n)
+            got = Sampler(t, top_p, rand=lambda: r).sample_from_candidates(order[:k], logits[order[:k]], scaled_max, exp_sum)
+            if got is None:
+                assert k < n          # only a truncated list may fail to reach top_p
+            else:
+                assert got == whole, (trial, k, got, whole)
