@@ -1005,13 +1005,22 @@ static int launch_tc_rows(rusty_cuda_ctx* ctx, const QLinearArgs& a, const void*
     p.bmu = p.tpu * BM;
     p.tiles = (p.N + p.bmu - 1) / p.bmu;
     int sched_sms = ctx->sm_count;
-#ifdef RUSTY_TIMELINE
-    {   // development aid: schedule as if the GPU had fewer SMs (what one SM can stream on its own)
+    {   // tuning aid: schedule as if the GPU had fewer SMs
         static const int sms_env = getenv("RUSTY_TC_SMS") ? atoi(getenv("RUSTY_TC_SMS")) : 0;
         if (sms_env > 0 && sms_env < sched_sms) sched_sms = sms_env;
     }
-#endif
     plan_tc_schedule(p.tiles, p.kb_total, sched_sms, dp_percent, WS_ACC_BYTES / ((size_t)p.tpu * Mpad * BM * 8), &sc);
+    // A GEMM CTA and a pre-pass block do not fit one SM together (registers), and the NEXT pair's pre-pass blocks are
+    // resident (two per SM, up to 16 SMs) while this GEMM's CTAs are placed.  A short launch whose every tile is cut
+    // (fewer tiles than SMs) and whose grid leaves those SMs no room gets its last CTAs placed only after the pre-pass
+    // has finished, 2-5 us late: plan it for 16 SMs fewer (q|k|v 6144 x 4096: 144 -> 96 CTAs, 18.2 -> 16.8 us).
+    // RUSTY_TC_ROOM=0 turns the rule off (tuning aid).
+    static const bool leave_room = !(getenv("RUSTY_TC_ROOM") && atoi(getenv("RUSTY_TC_ROOM")) == 0);
+    if (leave_room && sc.dp_tiles == 0 && sc.grid > sched_sms - 16 && sched_sms > 32) {
+        TcSchedule alt{};
+        plan_tc_schedule(p.tiles, p.kb_total, sched_sms - 16, dp_percent, WS_ACC_BYTES / ((size_t)p.tpu * Mpad * BM * 8), &alt);
+        if (alt.dp_tiles == 0) sc = alt;
+    }
     int grid = sc.grid;
     p.dp_tiles = sc.dp_tiles;
     p.sk_tiles = sc.sk_tiles;
