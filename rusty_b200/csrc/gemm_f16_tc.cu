@@ -59,6 +59,7 @@ struct F16Params {
     int ldy, y_col0;
     int act;                  // RUSTY_CUDA_ACT_*: the pair epilogue writes N/2 columns
     const void* residual;     // null, or added to every output (same layout as y)
+    PeerPush push;            // nranks > 1: every output is also stored into the other ranks' arenas (peer.cu)
     uint32_t idesc;
     rusty_cuda_dev_status* status;
 };
@@ -81,16 +82,28 @@ __device__ __forceinline__ float load_y<__nv_bfloat16>(const __nv_bfloat16* p) {
 // together.  With the pair activation rows 2j / 2j+1 of the weight are gate_j / up_j (MLP::forward,
 // rusty-graph/src/lib.rs:317-323): the even lane takes its neighbour's value and writes silu(gate) * up into column
 // (y_col0 + n) / 2; silu as kernels.wgsl:104-113.
+// The same element of every other rank's y, over NVLink (plain stores to peer addresses; the byte offsets of the other
+// arenas sit in shared memory: indexing the kernel parameter with a run-time index would copy it to local memory).
+struct PeerOut {
+    int n;
+    const long long* delta;
+};
 template <typename YT>
-__device__ __forceinline__ void store_out(const F16Params& p, YT* y, int m, int n, float v, bool row_ok) {
+__device__ __forceinline__ void store_everywhere(YT* dst, float v, const PeerOut& po) {
+    store_y<YT>(dst, v);
+    for (int g = 0; g < po.n; ++g) store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<char*>(dst) + po.delta[g]), v);
+}
+
+template <typename YT>
+__device__ __forceinline__ void store_out(const F16Params& p, YT* y, int m, int n, float v, bool row_ok, const PeerOut& po) {
     if (p.act) {
         const float up = __shfl_down_sync(0xffffffffu, v, 1);
         v = __fdividef(v, 1.0f + __expf(-v)) * up;
-        if (row_ok && m < p.Mx && !(n & 1)) store_y<YT>(y + (size_t)m * p.ldy + ((p.y_col0 + n) >> 1), v);
+        if (row_ok && m < p.Mx && !(n & 1)) store_everywhere<YT>(y + (size_t)m * p.ldy + ((p.y_col0 + n) >> 1), v, po);
     } else if (row_ok && m < p.Mx) {
         const size_t at = (size_t)m * p.ldy + p.y_col0 + n;
         if (p.residual) v += load_y<YT>(reinterpret_cast<const YT*>(p.residual) + at);
-        store_y<YT>(y + at, v);
+        store_everywhere<YT>(y + at, v, po);
     }
 }
 
@@ -199,6 +212,14 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
+    __shared__ long long s_peer_delta[PEER_MAX_RANKS];
+    if (threadIdx.x == 0) {
+        int k = 0;  // the other ranks, compacted (own rank left out); static indices into the parameter
+#pragma unroll
+        for (int g = 0; g < PEER_MAX_RANKS; ++g)
+            if (g < p.push.nranks && g != p.push.rank) s_peer_delta[k++] = p.push.delta[g];
+    }
+    const PeerOut po = {p.push.nranks > 1 ? p.push.nranks - 1 : 0, s_peer_delta};   // visible after the set-up barrier below
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < W_STAGES; ++s) {
@@ -347,7 +368,7 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const int c_lo = (warp - (2 + CONV_WARPS)) >= 4 ? c_split : 0;
         const int c_hi = (warp - (2 + CONV_WARPS)) >= 4 ? p.BN : c_split;
         YT* y = reinterpret_cast<YT*>(p.y);
-        const bool plain = !p.act && !p.residual;
+        const bool plain = !p.act && !p.residual && po.n == 0;
         pdl_wait();
         bool ok = true;
         int i = 0;
@@ -376,7 +397,7 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                         }
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) store_out<YT>(p, y, j * p.BN + c0 + e, n, __uint_as_float(v[e]) * sc, row_ok);
+                        for (int e = 0; e < 16; ++e) store_out<YT>(p, y, j * p.BN + c0 + e, n, __uint_as_float(v[e]) * sc, row_ok, po);
                     }
                 }
                 tc_fence_before();
@@ -431,7 +452,7 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                             for (int e = 0; e < 4; ++e) {
                                 const float vals[4] = {f[e].x, f[e].y, f[e].z, f[e].w};
 #pragma unroll
-                                for (int k = 0; k < 4; ++k) store_out<YT>(p, y, j * p.BN + c0 + e * 4 + k, n, vals[k] * sc, row_ok);
+                                for (int k = 0; k < 4; ++k) store_out<YT>(p, y, j * p.BN + c0 + e * 4 + k, n, vals[k] * sc, row_ok, po);
                             }
                         }
                     }
@@ -480,6 +501,7 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.y_col0 = (int)a.y_col0;
     p.act = a.act;
     p.residual = a.residual;
+    if (a.push && a.push->nranks > 1) p.push = *a.push;
     p.status = ctx->status_dev;
     // bf16 A x bf16 B -> f32: c_format=F32(1)@4, a_format=BF16(1)@7, b_format=BF16(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);

@@ -69,6 +69,8 @@ struct GmParams {
     int x_bf16, y_bf16;
     rusty_cuda_dev_status* status;
     long long* dbg;   // per-CTA timeline (16 slots each); null outside development builds
+    int n_peers;                          // other ranks whose copy of y also receives every output (peer.cu); 0: none
+    long long peer_delta[PEER_MAX_RANKS]; // byte offsets of their arenas, compacted (used with static indices only)
 };
 
 // Kernel timeline (%globaltimer stamps per CTA), compiled in only with -DRUSTY_TIMELINE (a development build).
@@ -223,8 +225,21 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
                 col >>= 1;
             }
             if (live) {
-                if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + col] = __float2bfloat16_rn(v);
-                else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + col] = v;
+                const size_t at = (size_t)m * p.ldy + col;
+                if (p.y_bf16) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.y) + at;
+                    const __nv_bfloat16 b = __float2bfloat16_rn(v);
+                    *dst = b;
+#pragma unroll
+                    for (int g = 0; g < PEER_MAX_RANKS - 1; ++g)   // the same element of every other rank's y, over NVLink
+                        if (g < p.n_peers) *reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(dst) + p.peer_delta[g]) = b;
+                } else {
+                    float* dst = reinterpret_cast<float*>(p.y) + at;
+                    *dst = v;
+#pragma unroll
+                    for (int g = 0; g < PEER_MAX_RANKS - 1; ++g)
+                        if (g < p.n_peers) *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_delta[g]) = v;
+                }
             }
         }
         if (lane == 0) GDBG(6);
@@ -501,6 +516,9 @@ int launch_gemv_mma(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.units = (p.N + 1) / 2;
     p.ldy = (int)a.ldy;
     p.y_col0 = (int)a.y_col0;
+    if (a.push && a.push->nranks > 1)
+        for (int g = 0; g < a.push->nranks && g < PEER_MAX_RANKS; ++g)
+            if (g != a.push->rank) p.peer_delta[p.n_peers++] = a.push->delta[g];
     p.act = a.act;
     p.x_bf16 = a.x_dtype == RUSTY_CUDA_BF16;
     p.y_bf16 = a.y_dtype == RUSTY_CUDA_BF16;

@@ -210,6 +210,8 @@ uint32_t f16tc_min_rows();
 
 // True when the kernel chosen for this shape stores into the peers' arenas itself.
 bool qlinear_pushes_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
+// True when that kernel also meets the other ranks itself (else rusty_cuda_qlinear_forward_pushed puts the wait kernel in front).
+bool qlinear_meets_in_kernel(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 // Forward into columns [y_col0, y_col0 + N) of a y whose rows are ldy elements apart.
 int qlinear_forward_cols(rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, const rusty_cuda_buf* x, int x_dtype,

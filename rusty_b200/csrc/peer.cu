@@ -230,8 +230,16 @@ int rusty_cuda_qlinear_forward_pushed(rusty_cuda_ctx* ctx, rusty_cuda_arena* are
                     (size_t)M * N * ys);
     if (M == 0 || Nl == 0) return RUSTY_CUDA_OK;
     static const bool unfused = getenv("RUSTY_PUSH_UNFUSED") != nullptr;  // development aid: always use the copy kernel
-    if (G > 1 && !unfused && qlinear_pushes_fused(ql_shard, x_dtype, M, y_dtype))
+    if (G > 1 && !unfused && qlinear_pushes_fused(ql_shard, x_dtype, M, y_dtype)) {
+        if (!qlinear_meets_in_kernel(ql_shard, x_dtype, M, y_dtype)) {   // the bf16 kernel: the meeting as a kernel in front
+            DeviceGuard g(ctx->device);
+            cudaError_t e = launch_pdl(peer_wait_kernel, dim3(1), dim3(32), 0, ctx->stream, arena->pp);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "peer_wait");
+            int rc = after_launch(ctx, "peer_wait");
+            if (rc) return rc;
+        }
         return qlinear_forward_cols(ctx, ql_shard, x, x_dtype, M, y_full, y_dtype, N, col0, &arena->pp);
+    }
     // Other kernels: wait, compute this rank's columns in place, copy them to the peers and signal.
     DeviceGuard g(ctx->device);
     if (G > 1) {

@@ -50,6 +50,13 @@ const char* qlinear_plan(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, 
 }
 
 bool qlinear_pushes_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype) {
+    const char* plan = qlinear_plan(ql, x_dtype, M, y_dtype);
+    return (strcmp(plan, "tcgen05") == 0 && tc_pushes_fused(M)) || strcmp(plan, "tcgen05_f16") == 0 || strcmp(plan, "gemv_mma") == 0;
+}
+
+// The int8 decode pair meets the other ranks in its own pre-pass; the bf16 kernel and the M <= 2 GEMV store to the peers
+// from their epilogues but need the meeting as a kernel in front of them.
+bool qlinear_meets_in_kernel(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype) {
     return strcmp(qlinear_plan(ql, x_dtype, M, y_dtype), "tcgen05") == 0 && tc_pushes_fused(M);
 }
 
