@@ -180,7 +180,13 @@ RUSTY_CUDA_API int rusty_cuda_add_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf*
  * matmul per forward" (rusty-loader/src/lib.rs:155-218 followed by
  * rusty-graph/src/lib.rs:69-70 -> rusty-autograd/src/lib.rs:468-477) with
  * kernels that read the 1-byte weights and their scales once per forward.
- * The object borrows (retains) the three buffers; it copies nothing.
+ * The object borrows (retains) the buffers it is given, with one exception: a
+ * SYM_ROW weight in LAYOUT_KN (rusty's own [in,out] Linear storage) with
+ * K % 16 == 0 is re-laid-out ONCE, inside this call, into an [out,in] buffer
+ * that the object owns (N*K more bytes of device memory), so that every
+ * forward runs on the TMA / tensor-core kernels; the caller's weight buffer
+ * is then not kept and may be released.  (RUSTY_KN_RELAYOUT=0 in the
+ * environment keeps the [in,out] CUDA-core kernel instead.)
  *   AFFINE_G64: weight u8 [N*K], scales/biases f32 [N*K/64]; K % 64 == 0 for
  *               LAYOUT_NK (N % 64 == 0 for LAYOUT_KN) so a group never
  *               straddles two rows.

@@ -79,7 +79,9 @@ struct rusty_cuda_qlinear {
     rusty_cuda_buf* scales = nullptr;
     rusty_cuda_buf* biases = nullptr;
     uint32_t N = 0, K = 0;
-    int layout = 0, qmode = 0;
+    int layout = 0, qmode = 0;   // layout of `weight` as the kernels read it
+    int given_layout = 0;        // layout the caller handed over ([in,out] weights with one scale per output are
+                                 // re-laid-out to [out,in] once, at create: `weight` is then the library's own copy)
     int act = 0;  // RUSTY_CUDA_ACT_*: applied to pairs of output features in the kernel's epilogue
 };
 
@@ -182,6 +184,8 @@ int launch_rms_norm(rusty_cuda_ctx* ctx, const float* x, const float* residual, 
 // whether the Linear's own activation pre-pass can apply the norm for this call
 bool qlinear_norm_fused(const rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 bool tc_norm_fused(uint32_t M, uint32_t K);
+// out[n][k] = in[k][n], bytes (the one-time re-layout of an [in,out] weight)
+int launch_transpose_u8(rusty_cuda_ctx* ctx, const uint8_t* in, uint8_t* out, uint32_t K, uint32_t N);
 int launch_residual_add(rusty_cuda_ctx* ctx, const void* a, const void* b, void* out, size_t n, int y_dtype);
 bool qlinear_residual_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 

@@ -181,8 +181,33 @@ int rusty_cuda_qlinear_create(rusty_cuda_ctx* ctx, rusty_cuda_buf* weight, rusty
     q->N = N;
     q->K = K;
     q->layout = layout;
+    q->given_layout = layout;
     q->qmode = qmode;
-    rusty_cuda_buf_retain(weight);
+    // rusty's own Linear stores [in,out] (rusty-graph/src/lib.rs:69-70: x . W).  The TMA / tensor-core kernels stream
+    // rows of [out,in]; with one scale per output feature the two layouts hold the same numbers, so the weight is
+    // re-laid-out ONCE here into a buffer the object owns (N*K more bytes of device memory; the caller's buffer is
+    // not kept and may be released) and every later forward takes the fast kernels.  The reference re-lays its
+    // weights at load as well (dequantisation to f32).  RUSTY_KN_RELAYOUT=0 keeps the [in,out] CUDA-core kernel.
+    static const bool relayout = !(getenv("RUSTY_KN_RELAYOUT") && atoi(getenv("RUSTY_KN_RELAYOUT")) == 0);
+    if (relayout && layout == RUSTY_CUDA_LAYOUT_KN && qmode == RUSTY_CUDA_QMODE_SYM_ROW && K % 16 == 0 && n > 0 && !ctx->capturing) {
+        rusty_cuda_buf* own = nullptr;
+        int rc = rusty_cuda_buf_alloc(ctx, n, 0, &own);
+        if (!rc) {
+            DeviceGuard g(ctx->device);
+            rc = launch_transpose_u8(ctx, (const uint8_t*)weight->ptr, (uint8_t*)own->ptr, K, N);
+            // the caller may free its buffer as soon as this call returns
+            if (!rc) rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "qlinear_create: re-layout");
+        }
+        if (rc) {
+            if (own) rusty_cuda_buf_release(own);
+            delete q;
+            return rc;
+        }
+        q->weight = own;   // the object's own reference
+        q->layout = RUSTY_CUDA_LAYOUT_NK;
+    } else {
+        rusty_cuda_buf_retain(weight);
+    }
     rusty_cuda_buf_retain(scales);
     if (biases) rusty_cuda_buf_retain(biases);
     *out = q;
@@ -194,7 +219,7 @@ int rusty_cuda_qlinear_set_activation(rusty_cuda_qlinear* ql, int act) {
     if (act != RUSTY_CUDA_ACT_NONE && act != RUSTY_CUDA_ACT_SWIGLU_PAIRS)
         return fail(ql->ctx, RUSTY_CUDA_ERR_INVALID_OPERATION, "qlinear_set_activation: unknown activation %d", act);
     if (act == RUSTY_CUDA_ACT_SWIGLU_PAIRS) {
-        if (ql->layout != RUSTY_CUDA_LAYOUT_NK || ql->qmode != RUSTY_CUDA_QMODE_SYM_ROW)
+        if (ql->given_layout != RUSTY_CUDA_LAYOUT_NK || ql->qmode != RUSTY_CUDA_QMODE_SYM_ROW)
             return fail(ql->ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "qlinear_set_activation: pairs need [out,in] storage with one scale per row");
         if (ql->N % 2 != 0)
             return fail(ql->ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "qlinear_set_activation: %u rows are not whole (gate, up) pairs", ql->N);

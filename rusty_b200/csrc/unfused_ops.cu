@@ -159,6 +159,22 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ 
     for (; i < n; i += stride) out[i] = __fadd_rn(a[i], b[i]);
 }
 
+// out[n][k] = in[k][n] for a [K, N] byte matrix: 32 x 32 tiles through shared memory (padded against bank conflicts).
+__global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t K, uint32_t N) {
+    __shared__ uint8_t tile[32][33];
+    const uint32_t n0 = blockIdx.x * 32u, k0 = blockIdx.y * 32u;
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;   // 32 x 8 threads
+    for (uint32_t r = ty; r < 32u; r += 8u) {
+        const uint32_t k = k0 + r, n = n0 + tx;
+        tile[r][tx] = (k < K && n < N) ? in[(size_t)k * N + n] : (uint8_t)0;
+    }
+    __syncthreads();
+    for (uint32_t r = ty; r < 32u; r += 8u) {
+        const uint32_t n = n0 + r, k = k0 + tx;
+        if (n < N && k < K) out[(size_t)n * K + k] = tile[tx][r];
+    }
+}
+
 // out = a + b with a and out of the output type of a Linear (f32 or bf16): the residual add behind a Linear whose
 // kernel has no epilogue for it.
 template <typename YT>
@@ -227,6 +243,13 @@ int launch_affine_dequantize_g64(rusty_cuda_ctx* ctx, const uint8_t* w, const fl
     if (blocks > cap) blocks = cap;
     affine_dequantize_g64_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(w, scales, biases, out, n);
     return after_launch(ctx, "affine_dequantize_g64");
+}
+
+int launch_transpose_u8(rusty_cuda_ctx* ctx, const uint8_t* in, uint8_t* out, uint32_t K, uint32_t N) {
+    const dim3 grid((N + 31) / 32, (K + 31) / 32);
+    if (grid.y > 65535u) return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "transpose: K=%u too large", K);
+    transpose_u8_kernel<<<grid, 256, 0, ctx->stream>>>(in, out, K, N);
+    return after_launch(ctx, "transpose_u8");
 }
 
 int launch_residual_add(rusty_cuda_ctx* ctx, const void* a, const void* b, void* out, size_t n, int y_dtype) {

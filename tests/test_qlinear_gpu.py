@@ -78,12 +78,24 @@ def test_gemv_shapes_affine(ctx, engine, oracle, M, K, N):
     assert rel_err(got, ref) <= TOL_FP32
 
 
-@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (2, 1000, 320), (3, 11008, 4096)])
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (2, 1000, 320), (3, 11008, 4096), (32, 4096, 1024), (7, 48, 40),
+                                   (256, 1024, 520)])
 def test_gemv_kn_layout(ctx, engine, oracle, M, K, N):
-    """rusty's own Linear orientation: weight stored [in, out]."""
+    """rusty's own Linear orientation: weight stored [in, out].  With one scale per output and K % 16 == 0 the weight is
+    re-laid-out once at create and takes the same kernels as [out, in] storage (bit-identical results); otherwise the
+    [in, out] CUDA-core kernel runs."""
     x, q, s = sym_row_linear(K * 3 + N, M, K, N)
     qkn = np.ascontiguousarray(q.T)
-    got = _forward(ctx, engine, QLinear.from_host(ctx, qkn, s, layout=capi.LAYOUT_KN), x)
+    ql_kn = QLinear.from_host(ctx, qkn, s, layout=capi.LAYOUT_KN)
+    got = _forward(ctx, engine, ql_kn, x)
+    if K % 16 == 0:
+        ql_nk = QLinear.from_host(ctx, q, s)
+        assert ql_kn.plan(M) == ql_nk.plan(M)
+        assert_bits_equal(got, _forward(ctx, engine, ql_nk, x))
+        if M >= 128:
+            assert ql_kn.plan(M, DType.BF16, DType.BF16) == "tcgen05_f16"
+    else:
+        assert ql_kn.plan(M) == "gemv"
     ref = oracle.matmul_bt(x, oracle.dequantize_rowscale(q, s), mt=True)
     assert rel_err(got, ref) <= TOL_FP32
     if N % 64 == 0:
