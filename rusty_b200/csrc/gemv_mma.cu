@@ -344,6 +344,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
                 fac_row[mm] = finite ? __longlong_as_double((long long)(1023 - e2 - 21) << 52) : (double)__int_as_float(0x7fc00000);
             }
         }
+        if (threadIdx.x == 0) GDBG(9);
         // digits of one item -> the warp's corner: column 4*m + i holds digit i (0 = most significant)
         auto emit = [&](int mrow, int c, const float4& v) {
             const float sm = mrow == 0 ? sc_row[0] : sc_row[1];
