@@ -137,6 +137,8 @@ int rusty_cuda_ctx_destroy(rusty_cuda_ctx* ctx) {
     if (!ctx) return RUSTY_CUDA_OK;
     DeviceGuard g(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    for (void* p : ctx->deferred_free) cudaFree(p);   // releases parked by a capture that was never ended
+    ctx->deferred_free.clear();
     rusty_cuda_pool_clear(ctx);
     tc_workspace_release(ctx);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -275,6 +277,9 @@ int rusty_cuda_buf_release(rusty_cuda_buf* buf) {
         // any later user of the buffer runs, so no synchronisation is needed.
         std::lock_guard<std::mutex> lk(ctx->pool_mu);
         ctx->pool_bins[buf->bytes].push_back(buf->ptr);
+    } else if (ctx->capturing) {
+        std::lock_guard<std::mutex> lk(ctx->pool_mu);
+        ctx->deferred_free.push_back(buf->ptr);   // freed when the capture ends
     } else {
         DeviceGuard g(ctx->device);
         cudaStreamSynchronize(ctx->stream);

@@ -25,6 +25,22 @@ int rusty_cuda_graph_end(rusty_cuda_ctx* ctx, rusty_cuda_graph** out) {
     ctx->capturing = false;
     cudaGraph_t graph = nullptr;
     int rc = check_cuda(ctx, cudaStreamEndCapture(ctx->stream, &graph), "cudaStreamEndCapture");
+    {   // releases that arrived while the capture was open
+        std::vector<void*> ptrs;
+        std::vector<rusty_cuda_graph*> graphs;
+        {
+            std::lock_guard<std::mutex> lk(ctx->pool_mu);
+            ptrs.swap(ctx->deferred_free);
+            graphs.swap(ctx->deferred_graphs);
+        }
+        if (!ptrs.empty() || !graphs.empty()) cudaStreamSynchronize(ctx->stream);
+        for (void* p : ptrs) cudaFree(p);
+        for (rusty_cuda_graph* g2 : graphs) {
+            cudaGraphExecDestroy(g2->exec);
+            cudaGraphDestroy(g2->graph);
+            delete g2;
+        }
+    }
     if (rc) return rc;
     uint64_t recorded = ctx->launches.load() - ctx->launches_at_capture;
     // Captured launches did not run: take them back out of the counter; each
@@ -63,6 +79,11 @@ int rusty_cuda_graph_launch(rusty_cuda_ctx* ctx, rusty_cuda_graph* graph) {
 
 int rusty_cuda_graph_destroy(rusty_cuda_graph* graph) {
     if (!graph) return RUSTY_CUDA_OK;
+    if (graph->ctx->capturing) {   // destroyed while another capture is open on its context: after that capture
+        std::lock_guard<std::mutex> lk(graph->ctx->pool_mu);
+        graph->ctx->deferred_graphs.push_back(graph);
+        return RUSTY_CUDA_OK;
+    }
     DeviceGuard g(graph->ctx->device);
     cudaStreamSynchronize(graph->ctx->stream);
     cudaGraphExecDestroy(graph->exec);

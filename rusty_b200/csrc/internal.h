@@ -49,6 +49,10 @@ struct rusty_cuda_ctx {
     int tc_dbg_seq = 0, tc_dbg_slots = 0;
     // stream capture in progress (rusty_cuda_graph_begin .. _end)
     bool capturing = false;
+    // Releases that arrive while a capture is open (a host-language destructor may run at any time) are parked here:
+    // freeing or synchronising would invalidate the capture.  rusty_cuda_graph_end performs them.
+    std::vector<void*> deferred_free;
+    std::vector<struct rusty_cuda_graph*> deferred_graphs;
     uint64_t launches_at_capture = 0;
 };
 

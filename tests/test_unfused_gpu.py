@@ -175,3 +175,40 @@ def test_shape_errors_are_status_codes(ctx, engine):
         engine.matmul(ctx, a, b, small)
     assert e.value.kind == "InvalidDimensions"
     ctx.sync()  # the context is still usable
+
+
+def test_release_while_a_capture_is_open_is_deferred(ctx, engine):
+    """A host-language destructor may run at any time, also between graph_begin and graph_end; freeing device memory
+    or synchronising there would invalidate the capture, so the release is parked until the capture has ended."""
+    from rusty_b200 import QLinear
+    from rusty_b200.backend import Graph
+    from rusty_b200.workloads import sym_row_linear
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal(1000).astype(np.float32)
+    b = rng.standard_normal(1000).astype(np.float32)
+    ta, tb, out = UnifiedTensor.new(ctx, a, [1000]), UnifiedTensor.new(ctx, b, [1000]), UnifiedTensor.empty(ctx, [1000])
+    victim = UnifiedTensor.new(ctx, a, [1000])          # not pooled: its release is a cudaFree
+    x, q, s = sym_row_linear(0, 1, 256, 64)
+    ql_victim = QLinear.from_host(ctx, q, s)             # a whole fused linear dies inside the capture as well
+    old = Graph(ctx)
+    with old:
+        engine.add(ctx, ta, tb, out)
+    g = Graph(ctx)
+    with g:
+        engine.add(ctx, ta, tb, out)
+        del victim
+        del ql_victim
+        del old                                          # a graph destroyed while another capture is open
+        engine.add(ctx, out, tb, out)
+    g.launch()
+    ctx.sync()
+    assert np.array_equal(out.to_vec(ctx), (a + b) + b)
+    # the context is fully usable afterwards (allocations, eager launches, another capture)
+    t2 = UnifiedTensor.new(ctx, b, [1000])
+    engine.add(ctx, t2, t2, out)
+    assert np.array_equal(out.to_vec(ctx), b + b)
+    g2 = Graph(ctx)
+    with g2:
+        engine.add(ctx, ta, ta, out)
+    g2.launch()
+    assert np.array_equal(out.to_vec(ctx), a + a)
