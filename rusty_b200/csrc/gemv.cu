@@ -388,7 +388,10 @@ int launch_mb(rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a, const void* x, v
     const bool affine = a.qmode == RUSTY_CUDA_QMODE_AFFINE_G64;
     if (a.layout == RUSTY_CUDA_LAYOUT_NK)
         return affine ? launch_nk<MB, true, XT, YT>(ctx, a, x, y, M) : launch_nk<MB, false, XT, YT>(ctx, a, x, y, M);
-    return affine ? launch_kn<MB, true, XT, YT>(ctx, a, x, y, M) : launch_kn<MB, false, XT, YT>(ctx, a, x, y, M);
+    if constexpr (MB <= 2)
+        return affine ? launch_kn<MB, true, XT, YT>(ctx, a, x, y, M) : launch_kn<MB, false, XT, YT>(ctx, a, x, y, M);
+    else
+        return rusty::fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "gemv: [in,out] weights take at most two rows per pass");
 }
 
 template <typename XT, typename YT>
@@ -403,18 +406,21 @@ int launch_typed(rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a) {
         }
         return (size_t)mb * a.K * 4 + (size_t)KN_SLICES * mb * KN_COLS * 4;
     };
-    int mb_max = a.layout == RUSTY_CUDA_LAYOUT_NK ? 4 : 2;
+    // [out,in]: up to eight activation rows share one pass over the weights (the reference's affine layout has no
+    // tensor-core kernel for f32 activations, so decode batches are passes of this kernel: 32 rows = 4 passes)
+    int mb_max = a.layout == RUSTY_CUDA_LAYOUT_NK ? 8 : 2;
     while (mb_max > 1 && stage_bytes(mb_max) > budget) mb_max >>= 1;
     if (stage_bytes(mb_max) > budget)
         return rusty::fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "gemv: K=%u does not fit the shared-memory stage", a.K);
     uint32_t m0 = 0;
     while (m0 < a.M) {
         int rows = (int)(a.M - m0);
-        int mb = rows >= 4 && mb_max >= 4 ? 4 : rows >= 2 && mb_max >= 2 ? 2 : 1;
+        int mb = rows >= 8 && mb_max >= 8 ? 8 : rows >= 4 && mb_max >= 4 ? 4 : rows >= 2 && mb_max >= 2 ? 2 : 1;
         if (rows > mb) rows = mb;
         const void* xp = (const char*)a.x + (size_t)m0 * a.K * sizeof(XT);
         void* yp = (char*)a.y + (size_t)m0 * a.ldy * sizeof(YT);
-        int rc = mb == 4   ? launch_mb<4, XT, YT>(ctx, a, xp, yp, rows)
+        int rc = mb == 8   ? launch_mb<8, XT, YT>(ctx, a, xp, yp, rows)
+                 : mb == 4 ? launch_mb<4, XT, YT>(ctx, a, xp, yp, rows)
                  : mb == 2 ? launch_mb<2, XT, YT>(ctx, a, xp, yp, rows)
                            : launch_mb<1, XT, YT>(ctx, a, xp, yp, rows);
         if (rc) return rc;
