@@ -185,8 +185,14 @@ RUSTY_CUDA_API int rusty_cuda_add_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf*
  * K % 16 == 0 is re-laid-out ONCE, inside this call, into an [out,in] buffer
  * that the object owns (N*K more bytes of device memory), so that every
  * forward runs on the TMA / tensor-core kernels; the caller's weight buffer
- * is then not kept and may be released.  (RUSTY_KN_RELAYOUT=0 in the
- * environment keeps the [in,out] CUDA-core kernel instead.)
+ * is then not kept and may be released.  An AFFINE_G64 weight in LAYOUT_KN
+ * (the reference's own quantised format: one scale and bias per 64
+ * consecutive OUTPUT features of an input row) with K % 128 == 0 is re-laid-out
+ * the same way, bytes to [out,in] and scales / biases to [N/64][K] (N*K*9/8
+ * more bytes; none of the caller's three buffers is kept): its forwards run on
+ * the int8 tensor-core GEMV with the group's scales folded into the
+ * activations.  (RUSTY_KN_RELAYOUT=0 in the environment keeps the [in,out]
+ * CUDA-core kernel for both.)
  *   AFFINE_G64: weight u8 [N*K], scales/biases f32 [N*K/64]; K % 64 == 0 for
  *               LAYOUT_NK (N % 64 == 0 for LAYOUT_KN) so a group never
  *               straddles two rows.

@@ -434,6 +434,7 @@ int launch_typed(rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a) {
 namespace rusty {
 
 bool gemv_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
+    if (a.qmode == QMODE_AFFINE_GC) return false;   // that re-layout exists for gemv_mma only
     if (a.layout == RUSTY_CUDA_LAYOUT_NK) return a.K % 16 == 0;
     if (a.act) return false;  // pairs are rows of an [out,in] matrix
     return a.N % 16 == 0;

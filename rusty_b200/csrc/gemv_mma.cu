@@ -54,6 +54,8 @@ constexpr int MAX_M = 2;                     // activation rows: 4 digit columns
 struct GmParams {
     const uint8_t* W;
     const float* scales;
+    const float* gscale;   // group-column affine weights (GC kernel): scale and bias of row group n / 64 at every k,
+    const float* gbias;    //   [N/64][K] each; the weight bytes are then unsigned
     const void* x;
     void* y;
     int M, N, K;
@@ -65,6 +67,7 @@ struct GmParams {
     int units;      // ceil(N / 2): row pairs dealt evenly to the CTAs
     int sc_cap;     // row scales kept in shared memory per CTA (>= the largest row share when it fits)
     int ldy, y_col0;
+    int gc_rows;    // GC kernel: weight rows per CTA (16, 32 or 64: a CTA stays inside one 64-row group)
     int act;        // RUSTY_CUDA_ACT_SWIGLU_PAIRS: rows 2j, 2j+1 -> column (y_col0 + 2j) / 2
     int x_bf16, y_bf16;
     rusty_cuda_dev_status* status;
@@ -83,6 +86,23 @@ struct GmParams {
 // D[16x8] += A[16x32] * B[32x8], int8 operands, int32 accumulators.
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 16 bytes of shared memory as a volatile asm statement, so that the load stays in front of the mbarrier arrive that
+// hands the ring slot back.  Written as a plain C++ load it was moved behind the arrive, down to the first use of the
+// value (the first two stages are fetched long before they are used): the registers then held what the slot had been
+// refilled with in the meantime, 16 rows further down the matrix.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// The same with unsigned weight bytes (affine weights are u8).
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -128,6 +148,23 @@ __device__ __noinline__ void emit_digits(float v0, float v1, float v2, float v3,
     }
 }
 
+// GC ("group columns"): the reference's own layout, [in,out] storage with one (scale, bias) per 64 consecutive
+// OUTPUT features of an input row, after its one-time re-layout to [out,in]:
+//     y[m,n] = sum_k x[m,k] * (u[n,k] * s[g,k] + b[g,k]),   g = n / 64
+//            = sum_k (x[m,k] * s[g,k]) * u[n,k]  +  sum_k x[m,k] * b[g,k]
+// so for the 64 rows of a group the scales move over to the activations: a' = x (.) s_g is digitised instead of x, the
+// unsigned weight bytes go into the tensor core as they are, and the bias term is one number per group and
+// activation row.  A CTA takes 16, 32 or 64 rows of one group, so everything it needs of s and b is two K-long vectors.
+// Weight rows per CTA of the GC kernel: the largest of 64, 32, 16 that still gives every SM a CTA (a CTA's fixed cost,
+// the digits of its activations, is paid per CTA; too few CTAs leave SMs idle).
+int gc_rows_per_cta(const rusty_cuda_ctx* ctx, uint32_t N, uint32_t M) {
+    const uint32_t pairs = (M + MAX_M - 1) / MAX_M, sms = ctx->sm_count > 0 ? (uint32_t)ctx->sm_count : 1u;
+    for (uint32_t rows = 64; rows > 16; rows /= 2)
+        if ((N / rows) * pairs >= sms) return (int)rows;
+    return 16;
+}
+
+template <bool GC>
 __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_constant__ CUtensorMap map_w, const GmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // carve: [weight stages][digits, one corner per warp][partials 2 x GW x 32 doubles][barriers][flag][row scales]
@@ -159,8 +196,16 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
     }
     __syncthreads();
 
+    // GC: blockIdx.y picks the pair of activation rows this CTA works on (batches of more than two rows)
+    const int m_base = GC ? (int)blockIdx.y * MAX_M : 0;
+    const int Mrows = GC ? min(MAX_M, p.M - m_base) : p.M;
     int row0, rows;
-    cta_rows(p, row0, rows);
+    if constexpr (GC) {
+        row0 = (int)blockIdx.x * p.gc_rows;
+        rows = min(p.gc_rows, p.N - row0);
+    } else {
+        cta_rows(p, row0, rows);
+    }
     const int groups = (rows + STAGE_ROWS - 1) / STAGE_ROWS;
     const int total = groups * p.nch;          // stages this CTA walks: index = group * nch + chunk
 
@@ -170,7 +215,8 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
     if (warp == GW + 1) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
-            const uint64_t pol = policy_evict_first();
+            // one pass over the weights: nothing to keep in L2; several row pairs: the other pairs' CTAs read them again
+            const uint64_t pol = (GC && gridDim.y > 1) ? policy_evict_last() : policy_evict_first();
             // What the ring will not hold at first: into L2 now, so that it is a short trip later.  Long streams
             // are left alone (the ring runs far ahead of the consumers there anyway).
             if (total <= 3 * p.stages)
@@ -193,7 +239,8 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
         // ------------------------------ reducer -------------------------------
         // The row scales are a property of the weight: fetch this CTA's share before waiting for the previous kernel,
         // so that no trip to memory is left in the per-group chain below.
-        for (int i = lane; i < min(rows, p.sc_cap); i += 32) s_wscale[i] = __ldg(p.scales + row0 + i);
+        if constexpr (!GC)
+            for (int i = lane; i < min(rows, p.sc_cap); i += 32) s_wscale[i] = __ldg(p.scales + row0 + i);
         __syncwarp();
         pdl_wait();  // y belongs to earlier kernels until now
         // lane = m * 16 + r: activation row m, weight row r of the group
@@ -203,14 +250,14 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
             if (!mbar_wait(&done[b], ((uint32_t)g >> 1) & 1u, abort_flag, p.status, 32)) break;
             if (g == 0 && lane == 0) GDBG(8);
             double a = 0.0;
-            const double* src = sPart + (size_t)b * GW * 32 + lane;
+            const volatile double* src = sPart + (size_t)b * GW * 32 + lane;   // volatile: read BEFORE the buffer is handed back below
 #pragma unroll
             for (int w = 0; w < GW; ++w) a += src[w * 32];   // the K slices in a fixed order: the same bits on every run
             __syncwarp();
             if (lane == 0) mbar_arrive(&freeb[b]);
             const int i0 = group_start(g) + r, n = row0 + i0;
-            const bool in = m < p.M && i0 < rows && i0 >= g * STAGE_ROWS;   // rows a shifted last group repeats are skipped
-            const float sc = !in ? 0.0f : (i0 < p.sc_cap ? s_wscale[i0] : __ldg(p.scales + n));
+            const bool in = m < Mrows && i0 < rows && i0 >= g * STAGE_ROWS;   // rows a shifted last group repeats are skipped
+            const float sc = !in ? 0.0f : GC ? 1.0f : (i0 < p.sc_cap ? s_wscale[i0] : __ldg(p.scales + n));
             // the sum of the slices is exact in double (integers times powers of two); one rounding to f32, then the
             // weight's scale (one more rounding), as in the other fused kernels
             float v = __double2float_rn(a) * sc;
@@ -225,7 +272,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
                 col >>= 1;
             }
             if (live) {
-                const size_t at = (size_t)m * p.ldy + col;
+                const size_t at = (size_t)(m_base + m) * p.ldy + col;
                 if (p.y_bf16) {
                     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.y) + at;
                     const __nv_bfloat16 b = __float2bfloat16_rn(v);
@@ -257,10 +304,11 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
         auto fetch = [&](uint4 (&w)[4]) {
             if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 33)) { ok = false; return; }
             const uint8_t* st = sW + (size_t)stage * STAGE_BYTES;
-            w[0] = *reinterpret_cast<const uint4*>(st + frag0);
-            w[1] = *reinterpret_cast<const uint4*>(st + frag1);
-            w[2] = *reinterpret_cast<const uint4*>(st + frag0 + 8 * 128);   // row g8 + 8: the same swizzle
-            w[3] = *reinterpret_cast<const uint4*>(st + frag1 + 8 * 128);
+            const uint32_t sa = smem_u32(st);
+            w[0] = lds128(sa + frag0);
+            w[1] = lds128(sa + frag1);
+            w[2] = lds128(sa + frag0 + 8 * 128);   // row g8 + 8: the same swizzle
+            w[3] = lds128(sa + frag1 + 8 * 128);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);   // this warp's share of the stage is in registers
             if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -271,15 +319,45 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
         if (total > 0) fetch(wA);
         if (ok && total > 1) fetch(wB);
 
+        // GC: the group's scale and bias vectors belong to the weight; this lane's share of the items held in
+        // registers is asked into L2 before the wait as well
+        constexpr int XV = 4;
+        auto item_k = [&](int c) { return c * KC + warp * KB + lane * 4; };
+        const float* gs = nullptr;
+        const float* gb = nullptr;
+        double cb_row[MAX_M] = {0.0, 0.0};   // this lane's, later this warp's, part of sum_k x[m,k] * b[g,k]
+        if constexpr (GC) {
+            gs = p.gscale + (size_t)(row0 / 64) * p.K;
+            gb = p.gbias + (size_t)(row0 / 64) * p.K;
+            int c = 0;
+#pragma unroll
+            for (int i = 0; i < XV; ++i) {
+                const int k = item_k(c);
+                const bool live = i < Mrows * p.nch && k < p.K;
+                if (live) {   // read beside x after the wait: a short trip then
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(gs + k));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(gb + k));
+                }
+                if (++c == p.nch) c = 0;
+            }
+        }
+        // GC: v <- v (.) s, and the bias sum when `with_bias` (the first of the two reads of an item)
+        auto fold_group = [&](int mrow, float4& v, const float4& s4, const float4& b4, bool with_bias) {
+            if (with_bias) {
+                const double d = (double)v.x * b4.x + (double)v.y * b4.y + (double)v.z * b4.z + (double)v.w * b4.w;
+                if (mrow == 0) cb_row[0] += d;
+                else cb_row[1] += d;
+            }
+            v.x *= s4.x; v.y *= s4.y; v.z *= s4.z; v.w *= s4.w;
+        };
+
         pdl_wait();  // x may come from the previous kernel
         if (threadIdx.x == 0) GDBG(1);
 
         // ---- this warp's slice of the activations: item i = (row m = i / nch, chunk c = i % nch) is the four
         // activations at k = c*KC + warp*KB + 4*lane.  The first XV items stay in registers between the maximum
         // and the digits (K <= 4096 with one row, 2048 with two); further items are read twice.
-        const int items = p.M * p.nch;
-        auto item_k = [&](int c) { return c * KC + warp * KB + lane * 4; };
-        constexpr int XV = 4;
+        const int items = Mrows * p.nch;
         float4 xv[XV];
         float mx_row[MAX_M] = {0.f, 0.f};
         auto fold_max = [&](int mrow, const float4& v) {
@@ -295,7 +373,13 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
 #pragma unroll
             for (int i = 0; i < XV; ++i) {
                 const int k = item_k(c);
-                xv[i] = (i < items && k < p.K) ? load_x4(p, mrow, k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                xv[i] = (i < items && k < p.K) ? load_x4(p, m_base + mrow, k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if constexpr (GC) {
+                    const bool live = i < items && k < p.K;
+                    const float4 s4 = live ? __ldg(reinterpret_cast<const float4*>(gs + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 b4 = live ? __ldg(reinterpret_cast<const float4*>(gb + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    fold_group(mrow, xv[i], s4, b4, true);
+                }
                 if (++c == p.nch) { c = 0; ++mrow; }
             }
             mrow = 0; c = 0;
@@ -311,7 +395,10 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
                 for (int u = 0; u < 4; ++u) {
                     const int k = item_k(c);
                     mr[u] = mrow;
-                    v[u] = (i0 + u < items && k < p.K) ? load_x4(p, mrow, k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const bool live = i0 + u < items && k < p.K;
+                    v[u] = live ? load_x4(p, m_base + mrow, k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if constexpr (GC)
+                        if (live) fold_group(mrow, v[u], __ldg(reinterpret_cast<const float4*>(gs + k)), __ldg(reinterpret_cast<const float4*>(gb + k)), true);
                     if (++c == p.nch) { c = 0; ++mrow; }
                 }
 #pragma unroll
@@ -324,7 +411,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
         double fac_row[MAX_M] = {0.0, 0.0};   // 1/s * 128^-3: powers of two, the product is exact
 #pragma unroll
         for (int mm = 0; mm < MAX_M; ++mm) {
-            if (mm < p.M) {
+            if (mm < Mrows) {
                 float v = mx_row[mm];
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
@@ -343,6 +430,13 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
                 // ... and NaN outputs.  2^(-e2 - 21) as a double, built from its exponent field
                 fac_row[mm] = finite ? __longlong_as_double((long long)(1023 - e2 - 21) << 52) : (double)__int_as_float(0x7fc00000);
             }
+        }
+        if constexpr (GC) {
+#pragma unroll
+            for (int mm = 0; mm < MAX_M; ++mm)
+                if (mm < Mrows)
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) cb_row[mm] += __shfl_xor_sync(0xffffffffu, cb_row[mm], off);
         }
         if (threadIdx.x == 0) GDBG(9);
         // digits of one item -> the warp's corner: column 4*m + i holds digit i (0 = most significant)
@@ -367,7 +461,10 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
                     const int k = item_k(c);
                     mr[u] = mrow;
                     cc[u] = c;
-                    v[u] = (i0 + u < items && k < p.K) ? load_x4(p, mrow, k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const bool live = i0 + u < items && k < p.K;
+                    v[u] = live ? load_x4(p, m_base + mrow, k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if constexpr (GC)
+                        if (live) fold_group(mrow, v[u], __ldg(reinterpret_cast<const float4*>(gs + k)), make_float4(0.f, 0.f, 0.f, 0.f), false);
                     if (++c == p.nch) { c = 0; ++mrow; }
                 }
 #pragma unroll
@@ -378,6 +475,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
         __syncwarp();
         if (threadIdx.x == 0) GDBG(3);
         const double fac = (j >> 1) == 0 ? fac_row[0] : fac_row[1];   // of the activation row this lane folds (m = j / 2)
+        [[maybe_unused]] const double cbw = (j >> 1) == 0 ? cb_row[0] : cb_row[1];   // GC: this K slice's bias term of that row
 
         // ---- main loop, software-pipelined over the stages ----
         const bool b_live = g8 < p.R;
@@ -396,10 +494,17 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
                 d0 = *reinterpret_cast<const uint4*>(dig_b + (size_t)c * KB);
                 d1 = *reinterpret_cast<const uint4*>(dig_b + (size_t)c * KB + 16);
             }
-            mma_s8(acc[0], w[0].x, w[2].x, w[0].y, w[2].y, d0.x, d0.y);
-            mma_s8(acc[1], w[0].z, w[2].z, w[0].w, w[2].w, d0.z, d0.w);
-            mma_s8(acc[2], w[1].x, w[3].x, w[1].y, w[3].y, d1.x, d1.y);
-            mma_s8(acc[3], w[1].z, w[3].z, w[1].w, w[3].w, d1.z, d1.w);
+            if constexpr (GC) {
+                mma_u8s8(acc[0], w[0].x, w[2].x, w[0].y, w[2].y, d0.x, d0.y);
+                mma_u8s8(acc[1], w[0].z, w[2].z, w[0].w, w[2].w, d0.z, d0.w);
+                mma_u8s8(acc[2], w[1].x, w[3].x, w[1].y, w[3].y, d1.x, d1.y);
+                mma_u8s8(acc[3], w[1].z, w[3].z, w[1].w, w[3].w, d1.z, d1.w);
+            } else {
+                mma_s8(acc[0], w[0].x, w[2].x, w[0].y, w[2].y, d0.x, d0.y);
+                mma_s8(acc[1], w[0].z, w[2].z, w[0].w, w[2].w, d0.z, d0.w);
+                mma_s8(acc[2], w[1].x, w[3].x, w[1].y, w[3].y, d1.x, d1.y);
+                mma_s8(acc[3], w[1].z, w[3].z, w[1].w, w[3].w, d1.z, d1.w);
+            }
             if (++c == p.nch) {
                 // accumulator element e: weight row g8 (e = 0, 1) or g8 + 8 (e = 2, 3), digit column 2j + (e & 1).
                 // Columns 4m .. 4m+3 are the digits of activation row m, most significant first: lane pair (2m, 2m+1).
@@ -419,10 +524,12 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
                 const int b = g & 1;
                 if (g >= 2 && !mbar_wait(&freeb[b], (((uint32_t)g >> 1) - 1u) & 1u, abort_flag, p.status, 34)) ok = false;
                 if (ok) {
-                    if (!(j & 1) && (j >> 1) < p.M) {
+                    if (!(j & 1) && (j >> 1) < Mrows) {
                         double* dst = sPart + (size_t)(b * GW + warp) * 32 + (j >> 1) * 16 + g8;
-                        dst[0] = (double)(v[0] * 16384 + p0) * fac;
-                        dst[8] = (double)(v[1] * 16384 + p1) * fac;
+                        double o0 = (double)(v[0] * 16384 + p0) * fac, o1 = (double)(v[1] * 16384 + p1) * fac;
+                        if constexpr (GC) { o0 += cbw; o1 += cbw; }
+                        dst[0] = o0;
+                        dst[8] = o1;
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&done[b]);
@@ -449,11 +556,12 @@ __global__ void __launch_bounds__(GM_THREADS, 2) gemv_mma_kernel(const __grid_co
     }
 }
 
-int launch_gm(rusty_cuda_ctx* ctx, const CUtensorMap& map_w, const GmParams& p, int grid, size_t smem) {
-    auto kern = gemv_mma_kernel;
+template <bool GC>
+int launch_gm(rusty_cuda_ctx* ctx, const CUtensorMap& map_w, const GmParams& p, dim3 grid, size_t smem) {
+    auto kern = gemv_mma_kernel<GC>;
     cudaError_t e = rusty::ensure_dynamic_smem((const void*)kern, ctx->device, smem);
     if (e != cudaSuccess) return rusty::check_cuda(ctx, e, "gemv_mma: cudaFuncSetAttribute");
-    cudaError_t le = launch_pdl(kern, dim3(grid), dim3(GM_THREADS), smem, ctx->stream, map_w, p);
+    cudaError_t le = launch_pdl(kern, grid, dim3(GM_THREADS), smem, ctx->stream, map_w, p);
     if (le != cudaSuccess) return rusty::check_cuda(ctx, le, "gemv_mma");
     return rusty::after_launch(ctx, "gemv_mma");
 }
@@ -461,21 +569,23 @@ int launch_gm(rusty_cuda_ctx* ctx, const CUtensorMap& map_w, const GmParams& p, 
 // Shared-memory plan: digit planes + partials + scale cache + barriers are fixed by the shape; the rest of the budget
 // is the ring of weight stages.
 bool plan_smem(const rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a, int* stages, size_t* smem, int* D, int* R, int* nch, int* sc_cap) {
-    *D = a.x_dtype == RUSTY_CUDA_F32 ? 4 : 3;
-    *R = 4 * (int)a.M;
+    const bool gc = a.qmode == rusty::QMODE_AFFINE_GC;
+    const int M = a.M > (uint32_t)MAX_M ? MAX_M : (int)a.M;   // (GC: more rows go as passes of two)
+    *D = (a.x_dtype == RUSTY_CUDA_F32 || gc) ? 4 : 3;   // (GC: x times a group scale is a full f32 whatever x was)
+    *R = 4 * M;
     *nch = (int)((a.K + KC - 1) / KC);
     const int sms = ctx->sm_count > 0 ? ctx->sm_count : 1;
     const int units = (int)((a.N + 1) / 2);
     const int grid = units < sms ? units : sms;
-    const int rows_max = 2 * ((units + grid - 1) / grid);
-    *sc_cap = rows_max < 4096 ? rows_max : 4096;
+    const int rows_max = gc ? gc_rows_per_cta(ctx, a.N, a.M) : 2 * ((units + grid - 1) / grid);
+    *sc_cap = gc ? 0 : rows_max < 4096 ? rows_max : 4096;
     const size_t dig = (size_t)GW * *R * ((size_t)*nch * KB + 16);   // one corner per warp
     const size_t part = (size_t)2 * GW * 32 * 8;
     const size_t fixed = dig + part + (size_t)*sc_cap * 4 + 1024;
     // Half of the SM at most while the kernel is short (the next kernel's CTA then sits beside this one and lands its
     // weights while this one computes); a CTA that streams many times the ring takes the whole SM: depth matters more.
     const size_t optin = ctx->smem_optin > 2048 ? ctx->smem_optin - 2048 : 0;
-    const bool longrun = (size_t)rows_max * a.K > 6 * (optin / 2);
+    const bool longrun = (size_t)rows_max * a.K > 6 * (optin / 2) || fixed + 1024 + 2 * (size_t)STAGE_BYTES > optin / 2;
     const size_t budget = longrun ? optin : optin / 2;
     if (budget < fixed + 1024 + 2 * (size_t)STAGE_BYTES) return false;
     int s = (int)((budget - fixed - 1024) / STAGE_BYTES);
@@ -490,8 +600,9 @@ bool plan_smem(const rusty_cuda_ctx* ctx, const rusty::QLinearArgs& a, int* stag
 namespace rusty {
 
 bool gemv_mma_supported(const rusty_cuda_ctx* ctx, const QLinearArgs& a) {
-    if (a.layout != RUSTY_CUDA_LAYOUT_NK || a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
-    if (a.M < 1 || a.M > (uint32_t)MAX_M) return false;
+    const bool gc = a.qmode == QMODE_AFFINE_GC;
+    if (a.layout != RUSTY_CUDA_LAYOUT_NK || (a.qmode != RUSTY_CUDA_QMODE_SYM_ROW && !gc)) return false;
+    if (gc ? (a.N % 64 != 0 || a.act || a.M < 1) : (a.M < 1 || a.M > (uint32_t)MAX_M)) return false;
     if (a.K % 128 != 0 || !encode_tiled_fn()) return false;   // the weight is read as [K/128][rows][128 bytes] by TMA
     static const bool off = getenv("RUSTY_NO_GEMV_MMA") != nullptr;
     if (off) return false;
@@ -506,8 +617,11 @@ int launch_gemv_mma(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     size_t smem = 0;
     if (!plan_smem(ctx, a, &p.stages, &smem, &p.D, &p.R, &p.nch, &p.sc_cap))
         return fail(ctx, RUSTY_CUDA_ERR_UNSUPPORTED, "gemv_mma: the digit planes of K=%u do not fit shared memory", a.K);
+    const bool gc = a.qmode == QMODE_AFFINE_GC;
     p.W = a.w;
     p.scales = a.scales;
+    p.gscale = gc ? a.scales : nullptr;
+    p.gbias = gc ? a.biases : nullptr;
     p.x = a.x;
     p.y = a.y;
     p.M = (int)a.M;
@@ -534,7 +648,22 @@ int launch_gemv_mma(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     CUtensorMap map_w;
     if (!make_map_u8_rows_by_kblocks(&map_w, a.w, a.N, a.K, STAGE_ROWS, KC / 128))
         return fail(ctx, RUSTY_CUDA_ERR_KERNEL_EXECUTION, "gemv_mma: cuTensorMapEncodeTiled failed");
-    return launch_gm(ctx, map_w, p, grid, smem);
+    if (!gc) return launch_gm<false>(ctx, map_w, p, dim3(grid), smem);
+    // group-column affine weights: one CTA per 32 rows and pair of activation rows (at most 65535 pairs per launch)
+    const uint32_t pairs = (a.M + MAX_M - 1) / MAX_M;
+    const size_t xs = p.x_bf16 ? 2 : 4, ys = p.y_bf16 ? 2 : 4;
+    for (uint32_t p0 = 0; p0 < pairs; p0 += 65535u) {
+        GmParams q = p;
+        q.gc_rows = gc_rows_per_cta(ctx, a.N, a.M);
+        const uint32_t np = pairs - p0 < 65535u ? pairs - p0 : 65535u, m0 = p0 * MAX_M;
+        q.M = (int)(a.M - m0 < np * MAX_M ? a.M - m0 : np * MAX_M);
+        q.x = reinterpret_cast<const char*>(a.x) + (size_t)m0 * a.K * xs;
+        q.y = reinterpret_cast<char*>(a.y) + (size_t)m0 * a.ldy * ys;
+        if (a.N / q.gc_rows > 148 || pairs > 1) q.dbg = nullptr;   // (development builds: a timeline region holds 148 CTAs of one launch)
+        int rc = launch_gm<true>(ctx, map_w, q, dim3(a.N / q.gc_rows, np), smem);
+        if (rc) return rc;
+    }
+    return RUSTY_CUDA_OK;
 }
 
 }  // namespace rusty

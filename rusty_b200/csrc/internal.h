@@ -190,6 +190,10 @@ bool qlinear_norm_fused(const rusty_cuda_ctx* ctx, const rusty_cuda_qlinear* ql,
 bool tc_norm_fused(uint32_t M, uint32_t K);
 // out[n][k] = in[k][n], bytes (the one-time re-layout of an [in,out] weight)
 int launch_transpose_u8(rusty_cuda_ctx* ctx, const uint8_t* in, uint8_t* out, uint32_t K, uint32_t N);
+int launch_transpose_f32(rusty_cuda_ctx* ctx, const float* in, float* out, uint32_t K, uint32_t N);
+// Internal quantisation mode of a re-laid-out AFFINE_G64 [in,out] weight: bytes stored [out,in], scales and biases
+// stored [N/64][K] (one pair per 64 consecutive OUTPUT features and input k).  Never crosses the C ABI.
+constexpr int QMODE_AFFINE_GC = 64;
 int launch_residual_add(rusty_cuda_ctx* ctx, const void* a, const void* b, void* out, size_t n, int y_dtype);
 bool qlinear_residual_fused(const rusty_cuda_qlinear* ql, int x_dtype, uint32_t M, int y_dtype);
 

@@ -20,6 +20,19 @@ static size_t dtype_size(int dt) {
     }
 }
 
+// whether the group-column affine GEMV can run a weight of this shape at all (checked before the re-layout)
+static bool gc_kernel_available(const rusty_cuda_ctx* ctx, uint32_t N, uint32_t K) {
+    QLinearArgs a{};
+    a.N = N;
+    a.K = K;
+    a.layout = RUSTY_CUDA_LAYOUT_NK;
+    a.qmode = QMODE_AFFINE_GC;
+    a.x_dtype = RUSTY_CUDA_F32;
+    a.y_dtype = RUSTY_CUDA_F32;
+    a.M = 2;
+    return gemv_mma_supported(ctx, a);
+}
+
 uint32_t f16tc_min_rows() {
     // RUSTY_F16_MIN_ROWS overrides the batch size from which bf16 activations take the fp16/bf16 MMA kernel (tuning aid).
     static int v = -1;
@@ -205,6 +218,38 @@ int rusty_cuda_qlinear_create(rusty_cuda_ctx* ctx, rusty_cuda_buf* weight, rusty
         }
         q->weight = own;   // the object's own reference
         q->layout = RUSTY_CUDA_LAYOUT_NK;
+    } else if (relayout && layout == RUSTY_CUDA_LAYOUT_KN && qmode == RUSTY_CUDA_QMODE_AFFINE_G64 && K % 128 == 0 && N % 64 == 0 && n > 0 &&
+               !ctx->capturing && gc_kernel_available(ctx, N, K)) {
+        // The reference's own quantised format: [in,out] bytes with a (scale, bias) per 64 consecutive OUTPUT features
+        // of an input row (rusty-loader/src/lib.rs:155-218).  Re-laid-out once as well: bytes to [out,in], scales and
+        // biases to [N/64][K], all three into buffers the object owns; the tensor-core GEMV then multiplies the
+        // activations by a group's scale vector instead of the weights (gemv_mma.cu).
+        rusty_cuda_buf *own = nullptr, *os = nullptr, *ob = nullptr;
+        const size_t gbytes = n / 64 * 4;
+        int rc = rusty_cuda_buf_alloc(ctx, n, 0, &own);
+        if (!rc) rc = rusty_cuda_buf_alloc(ctx, gbytes, 0, &os);
+        if (!rc) rc = rusty_cuda_buf_alloc(ctx, gbytes, 0, &ob);
+        if (!rc) {
+            DeviceGuard g(ctx->device);
+            rc = launch_transpose_u8(ctx, (const uint8_t*)weight->ptr, (uint8_t*)own->ptr, K, N);
+            if (!rc) rc = launch_transpose_f32(ctx, (const float*)scales->ptr, (float*)os->ptr, K, N / 64);
+            if (!rc) rc = launch_transpose_f32(ctx, (const float*)biases->ptr, (float*)ob->ptr, K, N / 64);
+            if (!rc) rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "qlinear_create: re-layout");
+        }
+        if (rc) {
+            if (own) rusty_cuda_buf_release(own);
+            if (os) rusty_cuda_buf_release(os);
+            if (ob) rusty_cuda_buf_release(ob);
+            delete q;
+            return rc;
+        }
+        q->weight = own;
+        q->scales = os;
+        q->biases = ob;
+        q->layout = RUSTY_CUDA_LAYOUT_NK;
+        q->qmode = QMODE_AFFINE_GC;
+        *out = q;
+        return RUSTY_CUDA_OK;
     } else {
         rusty_cuda_buf_retain(weight);
     }

@@ -159,14 +159,16 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ 
     for (; i < n; i += stride) out[i] = __fadd_rn(a[i], b[i]);
 }
 
-// out[n][k] = in[k][n] for a [K, N] byte matrix: 32 x 32 tiles through shared memory (padded against bank conflicts).
-__global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t K, uint32_t N) {
-    __shared__ uint8_t tile[32][33];
+// out[n][k] = in[k][n] for a [K, N] matrix of bytes or of f32: 32 x 32 tiles through shared memory (padded against bank
+// conflicts).
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_kernel(const T* __restrict__ in, T* __restrict__ out, uint32_t K, uint32_t N) {
+    __shared__ T tile[32][33];
     const uint32_t n0 = blockIdx.x * 32u, k0 = blockIdx.y * 32u;
     const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;   // 32 x 8 threads
     for (uint32_t r = ty; r < 32u; r += 8u) {
         const uint32_t k = k0 + r, n = n0 + tx;
-        tile[r][tx] = (k < K && n < N) ? in[(size_t)k * N + n] : (uint8_t)0;
+        tile[r][tx] = (k < K && n < N) ? in[(size_t)k * N + n] : T(0);
     }
     __syncthreads();
     for (uint32_t r = ty; r < 32u; r += 8u) {
@@ -248,8 +250,15 @@ int launch_affine_dequantize_g64(rusty_cuda_ctx* ctx, const uint8_t* w, const fl
 int launch_transpose_u8(rusty_cuda_ctx* ctx, const uint8_t* in, uint8_t* out, uint32_t K, uint32_t N) {
     const dim3 grid((N + 31) / 32, (K + 31) / 32);
     if (grid.y > 65535u) return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "transpose: K=%u too large", K);
-    transpose_u8_kernel<<<grid, 256, 0, ctx->stream>>>(in, out, K, N);
+    transpose_kernel<uint8_t><<<grid, 256, 0, ctx->stream>>>(in, out, K, N);
     return after_launch(ctx, "transpose_u8");
+}
+
+int launch_transpose_f32(rusty_cuda_ctx* ctx, const float* in, float* out, uint32_t K, uint32_t N) {
+    const dim3 grid((N + 31) / 32, (K + 31) / 32);
+    if (grid.y > 65535u) return fail(ctx, RUSTY_CUDA_ERR_INVALID_DIMENSIONS, "transpose: K=%u too large", K);
+    transpose_kernel<float><<<grid, 256, 0, ctx->stream>>>(in, out, K, N);
+    return after_launch(ctx, "transpose_f32");
 }
 
 int launch_residual_add(rusty_cuda_ctx* ctx, const void* a, const void* b, void* out, size_t n, int y_dtype) {

@@ -109,6 +109,39 @@ def test_gemv_kn_layout(ctx, engine, oracle, M, K, N):
         assert rel_err(got, ref) <= TOL_FP32
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (2, 128, 64), (1, 1152, 192), (2, 11008, 4096), (5, 4096, 11008), (1, 8192, 64),
+                                   (2, 6144, 128)])
+def test_affine_g64_in_rustys_own_layout_takes_the_tensor_core_gemv(ctx, engine, oracle, M, K, N):
+    """The reference's own quantised format ([in,out] bytes, one (scale, bias) per 64 consecutive output features of an
+    input row, rusty-loader/src/lib.rs:155-218) with K % 128 == 0: re-laid-out once at create, then the int8 tensor-core
+    GEMV with the group's scales folded into the activations.  Against the reference's arithmetic (dequantise, then the
+    f32 matmul) and against the exact sums."""
+    x, q, _ = sym_row_linear(K + 5 * N + M, M, K, N)
+    x[0, ::97] *= 40.0   # a heavy tail inside every K slice
+    rng = np.random.default_rng(K + N)
+    ukn = (np.ascontiguousarray(q.T).astype(np.int16) + 128).astype(np.uint8)
+    sg = rng.uniform(0.001, 0.02, size=K * N // 64).astype(np.float32)
+    bg = (-128.0 * sg + rng.uniform(-0.05, 0.05, size=sg.size)).astype(np.float32)
+    ql = QLinear.from_host(ctx, ukn, sg, bg, layout=capi.LAYOUT_KN)
+    assert ql.plan(M) == "gemv_mma"
+    got = _forward(ctx, engine, ql, x)
+    wkn = oracle.affine_dequantize(ukn, sg, bg, mt=True).reshape(K, N)
+    wf = np.ascontiguousarray(wkn.T)
+    ref = oracle.matmul_bt(x, wf, mt=True)
+    assert rel_err(got, ref) <= TOL_FP32
+    assert rel_err(got, oracle.matmul_bt_f64(x, wf)) <= max(_oracle_band(oracle, x, wf, ref), 1e-6) * 1.5
+    # bf16 activations are consumed exactly; a bf16 y is the f32 result rounded once
+    xb = bf16_bits_to_f32(f32_to_bf16_bits(x))
+    got_b = _forward(ctx, engine, ql, x, x_dtype=DType.BF16)
+    assert rel_err(got_b, oracle.matmul_bt(xb, wf, mt=True)) <= TOL_FP32
+    got16 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.BF16)
+    assert np.array_equal(f32_to_bf16_bits(got16), f32_to_bf16_bits(got_b))
+    # the same answer on every run, and rows of a batch do not depend on their neighbours
+    assert_bits_equal(got, _forward(ctx, engine, ql, x))
+    if M > 1:
+        assert_bits_equal(got[M - 1:], _forward(ctx, engine, ql, x[M - 1:]))
+
+
 def test_bf16_activations_and_outputs(ctx, engine, oracle):
     """bf16 x is consumed exactly (the oracle sees the rounded values); a bf16 y
     is the f32 result rounded once."""
