@@ -334,10 +334,10 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 }
                 if (!mbar_wait(&w_full[ws], wph, abort_flag, p.status, 16)) { ok = false; break; }
                 // row r of the swizzled tile: logical 16-byte chunk c sits at physical chunk c ^ (r & 7)
-                const uint4* row = reinterpret_cast<const uint4*>(sW + (size_t)ws * W_STAGE_BYTES + (size_t)r * WK);
+                const uint32_t row = smem_u32(sW + (size_t)ws * W_STAGE_BYTES + (size_t)r * WK);
                 uint4 raw[4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) raw[c] = row[(half * 4 + c) ^ (r & 7)];
+                for (int c = 0; c < 4; ++c) raw[c] = lds128(row + (uint32_t)(((half * 4 + c) ^ (r & 7)) << 4));   // (kept in front of the hand-back)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&w_empty[ws]);  // this warp's share is in registers
                 if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }

@@ -37,6 +37,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// 16 bytes of shared memory as a volatile asm statement, so that the load stays in front of the mbarrier arrive that
+// hands a ring slot back.  Written as plain C++ loads, the fragment loads of the GEMV were moved behind the arrive, down to
+// the first use of the values: the registers then held what the slot had been refilled with in the meantime.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
 // Bounded wait.  Returns false (after raising the status word) when the limit
 // expires or another role of this CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
