@@ -266,15 +266,21 @@ def run_reference(args, rank: int):
 # ----------------------------------------------------------------------------
 # single-Linear figures (rank 0, N = 1): GEMV GB/s and GEMM TFLOP/s
 # ----------------------------------------------------------------------------
-def bench_single_linear(ctx, eng, M, K, N, x_dtype, y_dtype, iters, warm, l2_bytes=126 * 2**20):
+def bench_single_linear(ctx, eng, M, K, N, x_dtype, y_dtype, iters, warm, l2_bytes=126 * 2**20, native=False):
     """Average device time per launch over `iters` launches that rotate through
-    enough distinct weight copies to exceed L2 (so every launch streams HBM)."""
-    from rusty_b200 import QLinear, UnifiedTensor
+    enough distinct weight copies to exceed L2 (so every launch streams HBM).  `native`: the weight in the reference's own
+    quantised format (u8 [in,out], one f32 scale and bias per 64 consecutive output features of an input row,
+    rusty-loader/src/lib.rs:155-218) instead of int8 [out,in] with one scale per output row."""
+    from rusty_b200 import QLinear, UnifiedTensor, capi
     from rusty_b200.backend import Event
-    from rusty_b200.workloads import sym_row_linear
+    from rusty_b200.workloads import affine_g64_from_sym, sym_row_linear
     x, q, s = sym_row_linear(0, M, K, N)
     copies = max(2, int(np.ceil(1.5 * l2_bytes / (N * K))) + 1)
-    qls = [QLinear.from_host(ctx, q, s) for _ in range(copies)]
+    if native:
+        u, sg, bg = affine_g64_from_sym(np.ascontiguousarray(q.T), 0)
+        qls = [QLinear.from_host(ctx, u, sg, bg, layout=capi.LAYOUT_KN) for _ in range(copies)]
+    else:
+        qls = [QLinear.from_host(ctx, q, s) for _ in range(copies)]
     from rusty_b200 import DType
     xt = UnifiedTensor.from_bf16(ctx, x, [M, K]) if x_dtype == DType.BF16 else UnifiedTensor.new(ctx, x, [M, K])
     y = UnifiedTensor.empty_with_dtype(ctx, [M, N], y_dtype)
@@ -294,7 +300,7 @@ def bench_single_linear(ctx, eng, M, K, N, x_dtype, y_dtype, iters, warm, l2_byt
     e1.record()
     ms = e0.elapsed_ms(e1) / iters
     plan = qls[0].plan(M, x_dtype, y_dtype)
-    alg_bytes = N * K + N * 4 + M * K * x_dtype.size_bytes() + M * N * y_dtype.size_bytes()
+    alg_bytes = N * K + (N * K // 64 * 8 if native else N * 4) + M * K * x_dtype.size_bytes() + M * N * y_dtype.size_bytes()
     del qls
     return {"M": M, "K": K, "N": N, "kernel": plan, "us_per_launch": ms * 1e3, "algorithmic_bytes": alg_bytes,
             "gbs": alg_bytes / (ms * 1e-3) / 1e9, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "weight_copies": copies}
@@ -570,7 +576,10 @@ def main():
         g2["frac_of_hbm_peak"] = g2["gbs"] / peaks["hbm_gbs"]
         mm = bench_single_linear(ctx, eng, 512, 4096, 11008, DType.BF16, DType.BF16, 30, 5)
         mm["frac_of_bf16_peak"] = mm["tflops"] / peaks["bf16_tflops"]
-        line["gemv"] = {"config0_f32_1x4096x4096": g1, "config1_bf16_1x4096x11008": g2}
+        g0 = bench_single_linear(ctx, eng, 1, 4096, 4096, DType.FP32, DType.FP32, 200, 20, native=True)
+        g0["frac_of_hbm_peak"] = g0["gbs"] / peaks["hbm_gbs"]
+        g0["weights"] = "the reference's own format: u8 [in,out], f32 scale and bias per 64 consecutive outputs of an input row"
+        line["gemv"] = {"config0_f32_1x4096x4096": g1, "config1_bf16_1x4096x11008": g2, "config0_native_affine_f32_1x4096x4096": g0}
         line["gemm"] = {"config1_bf16_512x4096x11008": mm, "peak_tflops": peaks["bf16_tflops"]}
         cs = CpuSample(stack_name, M)
         cs.two_step()
