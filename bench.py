@@ -459,7 +459,7 @@ def main():
                          "exchange at all, a diagnostic lower bound whose line is not a benchmark result")
     ap.add_argument("--no-swiglu", action="store_true",
                     help="write gate|up as [M, 2*ffn] instead of applying silu(gate)*up in the kernel's epilogue")
-    ap.add_argument("--single", default=None, metavar="MxKxN:f32|bf16",
+    ap.add_argument("--single", default=None, metavar="MxKxN:f32|bf16[-native]",
                     help="run ONE fused linear of this shape --steps times on rotating weight copies and print its "
                          "timing (small case for profiler captures; not the benchmark line)")
     args = ap.parse_args()
@@ -478,9 +478,10 @@ def main():
         from rusty_b200 import DType
         shape, _, dt = args.single.partition(":")
         M, K, N = (int(v) for v in shape.lower().split("x"))
-        d = DType.BF16 if dt == "bf16" else DType.FP32
+        native = dt.endswith("-native")   # e.g. 1x4096x4096:f32-native = the reference's own affine [in,out] format
+        d = DType.BF16 if dt.startswith("bf16") else DType.FP32
         ctx = rusty_b200.CudaContext(local_rank)
-        r = bench_single_linear(ctx, rusty_b200.ComputeEngine(ctx), M, K, N, d, d, max(1, args.steps), max(1, args.warmup))
+        r = bench_single_linear(ctx, rusty_b200.ComputeEngine(ctx), M, K, N, d, d, max(1, args.steps), max(1, args.warmup), native=native)
         print(json.dumps({"single": args.single, **r}), flush=True)
         return
 
