@@ -64,7 +64,7 @@ import torch, torch.distributed as dist
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo")                       # host channel for the IPC handles only
 import rusty_b200
-from rusty_b200 import DType, QLinear, UnifiedTensor
+from rusty_b200 import DType, QLinear, UnifiedTensor, capi
 from rusty_b200.shard import Arena, arena_layout, forward_pushed, shard_rows
 from rusty_b200.workloads import sym_row_linear
 from rusty_b200.backend import bf16_bits_to_f32
@@ -72,7 +72,8 @@ from parity import rel_err
 ctx = rusty_b200.CudaContext(rank)
 eng = rusty_b200.ComputeEngine(ctx)
 cases = [(32, 4096, 2048, DType.FP32), (1, 1024, 512, DType.FP32), (256, 512, 1024, DType.FP32),
-         (128, 1024, 768, DType.BF16), (3, 256, 6 * world, DType.FP32), (32, 4096, 2048, DType.FP32)]
+         (128, 1024, 768, DType.BF16), (3, 256, 6 * world, DType.FP32), (32, 4096, 2048, DType.FP32),
+         (2, 1024, 512, "native"), (5, 2048, 1024, "native")]   # native: the reference's affine [in,out] format
 sizes = [(i % 2, max(M * N * 4 for j, (M, K, N, dt) in enumerate(cases) if j % 2 == i % 2)) for i in range(len(cases))]
 offsets, total = arena_layout(sizes)
 arena = Arena(ctx, total, world, rank)
@@ -82,8 +83,20 @@ pending = []
 for i, (M, K, N, dt) in enumerate(cases):
     x, q, s = sym_row_linear(M + N + i, M, K, N)
     rows = shard_rows(N, world, rank)
-    shard = QLinear.from_host(ctx, q[rows], s[rows])
-    full = QLinear.from_host(ctx, q, s)
+    if dt == "native":
+        # u8 [K, N], one (scale, bias) per 64 consecutive outputs of an input row; a rank's shard is whole groups
+        dt = DType.FP32
+        rng = np.random.default_rng(i)
+        ukn = (np.ascontiguousarray(q.T).astype(np.int16) + 128).astype(np.uint8)
+        sg = rng.uniform(0.001, 0.02, size=(K, N // 64)).astype(np.float32)
+        bg = (-128.0 * sg + rng.uniform(-0.05, 0.05, size=sg.shape)).astype(np.float32)
+        g = slice(rows.start // 64, rows.stop // 64)
+        shard = QLinear.from_host(ctx, np.ascontiguousarray(ukn[:, rows]), np.ascontiguousarray(sg[:, g]), np.ascontiguousarray(bg[:, g]), layout=capi.LAYOUT_KN)
+        full = QLinear.from_host(ctx, ukn, sg, bg, layout=capi.LAYOUT_KN)
+        assert shard.plan(M) == "gemv_mma"
+    else:
+        shard = QLinear.from_host(ctx, q[rows], s[rows])
+        full = QLinear.from_host(ctx, q, s)
     xt = UnifiedTensor.from_bf16(ctx, x, [M, K]) if dt == DType.BF16 else UnifiedTensor.new(ctx, x, [M, K])
     y = arena.tensor(offsets[i % 2], [M, N], dt)
     forward_pushed(ctx, arena, shard, xt, M, y)
