@@ -35,6 +35,9 @@ WORKLOADS = {
     "llama3-8b-decode32": ("llama3-8b", 32, "Llama-3-8B-shaped GQA linear stack, random int8 weights, batch-32 decode"),
     "llama7b-decode1": ("llama7b", 1, "Llama-7B-shaped linear stack, random int8 weights, batch-1 decode"),
     "llama2-70b-decode64": ("llama2-70b", 64, "Llama-2-70B-shaped linear stack, random int8 weights, batch-64 decode"),
+    # the same batch-1 decode with every weight in the reference's own quantised format (fifth field: "native")
+    "llama7b-decode1-native": ("llama7b", 1, "Llama-7B-shaped linear stack, random u8 weights in the reference's own format "
+                               "([in,out], f32 scale and bias per 64 consecutive outputs of an input row), batch-1 decode", "f32", "native"),
     # prefill: every Linear at M = all prompt tokens, bf16 activations in and out, fp32 accumulate (tensor-core bound)
     "llama3-8b-prefill2048": ("llama3-8b", 2048, "Llama-3-8B-shaped GQA linear stack, random int8 weights, 2048-token prefill", "bf16"),
     "llama2-70b-prefill8192": ("llama2-70b", 8192, "Llama-2-70B-shaped linear stack, random int8 weights, batch 4 x 2048-token prefill", "bf16"),
@@ -45,6 +48,10 @@ def workload(name):
     """(stack, M, description, activation dtype) of a workload."""
     w = WORKLOADS[name]
     return w[0], w[1], w[2], (w[3] if len(w) > 3 else "f32")
+def workload_is_native(name):
+    """Whether the workload's weights are in the reference's own affine [in,out] format."""
+    w = WORKLOADS[name]
+    return len(w) > 4 and w[4] == "native"
 DEFAULT_WORKLOAD = "llama3-8b-decode32"
 
 
@@ -224,7 +231,9 @@ def workload_config(args, M: int, desc: str) -> dict:
     layers = shape.layers if args.layers is None else args.layers
     return {"workload": args.workload, "desc": desc, "batch_rows": M, "layers": layers,
             "linears_per_step": 4 * layers + 1,
-            "weights": "int8 [out,in], f32 scale per output row; q|k|v and gate|up run as one Linear each",
+            "weights": ("u8 [in,out], f32 scale and bias per 64 consecutive outputs of an input row (the reference's own format); "
+                        "q|k|v and gate|up run as one Linear each") if workload_is_native(args.workload)
+                       else "int8 [out,in], f32 scale per output row; q|k|v and gate|up run as one Linear each",
             "activations": "%s in, %s out, fp32 accumulate" % (act, act),
             "l2": "inputs larger than L2: every step streams all %.2f GB of weights, each layer from its own buffer"
                   % (sum(n * k for _p, n, k in shape.per_layer()) * layers / 1e9 + shape.vocab * shape.d / 1e9)}
@@ -307,7 +316,7 @@ def bench_single_linear(ctx, eng, M, K, N, x_dtype, y_dtype, iters, warm, l2_byt
 
 
 def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, warmup, clocks=False, e2e_logits=True,
-              norms=False, act="f32"):
+              norms=False, act="f32", native=False):
     """One workload on this process group: the device-timed step (inputs resident in HBM), the end-to-end step (host
     activations in, rank 0 reads the logits back) and the greedy step (the token chosen on the device).  Returns the
     max-over-ranks figures; builds and frees its own weights."""
@@ -319,7 +328,7 @@ def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, wa
     dt = DType.BF16 if act == "bf16" else DType.FP32
     npdt = np.uint16 if act == "bf16" else np.float32
     stack = LinearStack(ctx, shape, M, dt, dt, seed=0, rank=rank, world=world, layers=args.layers,
-                        swiglu=not args.no_swiglu, norms=norms)
+                        swiglu=not args.no_swiglu, norms=norms, native=native)
     if world > 1 and args.exchange != "none":
         from rusty_b200.shard import PushedStack, ShardedStack
         runner = PushedStack(stack, dist) if args.exchange == "push" else ShardedStack(stack, dist)
@@ -507,7 +516,8 @@ def main():
     ctx = rusty_b200.CudaContext(local_rank)
     eng = rusty_b200.ComputeEngine(ctx)
     shape = STACKS[stack_name]
-    r = run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, args.steps, args.warmup, clocks=True, act=act)
+    native = workload_is_native(args.workload)
+    r = run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, args.steps, args.warmup, clocks=True, act=act, native=native)
     ms_step, launches, clocks, e2e, greedy = r["ms_step"], r["launches"], r["clocks"], r["e2e"], r["greedy"]
     alg_bytes, weight_gb, plans, swiglu = r["alg_bytes"], r["weight_gb"], r["plans"], r["swiglu"]
 
@@ -550,7 +560,7 @@ def main():
 
     # The block's RMSNorms riding in the Linears that follow them (norm1 -> q|k|v, norm2 + residual -> gate|up, final
     # norm -> lm_head): the same step with 65 norms added, as an extra key.
-    if world == 1 and not args.no_extras and args.layers is None and not prefill:
+    if world == 1 and not args.no_extras and args.layers is None and not prefill and not native:
         rn = run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, args.steps, args.warmup, e2e_logits=False, norms=True)
         line["with_rms_norms"] = {"value": M / (rn["ms_step"] * 1e-3), "unit": "tokens/s", "ms_per_step": rn["ms_step"],
                                   "gpu_launches": rn["launches"],

@@ -29,7 +29,8 @@ from .workloads import StackShape
 class LinearStack:
     def __init__(self, ctx: CudaContext, shape: StackShape, M: int, x_dtype: DType = DType.FP32,
                  y_dtype: DType = DType.FP32, seed: int = 0, rank: int = 0, world: int = 1,
-                 layers: Optional[int] = None, fuse: bool = True, swiglu: bool = False, norms: bool = False):
+                 layers: Optional[int] = None, fuse: bool = True, swiglu: bool = False, norms: bool = False,
+                 native: bool = False, keep_host: bool = False):
         self.ctx, self.shape, self.M = ctx, shape, M
         self.x_dtype, self.y_dtype = x_dtype, y_dtype
         self.rank, self.world = rank, world
@@ -43,7 +44,13 @@ class LinearStack:
         self.full_n: List[int] = []              # output columns over all ranks
         # gate|up stored pair-interleaved with silu(gate)*up applied in the kernel's epilogue (MLP::forward,
         # rusty-graph/src/lib.rs:317-323): its output is [M, ffn] and the [M, 2*ffn] intermediate never exists
-        self.swiglu = swiglu and fuse
+        # native: every weight in the reference's own quantised format (u8 [in,out], one f32 scale and bias per 64
+        # consecutive output features of an input row, rusty-loader/src/lib.rs:155-218) instead of int8 [out,in] with
+        # one scale per output row; the pair epilogue needs the latter, so gate|up then writes [M, 2*ffn]
+        self.native = native
+        # keep_host (tests, small shapes only): the dequantised f32 weight [rows, K] of every Linear, as the reference holds it
+        self.host_wf: List[Optional[np.ndarray]] = []
+        self.swiglu = swiglu and fuse and not native
 
         def draw(n: int, k: int):
             if (n, k) not in host_w:
@@ -80,8 +87,22 @@ class LinearStack:
             else:
                 qcat = qs[0] if len(qs) == 1 else np.concatenate(qs, axis=0)
                 scat = ss[0] if len(ss) == 1 else np.concatenate(ss)
-                ql = QLinear.from_host(ctx, qcat, scat)
                 n_rows = qcat.shape[0]
+                if native:
+                    assert n_rows % 64 == 0, f"{name}: {n_rows} output features of this rank are not whole groups of 64"
+                    ukn = (np.ascontiguousarray(qcat.T).astype(np.int16) + 128).astype(np.uint8)
+                    sg = np.random.default_rng(seed + 131 * n_rows + k).uniform(0.001, 0.02, size=(k, n_rows // 64)).astype(np.float32)
+                    bg = (np.float32(-128.0) * sg).astype(np.float32)
+                    ql = QLinear.from_host(ctx, ukn, sg, bg, layout=capi.LAYOUT_KN)
+                    if keep_host:   # w[k, n] = u * s[k, n / 64] + b[k, n / 64], rounded as the reference's dequantisation does
+                        wkn = ukn.astype(np.float32) * np.repeat(sg, 64, axis=1) + np.repeat(bg, 64, axis=1)
+                        self.host_wf.append(np.ascontiguousarray(wkn.T))
+                else:
+                    ql = QLinear.from_host(ctx, qcat, scat)
+                    if keep_host:
+                        self.host_wf.append(qcat.astype(np.float32) * scat[:, None])
+            if len(self.host_wf) < len(self.qls) + 1:
+                self.host_wf.append(None)
             self.qls.append(ql)
             self.names.append(name)
             self.dims.append((n_rows, k))
@@ -128,7 +149,8 @@ class LinearStack:
 
     def algorithmic_bytes(self) -> int:
         xs, ys = self.x_dtype.size_bytes(), self.y_dtype.size_bytes()
-        b = sum(n * k + n * 4 + self.M * k * xs + self.M * no * ys for (n, k), no in zip(self.dims, self.out_n))
+        per_w = (lambda n, k: n * k + n * k // 64 * 8) if self.native else (lambda n, k: n * k + n * 4)
+        b = sum(per_w(n, k) + self.M * k * xs + self.M * no * ys for (n, k), no in zip(self.dims, self.out_n))
         for (n, k), w, r in zip(self.dims, self.norm_w, self.norm_res):
             if w is not None:   # norm weight, and for the residual form the residual read and the sum written
                 b += k * 4 + (2 * self.M * k * 4 if r is not None else 0)
