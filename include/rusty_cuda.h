@@ -191,7 +191,8 @@ RUSTY_CUDA_API int rusty_cuda_add_f32(rusty_cuda_ctx* ctx, const rusty_cuda_buf*
  * the same way, bytes to [out,in] and scales / biases to [N/64][K] (N*K*9/8
  * more bytes; none of the caller's three buffers is kept): its forwards run on
  * the int8 tensor-core GEMV with the group's scales folded into the
- * activations.  (RUSTY_KN_RELAYOUT=0 in the environment keeps the [in,out]
+ * activations (f32 activations: 1e-5 of the reference's arithmetic) and, with
+ * bf16 activations and M >= 65, on the bf16 tensor-core kernel (1e-2).  (RUSTY_KN_RELAYOUT=0 in the environment keeps the [in,out]
  * CUDA-core kernel for both.)
  *   AFFINE_G64: weight u8 [N*K], scales/biases f32 [N*K/64]; K % 64 == 0 for
  *               LAYOUT_NK (N % 64 == 0 for LAYOUT_KN) so a group never

@@ -145,6 +145,25 @@ __device__ __forceinline__ void u8x16_affine_to_bf16x2(const uint4& w, float sc,
     }
 }
 
+// The same with one (scale, bias) per element: 16 consecutive k of one row whose scales and biases are 16 consecutive
+// floats each (an [in,out] affine weight after its re-layout: groups run along the output dimension).
+__device__ __forceinline__ void u8x16_affine_vec_to_bf16x2(const uint4& w, const float* __restrict__ sc, const float* __restrict__ bi, uint32_t* out) {
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t u = words[i];
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sc) + i), b4 = __ldg(reinterpret_cast<const float4*>(bi) + i);
+        const float f0 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388608.0f, s4.x, b4.x);
+        const float f1 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388608.0f, s4.y, b4.y);
+        const float f2 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388608.0f, s4.z, b4.z);
+        const float f3 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388608.0f, s4.w, b4.w);
+        __nv_bfloat162 a = __floats2bfloat162_rn(f0, f1);
+        __nv_bfloat162 b = __floats2bfloat162_rn(f2, f3);
+        out[2 * i] = *reinterpret_cast<uint32_t*>(&a);
+        out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
+    }
+}
+
 // One piece of work: weight stages [s0, s1) of output tile `u`.  nseg > 1: the tile is shared with other CTAs.
 struct Piece {
     int u, s0, s1, nseg, lu;
@@ -189,7 +208,10 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-template <typename YT, bool AFFINE>
+// QM: 0 = one scale per output row (applied to the sums); 1 = AFFINE_G64 with groups along K ([N][K/64] scales and biases);
+// 2 = AFFINE_G64 of an [in,out] weight after its re-layout: one (scale, bias) per 64 consecutive OUTPUT rows and k,
+// stored [N/64][K] (internal mode QMODE_AFFINE_GC)
+template <typename YT, int QM>
 __global__ void __launch_bounds__(F16_THREADS, 1)
 qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const F16Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -324,7 +346,21 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             for (int s = pc.s0; s < pc.s1 && ok; ++s) {
                 // affine: this thread's 64 k-elements of the stage are exactly one group of its row (K % 64 == 0)
                 float g_sc = 0.0f, g_bi = 0.0f;
-                if constexpr (AFFINE) {
+                [[maybe_unused]] const float* gc_s = nullptr;   // QM == 2: this warp's 64 scales and 64 biases of the stage (its 32
+                [[maybe_unused]] const float* gc_b = nullptr;   // rows lie in one group: the addresses are warp-uniform)
+                if constexpr (QM == 2) {
+                    const int k0 = s * WK + half * 64;
+                    if (n_row < p.N && k0 < p.K) {
+                        gc_s = p.scales + (size_t)(n_row >> 6) * p.K + k0;
+                        gc_b = p.biases + (size_t)(n_row >> 6) * p.K + k0;
+                        // the next stage's two 256-byte lines into L1 while this stage is converted
+                        if (s + 1 < pc.s1 && k0 + WK < p.K && lane < 4) {
+                            asm volatile("prefetch.global.L1 [%0];" ::"l"(gc_s + WK + lane * 16));
+                            asm volatile("prefetch.global.L1 [%0];" ::"l"(gc_b + WK + lane * 16));
+                        }
+                    }
+                }
+                if constexpr (QM == 1) {
                     const int k0 = s * WK + half * 64;
                     if (n_row < p.N && k0 < p.K) {
                         const size_t g = ((size_t)n_row * p.K + k0) >> 6;
@@ -342,7 +378,15 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 if (lane == 0) mbar_arrive(&w_empty[ws]);  // this warp's share is in registers
                 if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
                 uint32_t cv[32];
-                if constexpr (AFFINE) {
+                if constexpr (QM == 2) {
+                    if (gc_s) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) u8x16_affine_vec_to_bf16x2(raw[c], gc_s + 16 * c, gc_b + 16 * c, cv + 8 * c);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) cv[e] = 0u;
+                    }
+                } else if constexpr (QM == 1) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) u8x16_affine_to_bf16x2(raw[c], g_sc, g_bi, cv + 8 * c);
                 } else {
@@ -378,7 +422,7 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const int t = pc.u % p.tiles_w, j = pc.u / p.tiles_w;
             const int n = t * BM + r;
             const bool row_ok = n < p.N;
-            const float sc = !row_ok ? 0.0f : AFFINE ? 1.0f : __ldg(p.scales + n);
+            const float sc = !row_ok ? 0.0f : QM != 0 ? 1.0f : __ldg(p.scales + n);
             if (!mbar_wait(d_full, (uint32_t)i & 1u, abort_flag, p.status, 18)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -478,7 +522,10 @@ namespace rusty {
 bool f16tc_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
     if (!encode_tiled_fn()) return false;
     if (a.layout != RUSTY_CUDA_LAYOUT_NK) return false;
-    if (a.qmode == RUSTY_CUDA_QMODE_AFFINE_G64 ? (a.K % 64 != 0 || a.act) : a.qmode != RUSTY_CUDA_QMODE_SYM_ROW) return false;
+    if (a.qmode == RUSTY_CUDA_QMODE_AFFINE_G64 ? (a.K % 64 != 0 || a.act)
+        : a.qmode == QMODE_AFFINE_GC          ? (a.K % 128 != 0 || a.N % 64 != 0 || a.act)
+                                              : a.qmode != RUSTY_CUDA_QMODE_SYM_ROW)
+        return false;
     if (a.x_dtype != RUSTY_CUDA_BF16) return false;
     if (a.K % 16 != 0) return false;
     if ((reinterpret_cast<uintptr_t>(a.w) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return false;
@@ -488,7 +535,7 @@ bool f16tc_supported(const rusty_cuda_ctx*, const QLinearArgs& a) {
 int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     F16Params p{};
     p.scales = a.scales;
-    p.biases = a.qmode == RUSTY_CUDA_QMODE_AFFINE_G64 ? a.biases : nullptr;
+    p.biases = (a.qmode == RUSTY_CUDA_QMODE_AFFINE_G64 || a.qmode == QMODE_AFFINE_GC) ? a.biases : nullptr;
     p.y = a.y;
     p.Mx = (int)a.M;
     p.N = (int)a.N;
@@ -544,9 +591,10 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
         }
     }
     const bool yb = a.y_dtype == RUSTY_CUDA_BF16;
-    const bool affine = p.biases != nullptr;
-    auto kern = affine ? (yb ? qlinear_f16_tc_kernel<__nv_bfloat16, true> : qlinear_f16_tc_kernel<float, true>)
-                       : (yb ? qlinear_f16_tc_kernel<__nv_bfloat16, false> : qlinear_f16_tc_kernel<float, false>);
+    const int qm = a.qmode == QMODE_AFFINE_GC ? 2 : p.biases != nullptr ? 1 : 0;
+    auto kern = qm == 2   ? (yb ? qlinear_f16_tc_kernel<__nv_bfloat16, 2> : qlinear_f16_tc_kernel<float, 2>)
+                : qm == 1 ? (yb ? qlinear_f16_tc_kernel<__nv_bfloat16, 1> : qlinear_f16_tc_kernel<float, 1>)
+                          : (yb ? qlinear_f16_tc_kernel<__nv_bfloat16, 0> : qlinear_f16_tc_kernel<float, 0>);
     {
         cudaError_t e = ensure_dynamic_smem((const void*)kern, ctx->device, smem);
         if (e != cudaSuccess) return check_cuda(ctx, e, "qlinear_f16_tc: cudaFuncSetAttribute");

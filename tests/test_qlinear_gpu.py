@@ -446,6 +446,32 @@ def test_prefill_affine_g64_on_the_bf16_kernel(ctx, engine, oracle, M, K, N):
     # f32 activations keep the exact CUDA-core kernel
     assert ql.plan(M, DType.FP32, DType.FP32) == "gemv"
 
+@pytest.mark.parametrize("M,K,N", [(128, 512, 256), (300, 4096, 1024), (96, 128, 64), (2048, 4096, 512), (65, 1152, 192), (512, 4096, 11008)])
+def test_prefill_native_affine_layout_on_the_bf16_kernel(ctx, engine, oracle, M, K, N):
+    """rusty's own [in,out] storage in the reference's affine format (groups of 64 along the OUTPUT dimension), bf16
+    activations, M >= 65: after the one-time re-layout the converter warps apply one (scale, bias) per element while
+    converting (a warp's 32 rows lie in one group, so the 64 scales of a stage are the same addresses for every lane)."""
+    x, q, _ = sym_row_linear(7 * K + N + M, M, K, N)
+    rng = np.random.default_rng(K + 3 * N)
+    ukn = (np.ascontiguousarray(q.T).astype(np.int16) + 128).astype(np.uint8)
+    sg = rng.uniform(0.001, 0.02, size=K * N // 64).astype(np.float32)
+    bg = (np.float32(-128.0) * sg * rng.uniform(0.9, 1.1, size=sg.size)).astype(np.float32)
+    ql = QLinear.from_host(ctx, ukn, sg, bg, layout=capi.LAYOUT_KN)
+    assert ql.plan(M, DType.BF16, DType.BF16) == "tcgen05_f16"
+    assert ql.plan(M, DType.FP32, DType.FP32) == "gemv_mma"      # f32 activations keep the exact path
+    xb = bf16_bits_to_f32(f32_to_bf16_bits(x))
+    got32 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.FP32)
+    got16 = _forward(ctx, engine, ql, x, x_dtype=DType.BF16, y_dtype=DType.BF16)
+    wf = np.ascontiguousarray(oracle.affine_dequantize(ukn, sg, bg, mt=True).reshape(K, N).T)
+    rows = slice(None) if M * N * K < 3e9 else [0, 1, M // 2, M - 1]
+    ref = oracle.matmul_bt(xb[rows], wf, mt=True)
+    assert np.isfinite(got32).all()
+    assert rel_err_rows(got32[rows], ref) <= TOL_BF16
+    assert rel_err_rows(got16[rows], ref) <= TOL_BF16
+    wb = bf16_bits_to_f32(f32_to_bf16_bits(wf)).reshape(N, K)
+    assert rel_err(got32[rows], xb[rows].astype(np.float64) @ wb.astype(np.float64).T) <= 5e-4
+
+
 @pytest.mark.parametrize("M,K,N", [(128, 512, 256), (512, 4096, 1024), (200, 1024, 130), (96, 4096, 4096), (300, 80, 24),
                                    (512, 4096, 11008)])
 def test_prefill_f16_shapes(ctx, engine, oracle, M, K, N):
