@@ -370,7 +370,19 @@ def run_stack(ctx, dist, args, stack_name, M, rank, world, local_rank, steps, wa
     barrier()
     launches = ctx.launch_count() - l0
     ms_step = max_over_ranks(ms_total / steps)
+    # A box whose NVML calls are slow yields only a sample or two in a 60 ms region: every rank then repeats the same
+    # steps, untimed, with the sampler still running, so that the clock figure always rests on a handful of samples
+    # of the device under this load; `samples_in_timed_region` says how many fell into the timed steps themselves.
+    in_region = len(sampler.sm) if sampler else 0
+    few = max_over_ranks(1.0 if (sampler and in_region < 5) else 0.0) > 0.0
+    if few:
+        for _ in range(3 * steps):   # the same count on every rank: the ranks meet in every Linear
+            runner.replay()
+        ctx.sync()
+        barrier()
     clk = sampler.stop() if sampler else None
+    if clk is not None:
+        clk["samples_in_timed_region"] = in_region
 
     # ---- end-to-end: host activations in on every rank, host logits out on rank 0, every step ----
     d_in = shape.d
