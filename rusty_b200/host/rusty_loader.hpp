@@ -325,9 +325,13 @@ public:
         const float* scales;
         const float* biases;
         size_t rows, cols, groups;
+        // column shards of [in,out] storage are gathered copies (a column block is not contiguous in the file)
+        std::shared_ptr<std::vector<unsigned char>> own_q;
+        std::shared_ptr<std::vector<float>> own_s, own_b;
     };
-    // Host views of the part of `name` that `rank` of `world` keeps (whole output rows; needs [out,in] storage and an
-    // input width that is a multiple of 64 when world > 1).
+    // Host views of the part of `name` that `rank` of `world` keeps: a block of output features made of whole groups --
+    // rows of an [out,in] matrix whose input width is a multiple of 64, or columns of an [in,out] matrix whose output
+    // width is a multiple of 64 * world.
     QuantizedShard quantized_shard(const std::string& name, int layout = RUSTY_CUDA_LAYOUT_KN, int rank = 0, int world = 1) const {
         const std::string wn = name + ".weight";
         if (!contains(wn)) throw LoaderError("MissingWeight", wn);
@@ -340,9 +344,25 @@ public:
         const size_t groups = (total + GROUP - 1) / GROUP;
         if ((s.second->end - s.second->begin) / 4 < groups || (b.second->end - b.second->begin) / 4 < groups)
             throw LoaderError("Safetensors", name + ": too few (scale, bias) pairs");
-        QuantizedShard out{w.first, reinterpret_cast<const float*>(s.first), reinterpret_cast<const float*>(b.first), rows, cols, groups};
-        if (world > 1) {
-            if (layout != RUSTY_CUDA_LAYOUT_NK) throw LoaderError("Safetensors", name + ": sharding by output rows needs the [out,in] layout");
+        QuantizedShard out{w.first, reinterpret_cast<const float*>(s.first), reinterpret_cast<const float*>(b.first), rows, cols, groups, {}, {}, {}};
+        if (world > 1 && layout == RUSTY_CUDA_LAYOUT_KN) {
+            // [in,out]: rows = input features, cols = output features; the groups of 64 run along the columns
+            if (cols % ((size_t)world * GROUP) != 0) throw LoaderError("Safetensors", name + ": cannot be cut into column shards of whole groups");
+            const size_t nl = cols / (size_t)world, gpr = cols / GROUP, gl = nl / GROUP;
+            out.own_q = std::make_shared<std::vector<unsigned char>>(rows * nl);
+            out.own_s = std::make_shared<std::vector<float>>(rows * gl);
+            out.own_b = std::make_shared<std::vector<float>>(rows * gl);
+            for (size_t r = 0; r < rows; ++r) {
+                std::memcpy(out.own_q->data() + r * nl, out.q + r * cols + (size_t)rank * nl, nl);
+                std::memcpy(out.own_s->data() + r * gl, out.scales + r * gpr + (size_t)rank * gl, gl * sizeof(float));
+                std::memcpy(out.own_b->data() + r * gl, out.biases + r * gpr + (size_t)rank * gl, gl * sizeof(float));
+            }
+            out.q = out.own_q->data();
+            out.scales = out.own_s->data();
+            out.biases = out.own_b->data();
+            out.cols = nl;
+            out.groups = rows * gl;
+        } else if (world > 1) {
             if (rows % (size_t)world != 0 || cols % GROUP != 0)
                 throw LoaderError("Safetensors", name + ": cannot be cut into row shards of whole groups");
             const size_t nl = rows / (size_t)world, gpr = cols / GROUP;

@@ -183,8 +183,9 @@ class WeightsContext:
     def upload_qlinear(self, name: str, ctx: CudaContext, layout: int = capi.LAYOUT_KN, rank: int = 0,
                        world: int = 1) -> QLinear:
         """`layout`: LAYOUT_KN when the stored matrix is [in,out] (what rusty's Linear multiplies by, lib.rs:69-70),
-        LAYOUT_NK when it is [out,in] (HF / MLX checkpoints).  Sharding by output rows needs LAYOUT_NK and an input
-        width that is a multiple of 64, so that no group straddles two rows."""
+        LAYOUT_NK when it is [out,in] (HF / MLX checkpoints).  A rank's shard is a block of output features made of
+        whole groups: rows of an [out,in] matrix whose input width is a multiple of 64, or columns of an [in,out] matrix
+        whose output width is a multiple of 64 * world."""
         q2, s, b = self.quantized_shard(name, layout, rank, world)
         return QLinear.from_host(ctx, q2, s, b, layout=layout)
 
@@ -194,9 +195,18 @@ class WeightsContext:
         if len(shape) != 2:
             raise LoaderError("Safetensors", f"{name}.weight: a linear weight has two dimensions, got {shape}")
         q2 = q.reshape(shape)
-        if world > 1:
-            if layout != capi.LAYOUT_NK:
-                raise LoaderError("Safetensors", f"{name}: sharding by output rows needs the [out,in] layout")
+        if world > 1 and layout == capi.LAYOUT_KN:
+            # [in,out] storage: the output features are the columns and the groups of 64 run along them, so a rank keeps
+            # whole groups of every input row (copied: a column block is not contiguous in the file)
+            k, n = shape
+            if n % (world * GROUP) != 0:
+                raise LoaderError("Safetensors", f"{name}: [{k},{n}] cannot be cut into {world} column shards of whole groups")
+            nl, gpr = n // world, n // GROUP
+            gl = nl // GROUP
+            q2 = np.ascontiguousarray(q2[:, rank * nl:(rank + 1) * nl])
+            s = np.ascontiguousarray(s.reshape(k, gpr)[:, rank * gl:(rank + 1) * gl]).ravel()
+            b = np.ascontiguousarray(b.reshape(k, gpr)[:, rank * gl:(rank + 1) * gl]).ravel()
+        elif world > 1:
             n, k = shape
             if n % world != 0 or k % GROUP != 0:
                 raise LoaderError("Safetensors", f"{name}: [{n},{k}] cannot be cut into {world} row shards of whole groups")

@@ -1,6 +1,7 @@
 // Exercises the C++ loader mirror (rusty_b200/host/rusty_loader.hpp).
 //   loader_test info <file>                       names, dtypes, shapes (host only: runs without a GPU)
-//   loader_test shard <file> <name> <rank> <world>  FNV-1a checksums of the rank's weight bytes / scales / biases (host only)
+//   loader_test shard <file> <name> <rank> <world>  FNV-1a checksums of the rank's weight bytes / scales / biases (host only);
+//                                                  shard_kn: the same with the matrix read as [in,out] (column shards)
 //   loader_test gpu <file> <name>                  upload both ways on device 0 and compare dequantise-then-matmul
 //                                                  with the fused linear (needs a GPU); prints "ok"
 #include <cmath>
@@ -39,8 +40,8 @@ int main(int argc, char** argv) {
             }
             return 0;
         }
-        if (mode == "shard" && argc == 6) {
-            const auto s = w.quantized_shard(argv[3], RUSTY_CUDA_LAYOUT_NK, std::atoi(argv[4]), std::atoi(argv[5]));
+        if ((mode == "shard" || mode == "shard_kn") && argc == 6) {
+            const auto s = w.quantized_shard(argv[3], mode == "shard" ? RUSTY_CUDA_LAYOUT_NK : RUSTY_CUDA_LAYOUT_KN, std::atoi(argv[4]), std::atoi(argv[5]));
             std::printf("%zu %zu %zu %llu %llu %llu\n", s.rows, s.cols, s.groups, fnv(s.q, s.rows * s.cols), fnv(s.scales, s.groups * 4),
                         fnv(s.biases, s.groups * 4));
             return 0;

@@ -62,6 +62,21 @@ def test_row_shards_match_the_python_loader(exe, checkpoint, world):
         assert r.returncode == 0 and r.stdout.strip() == want, r.stdout + r.stderr
 
 
+@pytest.mark.parametrize("world", [1, 3])
+def test_column_shards_of_in_out_storage_match_the_python_loader(exe, checkpoint, world):
+    """The same tensor read as [in,out] = [64, 192]: three column shards of one 64-group each."""
+    w = WeightsContext()
+    w.load_file(checkpoint)
+    for rank in range(world):
+        q2, s, b = w.quantized_shard("layers.0.q_proj", capi.LAYOUT_KN, rank, world)
+        want = f"{q2.shape[0]} {q2.shape[1]} {s.size} {_fnv(q2.tobytes())} {_fnv(s.tobytes())} {_fnv(b.tobytes())}"
+        r = subprocess.run([exe, "shard_kn", checkpoint, "layers.0.q_proj", str(rank), str(world)], capture_output=True, text=True,
+                           timeout=60)
+        assert r.returncode == 0 and r.stdout.strip() == want, r.stdout + r.stderr
+    r = subprocess.run([exe, "shard_kn", checkpoint, "layers.0.q_proj", "0", "2"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 3 and r.stdout.strip() == "LoaderError Safetensors"     # 96 columns are not whole groups
+
+
 def test_error_variants(exe, checkpoint, tmp_path):
     r = subprocess.run([exe, "info", str(tmp_path / "absent.safetensors")], capture_output=True, text=True, timeout=60)
     assert r.returncode == 3 and r.stdout.strip() == "LoaderError Io"

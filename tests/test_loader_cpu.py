@@ -107,9 +107,32 @@ def test_row_shards_reassemble_the_dequantised_matrix(tmp_path):
             parts.append(_dequant(q2, s2, b2))
         assert np.array_equal(np.concatenate(parts, axis=0), full)
     with pytest.raises(LoaderError):
-        w.quantized_shard("w", capi.LAYOUT_KN, 0, 2)       # [in,out] storage has no contiguous output rows
+        w.quantized_shard("w", capi.LAYOUT_KN, 0, 2)       # read as [in,out] = [32, 192]: 96 columns per rank are not whole groups
     with pytest.raises(LoaderError):
         w.quantized_shard("w", capi.LAYOUT_NK, 0, 3)       # 32 rows do not split three ways
+
+
+def test_column_shards_of_in_out_storage_reassemble_the_dequantised_matrix(tmp_path):
+    """rusty's own [in,out] storage: groups of 64 run along the output dimension, a rank keeps whole groups of every row."""
+    rng = np.random.default_rng(5)
+    k, n = 24, 512
+    q, s, b = _quantized(rng, (k, n))
+    path = str(tmp_path / "m.safetensors")
+    save_file(path, {"w.weight": q, "w.scales": s, "w.biases": b})
+    w = WeightsContext()
+    w.load_file(path)
+    full = _dequant(q, s, b)
+    for world in (1, 2, 4, 8):
+        parts = []
+        for rank in range(world):
+            q2, s2, b2 = w.quantized_shard("w", capi.LAYOUT_KN, rank, world)
+            assert q2.shape == (k, n // world) and q2.flags["C_CONTIGUOUS"] and s2.size == b2.size == k * n // world // GROUP
+            parts.append(_dequant(q2, s2, b2))
+        assert np.array_equal(np.concatenate(parts, axis=1), full)
+    with pytest.raises(LoaderError):
+        w.quantized_shard("w", capi.LAYOUT_KN, 0, 16)      # 32 columns per rank: half a group
+    with pytest.raises(LoaderError):
+        w.quantized_shard("w", capi.LAYOUT_KN, 0, 3)
 
 
 def test_too_few_scales_is_an_error(tmp_path):
