@@ -147,12 +147,12 @@ __device__ __forceinline__ void u8x16_affine_to_bf16x2(const uint4& w, float sc,
 
 // The same with one (scale, bias) per element: 16 consecutive k of one row whose scales and biases are 16 consecutive
 // floats each (an [in,out] affine weight after its re-layout: groups run along the output dimension).
-__device__ __forceinline__ void u8x16_affine_vec_to_bf16x2(const uint4& w, const float* __restrict__ sc, const float* __restrict__ bi, uint32_t* out) {
+__device__ __forceinline__ void u8x16_affine_vec_to_bf16x2(const uint4& w, const float* sc, const float* bi, uint32_t* out) {
     const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t u = words[i];
-        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sc) + i), b4 = __ldg(reinterpret_cast<const float4*>(bi) + i);
+        const float4 s4 = reinterpret_cast<const float4*>(sc)[i], b4 = reinterpret_cast<const float4*>(bi)[i];   // shared memory, broadcast
         const float f0 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388608.0f, s4.x, b4.x);
         const float f1 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388608.0f, s4.y, b4.y);
         const float f2 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388608.0f, s4.z, b4.z);
@@ -235,6 +235,8 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     __shared__ long long s_peer_delta[PEER_MAX_RANKS];
+    // QM == 2: per converter warp two buffers of (64 scales, 64 biases): those of the stage being converted and of the next
+    __shared__ __align__(16) float s_gc[QM == 2 ? CONV_WARPS * 256 : 4];
     if (threadIdx.x == 0) {
         int k = 0;  // the other ranks, compacted (own rank left out); static indices into the parameter
 #pragma unroll
@@ -346,19 +348,31 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             for (int s = pc.s0; s < pc.s1 && ok; ++s) {
                 // affine: this thread's 64 k-elements of the stage are exactly one group of its row (K % 64 == 0)
                 float g_sc = 0.0f, g_bi = 0.0f;
-                [[maybe_unused]] const float* gc_s = nullptr;   // QM == 2: this warp's 64 scales and 64 biases of the stage (its 32
-                [[maybe_unused]] const float* gc_b = nullptr;   // rows lie in one group: the addresses are warp-uniform)
+                // QM == 2: the warp's 32 rows lie in one 64-row group, so the stage's 64 scales and 64 biases are the same
+                // for every lane: lane l copies four of them (cp.async, 16 bytes) into the warp's own corner of shared
+                // memory, one stage ahead of the conversion that reads them back as broadcasts
+                [[maybe_unused]] const float* gc = nullptr;
                 if constexpr (QM == 2) {
-                    const int k0 = s * WK + half * 64;
-                    if (n_row < p.N && k0 < p.K) {
-                        gc_s = p.scales + (size_t)(n_row >> 6) * p.K + k0;
-                        gc_b = p.biases + (size_t)(n_row >> 6) * p.K + k0;
-                        // the next stage's two 256-byte lines into L1 while this stage is converted
-                        if (s + 1 < pc.s1 && k0 + WK < p.K && lane < 4) {
-                            asm volatile("prefetch.global.L1 [%0];" ::"l"(gc_s + WK + lane * 16));
-                            asm volatile("prefetch.global.L1 [%0];" ::"l"(gc_b + WK + lane * 16));
+                    float* mine = s_gc + (size_t)(warp - 2) * 256;
+                    const bool rows_ok = n_row - lane < p.N;   // (N % 64 == 0: the group is inside the matrix or outside)
+                    auto issue = [&](int st, int buf) {
+                        const int k0 = st * WK + half * 64;
+                        if (rows_ok && k0 < p.K) {
+                            const float* src = (lane < 16 ? p.scales : p.biases) + (size_t)(n_row >> 6) * p.K + k0 + (lane & 15) * 4;
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(mine + buf * 128 + lane * 4)), "l"(src) : "memory");
                         }
+                        asm volatile("cp.async.commit_group;" ::: "memory");
+                    };
+                    const int buf = (s - pc.s0) & 1;
+                    if (s == pc.s0) issue(s, buf);
+                    if (s + 1 < pc.s1) {
+                        issue(s + 1, buf ^ 1);
+                        asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    } else {
+                        asm volatile("cp.async.wait_group 0;" ::: "memory");
                     }
+                    __syncwarp();
+                    if (rows_ok && s * WK + half * 64 < p.K) gc = mine + buf * 128;
                 }
                 if constexpr (QM == 1) {
                     const int k0 = s * WK + half * 64;
@@ -379,9 +393,9 @@ qlinear_f16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
                 uint32_t cv[32];
                 if constexpr (QM == 2) {
-                    if (gc_s) {
+                    if (gc) {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) u8x16_affine_vec_to_bf16x2(raw[c], gc_s + 16 * c, gc_b + 16 * c, cv + 8 * c);
+                        for (int c = 0; c < 4; ++c) u8x16_affine_vec_to_bf16x2(raw[c], gc + 16 * c, gc + 64 + 16 * c, cv + 8 * c);
                     } else {
 #pragma unroll
                         for (int e = 0; e < 32; ++e) cv[e] = 0u;
@@ -552,7 +566,9 @@ int launch_f16tc(rusty_cuda_ctx* ctx, const QLinearArgs& a) {
     p.status = ctx->status_dev;
     // bf16 A x bf16 B -> f32: c_format=F32(1)@4, a_format=BF16(1)@7, b_format=BF16(1)@10, N>>3 @17, M>>4 @24
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-    const size_t budget = ctx->smem_optin > 4096 ? ctx->smem_optin - 4096 : 0;
+    // (the group-column affine variant keeps 8 KB of static shared memory for its scales and biases)
+    const size_t reserve = a.qmode == QMODE_AFFINE_GC ? 4096 + 8192 : 4096;
+    const size_t budget = ctx->smem_optin > reserve ? ctx->smem_optin - reserve : 0;
     const size_t x_stage = (size_t)p.BN * XK * 2;
     int xs = (int)((budget - 1024 - 512 - (size_t)W_STAGES * W_STAGE_BYTES) / x_stage);
     if (xs > 8) xs = 8;
