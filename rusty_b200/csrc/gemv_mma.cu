@@ -35,6 +35,10 @@
 //     fixed order, applies scale[n] (held in shared memory; and silu(gate)*up for pairs), rounds to f32 and stores y,
 //     while the compute warps are already on the next group.
 // Every mbarrier wait is bounded.
+//
+// A second instantiation (GC, further down) runs the reference's own quantised format -- u8 [in,out] with one scale and
+// bias per 64 consecutive OUTPUT features of an input row -- after its one-time re-layout to [out,in]: there the scales
+// ride on the activations, one CTA owns part of one 64-row group and one pair of activation rows.
 #include <cstdlib>
 
 #include "tc_common.cuh"
