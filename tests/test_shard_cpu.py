@@ -1,6 +1,7 @@
 """world_size-2 test of the sharding rule on CPU ranks (gloo): each rank applies
-the oracle to its row shard, the pieces are all-gathered and reassembled, and
-the result must equal the unsharded oracle bit for bit."""
+the oracle to its shard of output features (rows of [out,in] weights; columns of the reference's own [in,out] affine
+format, taken through the loader), the pieces are all-gathered and reassembled, and the result must equal the unsharded
+oracle bit for bit."""
 import os
 import sys
 
@@ -41,6 +42,29 @@ def _worker(rank: int, world: int, port: int, q):
         act = assemble([p.numpy() for p in pieces])
         act_ref = O.mul(O.silu(O.qlinear_rowscale(x, w[:F], s[:F])), O.qlinear_rowscale(x, w[F:], s[F:]))
         ok = ok and act.shape == act_ref.shape and np.array_equal(act.view(np.uint32), act_ref.view(np.uint32))
+        # the reference's own format through the loader: u8 [in,out] with a (scale, bias) per 64 consecutive outputs of an
+        # input row; a rank's shard is a column block of whole groups and yields a block of columns of y
+        import tempfile
+        from rusty_b200 import capi
+        from rusty_b200.loader import WeightsContext, save_file
+        Kn, Nn = 128, 256
+        rng = np.random.default_rng(7)
+        ukn = rng.integers(0, 256, size=(Kn, Nn), dtype=np.uint8)
+        sg = rng.uniform(0.001, 0.02, size=Kn * Nn // 64).astype(np.float32)
+        bg = (-128.0 * sg + rng.uniform(-0.05, 0.05, size=sg.size)).astype(np.float32)
+        xn = rng.standard_normal((M, Kn), dtype=np.float32)
+        path = os.path.join(tempfile.gettempdir(), "rusty_shard_cpu_%d_%d.safetensors" % (port, rank))
+        save_file(path, {"w.weight": ukn, "w.scales": sg, "w.biases": bg})
+        wc = WeightsContext()
+        wc.load_file(path)
+        q2, s2, b2 = wc.quantized_shard("w", capi.LAYOUT_KN, rank, world)
+        os.unlink(path)
+        yn_local = O.qlinear_affine(xn, q2, s2, b2, q2.shape, layout_nk=False)
+        pieces = [torch.empty(M, Nn // world, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(pieces, torch.from_numpy(np.ascontiguousarray(yn_local)))
+        yn = assemble([p.numpy() for p in pieces])
+        yn_ref = O.qlinear_affine(xn, ukn, sg, bg, ukn.shape, layout_nk=False)
+        ok = ok and yn.shape == yn_ref.shape and np.array_equal(yn.view(np.uint32), yn_ref.view(np.uint32))
         # the timing protocol of the bench: max over ranks
         t = torch.tensor([float(rank + 1)], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
