@@ -27,6 +27,18 @@ def test_workload_table_is_consistent():
     assert b.workload(b.DEFAULT_WORKLOAD)[:2] == ("llama3-8b", 32) and b.workload(b.DEFAULT_WORKLOAD)[3] == "f32"
 
 
+def test_native_format_workload_is_flagged_and_described():
+    b = _bench()
+    assert b.workload_is_native("llama7b-decode1-native") and not b.workload_is_native("llama7b-decode1")
+    assert [n for n in b.WORKLOADS if b.workload_is_native(n)] == ["llama7b-decode1-native"]
+    args = types.SimpleNamespace(workload="llama7b-decode1-native", layers=None)
+    stack, M, desc, act = b.workload(args.workload)
+    cfg = b.workload_config(args, M, desc)
+    assert (stack, M, act) == ("llama7b", 1, "f32") and "[in,out]" in cfg["weights"] and "64 consecutive outputs" in cfg["weights"]
+    plain = b.workload_config(types.SimpleNamespace(workload="llama7b-decode1", layers=None), 1, "d")
+    assert "[out,in]" in plain["weights"] and cfg["linears_per_step"] == plain["linears_per_step"] == 129
+
+
 def test_both_arms_print_the_same_config():
     b = _bench()
     args = types.SimpleNamespace(workload=b.DEFAULT_WORKLOAD, layers=None)
